@@ -1,0 +1,134 @@
+/* C ABI of the B200 (sm_100a) attention operators.
+ *
+ * Each entry point replaces one dispatcher op that TileCadence's generated extensions register
+ * with TORCH_LIBRARY, with the tensors flattened to raw device pointers, explicit sizes and
+ * element strides. Conventions shared by every call:
+ *   - returns TC_OK (0) or a TC_ERR_* code; tc_last_error() gives the thread-local message
+ *     (the counterpart of the reference's TORCH_CHECK text);
+ *   - `device` is the CUDA ordinal that owns every pointer, `stream` a cudaStream_t (NULL = legacy
+ *     default stream). Work is enqueued on that stream; there is no host synchronisation and no
+ *     host read of device lengths (tilecadence/cuda/decode/decode.cu:50-52);
+ *   - the caller owns and preallocates every buffer, workspaces included; nothing is allocated per
+ *     call. The library keeps one small per-device block (split tickets and a kernel status word)
+ *     that it allocates on the first call for a device, so the first call on a device must happen
+ *     outside CUDA-graph capture;
+ *   - layouts are the reference's: Q/O [B,T,Hq,128], K/V and caches [B,*,Hkv,128], 16-bit
+ *     elements, last dimension contiguous; LSE fp32, natural log; four query heads per KV head;
+ *   - only compute capability 10.x devices are accepted: there is no fallback path.
+ */
+#ifndef TILECADENCE_B200_H
+#define TILECADENCE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TC_OK 0
+#define TC_ERR_INVALID 1 /* argument check failed (shape, stride, alignment, aliasing, range) */
+#define TC_ERR_CUDA 2    /* a CUDA runtime/driver call failed */
+#define TC_ERR_DEVICE 3  /* not an sm_100 device */
+#define TC_ERR_KERNEL 4  /* a kernel reported a bounded wait that expired */
+
+#define TC_ABI_VERSION 1
+
+/* Thread-local text of the last failure on this host thread ("" if none). */
+const char* tc_last_error(void);
+int tc_abi_version(void);
+
+/* Reads and clears the per-device kernel status word (synchronises the device). *status is 0
+ * when no kernel wait expired since the previous call. Has no counterpart in the reference,
+ * whose kernels have no bounded waits. */
+int tc_device_status(int device, int32_t* status);
+
+/* ---------------------------------------------------------------------------------- prefill
+ * Causal GQA prefill, BF16, O + LSE.
+ *
+ * workspace_spec replaces `workspace_spec(q,k,v,num_splits,mapping,causal) -> int[3]`
+ * (tilecadence/cuda/prefill/binding.cpp:12, prefill.cu:106-120): spec = {1, 0, 0}.
+ * num_splits must be 0, mapping 0 or 1, causal non-zero, batch 1 or 4, 128 <= tokens <= 32768
+ * (prefill.cu:69-74,109-114). q_heads is 32 in the reference; a multiple of 8 up to 32 is accepted
+ * so that a rank can hold a KV-head-group shard.
+ */
+int tc_prefill_workspace_spec(int device, int64_t batch, int64_t tokens, int64_t q_heads, int64_t num_splits,
+                              int64_t mapping, int causal, int64_t spec[3]);
+
+/* Replaces `forward_out(q,k,v,out!,lse!,workspace_o!,workspace_lse!,num_splits,mapping,scale,causal)`
+ * (tilecadence/cuda/prefill/binding.cpp:11, prefill.cu:122-152, common.cuh:36-78).
+ * q [B,T,Hq,128], k/v [B,T,Hq/4,128] with element strides {batch,row,head} (multiples of 8, last
+ * dimension contiguous, 16-byte aligned bases); out contiguous like q; lse contiguous [B,Hq,T].
+ * workspace_*_elems must be 0 (single split). mapping 1 stages the per-row LSE of both heads in the
+ * released terminal K stage at the planner's offsets; mapping 0 uses a dedicated staging area. Both
+ * give bit-identical results. dtype_fp16 = 0 selects BF16 (the reference's only prefill type).
+ */
+int tc_prefill_forward_out(int device, void* stream, const void* q, const int64_t q_strides[3], const void* k,
+                           const int64_t k_strides[3], const void* v, const int64_t v_strides[3], void* out,
+                           float* lse, int64_t workspace_o_elems, int64_t workspace_lse_elems, int64_t batch,
+                           int64_t tokens, int64_t q_heads, int64_t num_splits, int64_t mapping, double scale,
+                           int causal);
+
+/* Replaces `resources(q,k,v,num_splits,mapping,causal) -> int[]` (prefill.cu:154-167): 12 header
+ * values, 8 kernel attributes (threads, dynamic smem, static smem, registers/thread, local
+ * bytes/thread, binary version, PTX version, active CTAs/SM), 8 zeros, 18 layout values. */
+int tc_prefill_resources(int device, const int64_t q_strides[3], const int64_t k_strides[3],
+                         const int64_t v_strides[3], int64_t batch, int64_t tokens, int64_t q_heads,
+                         int64_t num_splits, int64_t mapping, int causal, int64_t* values, int64_t capacity,
+                         int64_t* count);
+
+/* ---------------------------------------------------------------------------------- decode
+ * Split-KV decode for one new token per sequence with the KV-cache append fused in.
+ *
+ * Replaces `workspace_spec(q,kcache,old_lengths,num_splits,mapping,append) -> int[3]`
+ * (tilecadence/cuda/decode/binding.cpp:21, decode.cu:76-83): spec = {splits,
+ * splits*B*Hq*128, splits*B*Hq} fp32 elements (zeros when splits == 1). num_splits 0 picks the
+ * split count from the SM count; a positive value (<= 128) is used as given.
+ */
+int tc_decode_workspace_spec(int device, int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits,
+                             int64_t mapping, int append, int64_t spec[3]);
+
+/* Replaces `forward_out(q,kcache!,vcache!,knew,vnew,old_lengths,out!,lse!,workspace_o!,
+ * workspace_lse!,num_splits,mapping,append)` (tilecadence/cuda/decode/binding.cpp:17-20,
+ * decode.cu:158-193). q/out [B,1,Hq,128] BF16 contiguous, caches [B,capacity,Hkv,128] contiguous,
+ * knew/vnew [B,1,Hkv,128], old_lengths int32[B] on the device with 0 <= old_lengths[b] <= capacity-1
+ * when append is set; lse fp32 [B,Hq,1]. With append, row old_lengths[b] of both caches receives the
+ * new K/V row (bit copy) and keys [0, old_lengths[b]] are attended; without, keys [0, old_lengths[b]).
+ * Softmax scale is 128^-0.5 (decode.cu:106). The split partials are merged inside the same launch
+ * by the last CTA to finish each (batch, KV head). All ten buffers must be pairwise disjoint
+ * (decode.cu:176-177). Calls that share a device must not overlap on the GPU (they share tickets).
+ */
+int tc_decode_forward_out(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                          const void* vnew, const int32_t* old_lengths, void* out, float* lse,
+                          float* workspace_o, int64_t workspace_o_elems, float* workspace_lse,
+                          int64_t workspace_lse_elems, int64_t batch, int64_t capacity, int64_t kv_heads,
+                          int64_t num_splits, int64_t mapping, int append);
+
+/* KV-sequence-sharded variant for multi-GPU decode; no counterpart in the reference (it has no
+ * distributed path). The caches hold global rows [kv_shard_start, kv_shard_start + capacity) of each
+ * sequence; old_lengths stay global. The shard that owns row old_lengths[b] performs the append.
+ * Outputs are this shard's normalised partial O (fp32 [B,Hq,128]) and partial LSE (fp32 [B,Hq],
+ * -inf where the shard holds no visible key), ready for an all-gather + tc_combine_partials. */
+int tc_decode_partial_out(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                          const void* vnew, const int32_t* old_lengths, float* partial_o, float* partial_lse,
+                          float* workspace_o, int64_t workspace_o_elems, float* workspace_lse,
+                          int64_t workspace_lse_elems, int64_t batch, int64_t capacity, int64_t kv_heads,
+                          int64_t num_splits, int64_t mapping, int append, int64_t kv_shard_start);
+
+/* LSE-weighted merge of `parts` partial results: the arithmetic of the split combine the reference
+ * launches after its decode kernel (decode.cu:131-140): LSE = ln sum_s exp(LSE_s),
+ * O = sum_s exp(LSE_s - LSE) O_s. partial_o fp32 [parts, rows, 128], partial_lse fp32
+ * [parts, rows]; out BF16 [rows,128], lse fp32 [rows]. Rows with no contribution give O = 0,
+ * LSE = +inf. */
+int tc_combine_partials(int device, void* stream, const float* partial_o, const float* partial_lse, int64_t parts,
+                        int64_t rows, void* out, float* lse);
+
+/* Replaces `resources(q,kcache,old_lengths,num_splits,mapping,append) -> int[]`
+ * (decode.cu:203-229): 12 header values, 8 attributes of the split kernel, 8 of the standalone
+ * combine kernel, 6 tail values. */
+int tc_decode_resources(int device, int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits,
+                        int64_t mapping, int append, int64_t* values, int64_t capacity_values, int64_t* count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TILECADENCE_B200_H */

@@ -1,0 +1,140 @@
+"""CPU oracle for the attention hot path. TEST INFRASTRUCTURE ONLY.
+
+Nothing in the product path may import this module; only ``tests/``, ``__graft_entry__.smoke()``
+and the CPU-baseline legs of ``bench.py`` use it, as the checker or as the timed CPU arm.
+
+It restates, in fp32 torch on the host, the only CPU-capable attention the reference ships:
+``tilecadence/bench_exchange.py:54-60`` (``_reference``): transpose to [B,H,S,D], fp32,
+``scores = q @ k^T * scale``, causal ``masked_fill(col > row, -inf)``, ``softmax @ v`` and
+``logsumexp``. On top of that come the conventions the reference's CUDA path adds:
+
+* GQA: query head ``h`` reads KV head ``h // 4`` (``long_prefill_rowblock.cuh:219,225``; decode row
+  mapping ``cuda/decode/decode.cu:97-105``);
+* decode visibility: keys ``[0, old_len + 1)`` after the append, ``[0, old_len)`` without, no causal
+  mask (``cuda/prefill/common.cuh:49``, ``ab_fused_splitkv.cuh:36,231``), scale 128^-0.5
+  (``decode.cu:106``); the append is a bit copy of the new row into row ``old_len``
+  (``ab_fused_splitkv.cuh:189-212``);
+* LSE is the natural-log ``m*scale + ln(sum)`` (``cuda/exchange/backend.cuh:417``); a row with no
+  visible key gives O = 0 and LSE = +inf in a final result, -inf in a split partial
+  (``ab_fused_splitkv.cuh:82,322``);
+* split merge: ``LSE = ln sum_s exp(LSE_s)``, ``O = sum_s exp(LSE_s - LSE) O_s`` (the combine kernel
+  launched at ``decode.cu:131-140``).
+
+Pinned against outputs of the reference's own ``_reference`` (imported from the reference tree when
+the fixtures were generated): see ``tests/golden/make_golden.py`` and ``tests/test_oracle_golden.py``.
+The reference stores no golden vectors of its own for this path.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+GROUP = 4  # query heads per KV head
+DIM = 128
+DEFAULT_SCALE = DIM ** -0.5
+
+
+def seeded_normal(seed, *shapes, dtype=torch.bfloat16):
+    """N(0,1) tensors drawn in order from one CPU generator and cast to ``dtype``."""
+    generator = torch.Generator().manual_seed(seed)
+    return [torch.randn(shape, generator=generator, dtype=torch.float32).to(dtype) for shape in shapes]
+
+
+def attention(q, k, v, causal, scale=DEFAULT_SCALE, row_block=1024):
+    """O [B,Sq,Hq,D] fp32 and LSE [B,Hq,Sq] fp32 for BSHD inputs; KV heads are shared by groups.
+
+    ``bench_exchange.py:54-60`` evaluated per KV head and per block of query rows so that the
+    score matrix stays small at long sequence lengths. Causal alignment is top-left with
+    ``Sq == Sk`` (the prefill contract).
+    """
+    batch, sq, hq, dim = q.shape
+    sk, hkv = k.shape[1], k.shape[2]
+    assert hq % hkv == 0 and v.shape == k.shape and (not causal or sq == sk)
+    group = hq // hkv
+    out = torch.empty((batch, sq, hq, dim), dtype=torch.float32)
+    lse = torch.empty((batch, hq, sq), dtype=torch.float32)
+    for b in range(batch):
+        for g in range(hkv):
+            kh = k[b, :, g].float()  # [Sk, D]
+            vh = v[b, :, g].float()
+            qh = q[b, :, g * group:(g + 1) * group].float().permute(1, 0, 2)  # [group, Sq, D]
+            for r0 in range(0, sq, row_block):
+                r1 = min(sq, r0 + row_block)
+                visible = r1 if causal else sk
+                scores = (qh[:, r0:r1] @ kh[:visible].T) * scale  # [group, rows, visible]
+                if causal:
+                    rows = torch.arange(r0, r1)[:, None]
+                    cols = torch.arange(visible)[None, :]
+                    scores.masked_fill_(cols > rows, float("-inf"))
+                lse[b, g * group:(g + 1) * group, r0:r1] = scores.logsumexp(dim=-1)
+                out[b, r0:r1, g * group:(g + 1) * group] = (scores.softmax(dim=-1) @ vh[:visible]).permute(1, 0, 2)
+    return out, lse
+
+
+def decode_step(q, kcache, vcache, knew, vnew, old_lengths, append=True, scale=DEFAULT_SCALE,
+                shard_start=0, partial=False):
+    """One decode step on host tensors; returns (O, LSE, kcache_after, vcache_after).
+
+    q [B,1,Hq,D]; caches [B,C,Hkv,D] holding global rows [shard_start, shard_start + C);
+    knew/vnew [B,1,Hkv,D]; old_lengths int [B] (global). O is fp32 [B,1,Hq,D], LSE fp32 [B,Hq,1].
+    With ``partial`` an empty row gets LSE = -inf (a split partial) instead of +inf.
+    """
+    batch, _, hq, dim = q.shape
+    capacity, hkv = kcache.shape[1], kcache.shape[2]
+    group = hq // hkv
+    kcache, vcache = kcache.clone(), vcache.clone()
+    out = torch.zeros((batch, 1, hq, dim), dtype=torch.float32)
+    lse = torch.empty((batch, hq, 1), dtype=torch.float32)
+    for b in range(batch):
+        old = int(old_lengths[b])
+        row = old - shard_start
+        if append and 0 <= row < capacity:
+            kcache[b, row] = knew[b, 0]
+            vcache[b, row] = vnew[b, 0]
+        visible = min(max(old + (1 if append else 0) - shard_start, 0), capacity)
+        if visible == 0:
+            lse[b] = float("-inf") if partial else float("inf")
+            continue
+        for g in range(hkv):
+            qh = q[b, 0, g * group:(g + 1) * group].float()  # [group, D]
+            scores = (qh @ kcache[b, :visible, g].float().T) * scale
+            lse[b, g * group:(g + 1) * group, 0] = scores.logsumexp(dim=-1)
+            out[b, 0, g * group:(g + 1) * group] = scores.softmax(dim=-1) @ vcache[b, :visible, g].float()
+    return out, lse, kcache, vcache
+
+
+def combine(partial_o, partial_lse):
+    """Merge ``parts`` partial results: partial_o [parts, rows, D] fp32, partial_lse [parts, rows].
+
+    Returns O [rows, D] fp32 and LSE [rows] (+inf where no part contributed).
+    """
+    lse_max = partial_lse.max(dim=0).values
+    safe_max = torch.where(torch.isinf(lse_max), torch.zeros_like(lse_max), lse_max)
+    weights = torch.exp(partial_lse - safe_max[None])
+    weights = torch.where(torch.isinf(partial_lse) & (partial_lse < 0), torch.zeros_like(weights), weights)
+    total = weights.sum(dim=0)
+    safe_o = torch.where(weights[..., None] > 0, partial_o, torch.zeros_like(partial_o))
+    merged = (weights[..., None] * safe_o).sum(dim=0) / torch.where(total > 0, total, torch.ones_like(total))[..., None]
+    lse = torch.where(total > 0, safe_max + torch.log(total), torch.full_like(total, float("inf")))
+    return merged, lse
+
+
+def check_outputs(actual_o, actual_lse, expected_o, expected_lse, dtype=torch.bfloat16):
+    """The acceptance bar: max-abs O error <= 2e-2 (BF16) / 1e-2 (FP16), LSE <= 1e-3 relative.
+
+    Returns the two measured errors; raises AssertionError when either bound is exceeded.
+    """
+    o_tolerance = 2e-2 if dtype == torch.bfloat16 else 1e-2
+    o_error = (actual_o.float().cpu() - expected_o.float()).abs().max().item()
+    finite = torch.isfinite(expected_lse)
+    got, want = actual_lse.float().cpu(), expected_lse.float()
+    assert torch.equal(torch.isfinite(got), finite), "LSE finiteness pattern differs"
+    assert torch.equal(got[~finite], want[~finite]), "non-finite LSE values differ"
+    if finite.any():
+        lse_error = ((got[finite] - want[finite]).abs() / want[finite].abs().clamp_min(1.0)).max().item()
+    else:
+        lse_error = 0.0
+    assert math.isfinite(o_error) and o_error <= o_tolerance, f"O max-abs error {o_error} > {o_tolerance}"
+    assert lse_error <= 1e-3, f"LSE relative error {lse_error} > 1e-3"
+    return o_error, lse_error

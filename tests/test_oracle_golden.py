@@ -1,0 +1,93 @@
+"""Pin the CPU oracle against vectors produced by the reference's own CPU attention.
+
+The fixtures come from ``tilecadence/bench_exchange.py:54-60`` (``_reference``) imported from the
+reference tree by ``tests/golden/make_golden.py``.
+"""
+import importlib.util
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention as oracle
+
+GOLDEN = Path(__file__).parent / "golden"
+
+
+@pytest.fixture(scope="module")
+def golden():
+    spec = importlib.util.spec_from_file_location("make_golden", GOLDEN / "make_golden.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module, np.load(GOLDEN / "attention_golden.npz")
+
+
+def compare(module, data, case, inputs, out, lse):
+    assert bytes(module.digest(*inputs)) == bytes(data[f"{case}_inputs_sha256"]), "seeded inputs drifted"
+    stride = module.STRIDES[case]
+    np.testing.assert_allclose(out[:, ::stride].numpy(), data[f"{case}_o_rows"], rtol=1e-5, atol=2e-6)
+    np.testing.assert_allclose(lse.numpy(), data[f"{case}_lse"], rtol=1e-5, atol=2e-6)
+    checksum = np.array([out.double().sum().item(), out.double().abs().sum().item()])
+    np.testing.assert_allclose(checksum, data[f"{case}_o_checksum"], rtol=1e-6)
+
+
+def test_two_tile_noncausal_fp16(golden):
+    module, data = golden
+    q, k, v = module.golden_inputs("two_tile")
+    out, lse = oracle.attention(q, k, v, causal=False)
+    compare(module, data, "two_tile", (q, k, v), out, lse)
+
+
+def test_causal_gqa_prefill_bf16(golden):
+    module, data = golden
+    q, k, v = module.golden_inputs("prefill")
+    for row_block in (1024, 50):
+        out, lse = oracle.attention(q, k, v, causal=True, row_block=row_block)
+        compare(module, data, "prefill", (q, k, v), out, lse)
+
+
+def test_decode_with_append(golden):
+    module, data = golden
+    kcache, vcache, q, knew, vnew, old = module.golden_inputs("decode")
+    out, lse, kafter, vafter = oracle.decode_step(q, kcache, vcache, knew, vnew, old, append=True)
+    compare(module, data, "decode", (kcache, vcache, q, knew, vnew), out, lse.transpose(1, 2).reshape(2, 8, 1))
+    for b, length in enumerate(old.tolist()):
+        assert torch.equal(kafter[b, length].view(torch.int16), knew[b, 0].view(torch.int16))
+        assert torch.equal(vafter[b, length].view(torch.int16), vnew[b, 0].view(torch.int16))
+        keep = torch.ones(200, dtype=torch.bool)
+        keep[length] = False
+        assert torch.equal(kafter[b, keep].view(torch.int16), kcache[b, keep].view(torch.int16))
+
+
+def test_sharded_partials_merge_to_the_unsharded_result():
+    """Split anywhere along the KV sequence, merge with the LSE combine: same O and LSE."""
+    kcache, vcache, q, knew, vnew = oracle.seeded_normal(11, (2, 96, 2, 128), (2, 96, 2, 128), (2, 1, 8, 128),
+                                                         (2, 1, 2, 128), (2, 1, 2, 128))
+    old = torch.tensor([70, 3], dtype=torch.int32)
+    want_o, want_lse, want_k, _ = oracle.decode_step(q, kcache, vcache, knew, vnew, old)
+    parts_o, parts_lse, rows = [], [], []
+    for start in (0, 32, 64):
+        o, lse, kshard, _ = oracle.decode_step(q, kcache[:, start:start + 32], vcache[:, start:start + 32], knew, vnew,
+                                               old, shard_start=start, partial=True)
+        parts_o.append(o.reshape(16, 128))
+        parts_lse.append(lse.reshape(16))
+        rows.append(kshard)
+    assert torch.equal(torch.cat(rows, dim=1).view(torch.int16), want_k.view(torch.int16))
+    merged_o, merged_lse = oracle.combine(torch.stack(parts_o), torch.stack(parts_lse))
+    torch.testing.assert_close(merged_o, want_o.reshape(16, 128), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(merged_lse, want_lse.reshape(16), rtol=1e-5, atol=1e-6)
+
+
+def test_combine_handles_empty_parts():
+    o = torch.randn(3, 4, 128)
+    lse = torch.tensor([[0.5, float("-inf"), float("-inf"), 1.0],
+                        [float("-inf"), float("-inf"), 2.0, 1.0],
+                        [float("-inf"), float("-inf"), float("-inf"), 1.0]])
+    o[1, 1] = float("nan")  # an unused part may hold anything
+    merged, merged_lse = oracle.combine(o, lse)
+    assert torch.equal(merged[0], o[0, 0]) and merged_lse[0] == 0.5
+    assert torch.equal(merged[1], torch.zeros(128)) and merged_lse[1] == float("inf")
+    assert torch.equal(merged[2], o[1, 2])
+    torch.testing.assert_close(merged[3], o[:, 3].mean(dim=0))
+    torch.testing.assert_close(merged_lse[3], torch.tensor(1.0 + np.log(3.0), dtype=torch.float32))

@@ -1,0 +1,13 @@
+// Compile-time schedule of the split-KV decode kernel. The two *_OFFSET_BYTES values are the
+// planner's answer for the "decode" handoff and are rewritten by tilecadence_b200.operator.emit;
+// they are byte offsets inside the released terminal V stage (stage 0 of the K/V ring, V first).
+#pragma once
+#define V10_FAMILY_CODE 7901
+#define AB_DECODE_WARPS 4
+#define AB_DECODE_BLOCK_N 64
+#define AB_DECODE_STAGES 3
+#define AB_DECODE_STAGE_BYTES 32768
+#define AB_DECODE_TERMINAL_V_BYTES 16384
+#define AB_DECODE_CTAS_PER_SM 2
+#define AB_DECODE_O_OFFSET_BYTES 0
+#define AB_DECODE_LSE_OFFSET_BYTES 2048

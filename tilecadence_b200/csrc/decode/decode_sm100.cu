@@ -1,0 +1,657 @@
+// Split-KV decode for one query token per sequence (GQA, four query heads per KV head, D = 128)
+// with the KV-cache append and the LSE-weighted split reduction fused into one launch.
+//
+// Path replaced: tilecadence/cuda/decode/decode.cu:158-193 (host checks and dispatch),
+// ab_fused_splitkv.cuh:6-471 (split kernel, fused append :189-212, compact epilogue :327-397) and
+// the separate combine launch (decode.cu:131-140).
+//
+// The kernel is HBM-bound: every visible K and V row is read exactly once, 256 bytes per row per
+// KV head. One CTA = (batch, KV head, split). A producer warp streams 64-key K/V tiles through a
+// ring of shared-memory stages with TMA (128-byte swizzle) and mbarriers; four consumer warps each
+// own 16 keys of a tile and run QK^T / PV on warp-level bf16 MMAs with an online softmax, so
+// arithmetic never limits the stream. Split ranges follow the device-side lengths. The per-warp
+// partials are merged through the released terminal stage: the four output rows and their LSE
+// are staged at the planner's offsets inside the terminal V region, published with one barrier and
+// exported with one 16-byte vector per thread. The last CTA to finish a (batch, KV head) merges
+// the split partials, so no second launch is needed.
+#include "config.cuh"
+#include "tc_host.cuh"
+#include "tc_ptx.cuh"
+
+#include <cmath>
+
+namespace {
+
+constexpr int kTileN = AB_DECODE_BLOCK_N;
+constexpr int kStages = AB_DECODE_STAGES;
+constexpr int kStageBytes = AB_DECODE_STAGE_BYTES;
+constexpr int kHalfBytes = kTileN * 128;  // one 64-element half of the head dimension, all tile rows
+constexpr int kVBytes = 2 * kHalfBytes;
+constexpr int kConsumerWarps = AB_DECODE_WARPS;
+constexpr int kConsumerThreads = 32 * kConsumerWarps;
+constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kGroup = 4;  // query heads per KV head
+constexpr int kDim = 128;
+constexpr int kMaxSplits = 128;
+constexpr int kStagingBytes = 2304;  // dedicated O/LSE staging when the handoff is disabled
+constexpr int kBarrierBytes = 256;
+
+static_assert(kStageBytes == 2 * kVBytes, "a stage holds one V tile followed by one K tile");
+static_assert(kTileN == 16 * kConsumerWarps, "each consumer warp owns 16 keys of a tile");
+static_assert(AB_DECODE_TERMINAL_V_BYTES == kVBytes, "planner donor size must match the V tile");
+static_assert(AB_DECODE_O_OFFSET_BYTES % 16 == 0 && AB_DECODE_LSE_OFFSET_BYTES % 16 == 0, "vector export");
+static_assert(AB_DECODE_O_OFFSET_BYTES + 2048 <= kVBytes && AB_DECODE_LSE_OFFSET_BYTES + 16 <= kVBytes,
+              "handoff regions must lie inside the terminal V stage");
+static_assert(AB_DECODE_O_OFFSET_BYTES + 2048 <= AB_DECODE_LSE_OFFSET_BYTES ||
+                  AB_DECODE_LSE_OFFSET_BYTES + 16 <= AB_DECODE_O_OFFSET_BYTES,
+              "handoff regions must not overlap");
+
+constexpr int shared_bytes(bool handoff) {
+    return 1024 + kStages * kStageBytes + kBarrierBytes + (handoff ? 0 : kStagingBytes);
+}
+
+struct DecodeParams {
+    const __nv_bfloat16* q;
+    __nv_bfloat16* kcache;
+    __nv_bfloat16* vcache;
+    const __nv_bfloat16* knew;
+    const __nv_bfloat16* vnew;
+    const int32_t* old_lengths;
+    __nv_bfloat16* out;  // final O, bf16 [B,1,Hq,128] (partial == 0)
+    float* lse;          // final LSE [B,Hq] or partial LSE
+    float* partial_o;    // fp32 [B,Hq,128] (partial == 1)
+    float* ws_o;
+    float* ws_lse;
+    int32_t* tickets;
+    int32_t* status;
+    int batch, capacity, kv_heads, splits, append, partial;
+    int64_t shard_start;
+    float scale, scale_log2;
+};
+
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+
+__device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk16) {
+    // Byte offset of 16-byte chunk `chunk16` (0..15 across the 128-element row) of tile row `row`
+    // inside a K or V tile: two 64-element halves, each row 128 bytes, 128-byte TMA swizzle.
+    return (chunk16 >> 3) * kHalfBytes + row * 128 + (((chunk16 & 7) ^ (row & 7)) << 4);
+}
+
+// Merge `count` normalised partials (natural-log LSE) for one row / four columns.
+struct Merged {
+    float4 o;
+    float lse;  // -inf when nothing contributed
+};
+
+template <bool kHandoff>
+__global__ void __launch_bounds__(kThreads, AB_DECODE_CTAS_PER_SM)
+decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                      const DecodeParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+    uint64_t* empty = full + kStages;
+    int* flag = reinterpret_cast<int*>(empty + kStages);
+    uint8_t* staging = kHandoff ? smem : smem + kStages * kStageBytes + kBarrierBytes;
+    float* stage_o = reinterpret_cast<float*>(staging + (kHandoff ? AB_DECODE_O_OFFSET_BYTES : 0));
+    float* stage_lse = reinterpret_cast<float*>(staging + (kHandoff ? AB_DECODE_LSE_OFFSET_BYTES : 2048));
+
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q_heads = p.kv_heads * kGroup;
+
+    // Device-side lengths: no host read. Values outside the contract are clamped so that no
+    // address leaves the cache.
+    int64_t old_len = p.old_lengths[b];
+    old_len = old_len < 0 ? 0 : old_len;
+    const int64_t visible_global = old_len + (p.append ? 1 : 0);
+    int64_t visible_local = visible_global - p.shard_start;
+    visible_local = visible_local < 0 ? 0 : (visible_local > p.capacity ? p.capacity : visible_local);
+    const int n_valid = int(visible_local);
+    const int64_t append_local = old_len - p.shard_start;
+    const bool do_append = p.append && append_local >= 0 && append_local < p.capacity;
+    const int append_row = do_append ? int(append_local) : -1;
+
+    const int tiles = (n_valid + kTileN - 1) / kTileN;
+    const int tile_begin = int((int64_t(split) * tiles) / p.splits);
+    const int tile_end = int((int64_t(split + 1) * tiles) / p.splits);
+    const int n_tiles = tile_end - tile_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], kConsumerWarps);
+        }
+        tc::mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------------ producer warp
+        if (lane == 0 && n_tiles > 0) {
+            tc::tma_prefetch_desc(&kmap);
+            tc::tma_prefetch_desc(&vmap);
+            const uint64_t policy = tc::policy_evict_first();
+            for (int it = 0; it < n_tiles; ++it) {
+                const int stage = (n_tiles - 1 - it) % kStages;  // the last tile always lands in stage 0
+                const uint32_t generation = uint32_t(it / kStages);
+                if (!tc::mbar_wait(&empty[stage], (generation & 1) ^ 1)) {
+                    atomicCAS(p.status, 0, 1);
+                    break;
+                }
+                uint8_t* base = smem + stage * kStageBytes;
+                const int row0 = (tile_begin + it) * kTileN;
+                tc::mbar_arrive_expect_tx(&full[stage], kStageBytes);
+                tc::tma_load_4d(base, &vmap, &full[stage], 0, kvh, row0, b, policy);
+                tc::tma_load_4d(base + kHalfBytes, &vmap, &full[stage], 64, kvh, row0, b, policy);
+                tc::tma_load_4d(base + kVBytes, &kmap, &full[stage], 0, kvh, row0, b, policy);
+                tc::tma_load_4d(base + kVBytes + kHalfBytes, &kmap, &full[stage], 64, kvh, row0, b, policy);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- consumer warps
+    const int qrow = lane >> 2;       // query head within the group; rows >= 4 are padding
+    const int quad = lane & 3;
+    const bool row_ok = qrow < kGroup;
+    uint32_t qa[8][2];
+    {
+        const uint32_t* qptr = reinterpret_cast<const uint32_t*>(
+            p.q + (int64_t(b) * q_heads + kvh * kGroup + (row_ok ? qrow : 0)) * kDim);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            qa[ks][0] = row_ok ? __ldg(qptr + ks * 8 + quad) : 0u;
+            qa[ks][1] = row_ok ? __ldg(qptr + ks * 8 + 4 + quad) : 0u;
+        }
+    }
+    float o[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float row_max = -INFINITY, row_sum = 0.f;
+    bool failed = false;
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int stage = (n_tiles - 1 - it) % kStages;
+        const uint32_t generation = uint32_t(it / kStages);
+        if (!tc::mbar_wait(&full[stage], generation & 1)) {
+            failed = true;
+            break;
+        }
+        uint8_t* vbase = smem + stage * kStageBytes;
+        uint8_t* kbase = vbase + kVBytes;
+        const int tile_row0 = (tile_begin + it) * kTileN;
+        const int warp_row0 = tile_row0 + warp * 16;  // first cache row owned by this warp
+        const int valid = n_valid - warp_row0;         // >= 16: all of this warp's keys are visible
+
+        if (append_row >= warp_row0 && append_row < warp_row0 + 16) {
+            // Fused append: the new row goes to both caches and patches this tile in shared memory,
+            // so the value the TMA copy fetched for that row never matters.
+            const uint32_t r = uint32_t(append_row - tile_row0);
+            const int chunk = lane & 15;
+            const bool is_v = lane >= 16;
+            const uint4 value = __ldg(reinterpret_cast<const uint4*>(
+                (is_v ? p.vnew : p.knew) + (int64_t(b) * p.kv_heads + kvh) * kDim) + chunk);
+            *reinterpret_cast<uint4*>((is_v ? vbase : kbase) + swizzled(r, chunk)) = value;
+            __nv_bfloat16* cache = is_v ? p.vcache : p.kcache;
+            reinterpret_cast<uint4*>(cache + ((int64_t(b) * p.capacity + append_row) * p.kv_heads + kvh) * kDim)[chunk] =
+                value;
+            tc::fence_proxy_async_smem();
+            __syncwarp();
+        }
+        if (valid < 16) {
+            // Rows past the visible length may hold anything (NaN included): zero V so that
+            // 0 * garbage cannot reach the accumulator. K garbage is masked by index below.
+            const int first = valid < 0 ? 0 : valid;
+            for (int idx = lane; idx < 256; idx += 32) {
+                const int rr = idx >> 4;
+                if (rr >= first)
+                    *reinterpret_cast<uint4*>(vbase + swizzled(uint32_t(warp * 16 + rr), uint32_t(idx & 15))) =
+                        make_uint4(0, 0, 0, 0);
+            }
+            tc::fence_proxy_async_smem();
+            __syncwarp();
+        }
+
+        if (valid > 0) {
+            float s[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+            const uint32_t kaddr = tc::smem_u32(kbase);
+            const uint32_t vaddr = tc::smem_u32(vbase);
+            const int mat = lane >> 3, mrow = lane & 7;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                // matrices: (keys 0-7, d lo) (keys 0-7, d hi) (keys 8-15, d lo) (keys 8-15, d hi)
+                const uint32_t r = uint32_t(warp * 16 + (mat >> 1) * 8 + mrow);
+                const uint32_t chunk = uint32_t(ks * 2 + (mat & 1));
+                uint32_t b00, b01, b10, b11;
+                tc::ldmatrix_x4(kaddr + swizzled(r, chunk), b00, b01, b10, b11);
+                tc::mma_bf16_16816(s[0], qa[ks][0], 0u, qa[ks][1], 0u, b00, b01);
+                tc::mma_bf16_16816(s[1], qa[ks][0], 0u, qa[ks][1], 0u, b10, b11);
+            }
+            if (valid < 16) {
+#pragma unroll
+                for (int n = 0; n < 2; ++n)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e)
+                        if (n * 8 + quad * 2 + e >= valid) s[n][e] = -INFINITY;
+            }
+            float tile_max = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+            tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+            tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+            const float new_max = fmaxf(row_max, tile_max);  // finite: key 0 of this warp is visible
+            const float alpha = tc::fast_exp2((row_max - new_max) * p.scale_log2);
+            const float bias = new_max * p.scale_log2;
+            float pr[2][2];
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) pr[n][e] = tc::fast_exp2(fmaf(s[n][e], p.scale_log2, -bias));
+            row_sum = fmaf(row_sum, alpha, (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]));
+            row_max = new_max;
+#pragma unroll
+            for (int n = 0; n < 16; ++n) {
+                o[n][0] *= alpha;
+                o[n][1] *= alpha;
+            }
+            const uint32_t pa0 = row_ok ? tc::pack_bf16x2(pr[0][0], pr[0][1]) : 0u;
+            const uint32_t pa2 = row_ok ? tc::pack_bf16x2(pr[1][0], pr[1][1]) : 0u;
+#pragma unroll
+            for (int np = 0; np < 8; ++np) {
+                // matrices: (keys 0-7, d n0) (keys 8-15, d n0) (keys 0-7, d n0+1) (keys 8-15, d n0+1)
+                const uint32_t r = uint32_t(warp * 16 + (mat & 1) * 8 + mrow);
+                const uint32_t chunk = uint32_t(np * 2 + (mat >> 1));
+                uint32_t v00, v01, v10, v11;
+                tc::ldmatrix_x4_trans(vaddr + swizzled(r, chunk), v00, v01, v10, v11);
+                tc::mma_bf16_16816(o[2 * np], pa0, 0u, pa2, 0u, v00, v01);
+                tc::mma_bf16_16816(o[2 * np + 1], pa0, 0u, pa2, 0u, v10, v11);
+            }
+        }
+        __syncwarp();
+        if (it + 1 < n_tiles && lane == 0) tc::mbar_arrive(&empty[stage]);
+    }
+    if (failed) atomicCAS(p.status, 0, 2);
+
+    // ---------------------------------------------------------------------- CTA epilogue
+    // Quad-partial row sums become full sums; each warp parks its partial in the K rows it owns in
+    // the terminal stage (nobody else reads those rows), then one barrier releases the whole stage.
+    row_sum += __shfl_xor_sync(0xffffffffu, row_sum, 1);
+    row_sum += __shfl_xor_sync(0xffffffffu, row_sum, 2);
+    uint8_t* terminal_k = smem + kVBytes;
+    float* part_o = reinterpret_cast<float*>(terminal_k + warp * 2048);                 // [4][128]
+    float* part_ml = reinterpret_cast<float*>(terminal_k + kHalfBytes + warp * 2048);   // [4][2]
+    if (row_ok) {
+#pragma unroll
+        for (int n = 0; n < 16; ++n)
+            *reinterpret_cast<float2*>(part_o + qrow * kDim + n * 8 + quad * 2) = make_float2(o[n][0], o[n][1]);
+        if (quad == 0) *reinterpret_cast<float2*>(part_ml + qrow * 2) = make_float2(row_max, row_sum);
+    }
+    consumer_barrier();  // all K/V readers are done: the terminal V region changes owner here
+
+    const int tid = threadIdx.x;
+    const int row = tid >> 5;        // query head within the group
+    const int col4 = tid & 31;       // float4 column
+    {
+        float m_w[kConsumerWarps], l_w[kConsumerWarps];
+        float m_all = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+            const float2 ml = *reinterpret_cast<const float2*>(terminal_k + kHalfBytes + w * 2048 + row * 8);
+            m_w[w] = ml.x;
+            l_w[w] = ml.y;
+            m_all = fmaxf(m_all, ml.x);
+        }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float l_all = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+            const float weight = m_w[w] == -INFINITY ? 0.f : tc::fast_exp2((m_w[w] - m_all) * p.scale_log2);
+            const float4 v = *reinterpret_cast<const float4*>(terminal_k + w * 2048 + row * 512 + col4 * 16);
+            l_all = fmaf(weight, l_w[w], l_all);
+            acc.x = fmaf(weight, v.x, acc.x);
+            acc.y = fmaf(weight, v.y, acc.y);
+            acc.z = fmaf(weight, v.z, acc.z);
+            acc.w = fmaf(weight, v.w, acc.w);
+        }
+        const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+        acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+        *reinterpret_cast<float4*>(stage_o + row * kDim + col4 * 4) = acc;
+        if (col4 == 0) stage_lse[row] = l_all > 0.f ? fmaf(m_all, p.scale, logf(l_all)) : -INFINITY;
+    }
+    consumer_barrier();  // publish the four output rows and their LSE together
+
+    const int64_t head_slot = int64_t(b) * p.kv_heads + kvh;  // index of the (batch, KV head) pair
+    float4 final_o;
+    float final_lse;
+    if (p.splits > 1) {
+        // Vector export of the staged tile: one 16-byte word per thread.
+        const int64_t slot = int64_t(split) * p.batch * p.kv_heads + head_slot;
+        reinterpret_cast<uint4*>(p.ws_o + slot * (kGroup * kDim))[tid] = reinterpret_cast<const uint4*>(stage_o)[tid];
+        if (tid == 0)
+            *reinterpret_cast<uint4*>(p.ws_lse + slot * kGroup) = *reinterpret_cast<const uint4*>(stage_lse);
+        __threadfence();
+        consumer_barrier();
+        if (tid == 0) {
+            const int ticket = atomicAdd(p.tickets + head_slot, 1);
+            *flag = ticket == p.splits - 1;
+        }
+        consumer_barrier();
+        if (!*flag) return;
+        __threadfence();
+        // Last CTA of this (batch, KV head): LSE-weighted merge of every split's partial.
+        const int64_t stride_lse = int64_t(p.batch) * p.kv_heads * kGroup;
+        const float* lse_base = p.ws_lse + head_slot * kGroup + row;
+        const float4* o_base = reinterpret_cast<const float4*>(p.ws_o + head_slot * (kGroup * kDim) + row * kDim) + col4;
+        const int64_t stride_o4 = stride_lse * (kDim / 4);
+        float lse_max = -INFINITY;
+        for (int s = 0; s < p.splits; ++s) lse_max = fmaxf(lse_max, __ldcg(lse_base + s * stride_lse));
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float total = 0.f;
+        if (lse_max != -INFINITY) {
+#pragma unroll 8
+            for (int s = 0; s < p.splits; ++s) {
+                const float part_lse = __ldcg(lse_base + s * stride_lse);
+                const float4 v = __ldcg(o_base + s * stride_o4);
+                const bool used = part_lse != -INFINITY;
+                const float weight = used ? __expf(part_lse - lse_max) : 0.f;
+                total += weight;
+                acc.x += used ? weight * v.x : 0.f;
+                acc.y += used ? weight * v.y : 0.f;
+                acc.z += used ? weight * v.z : 0.f;
+                acc.w += used ? weight * v.w : 0.f;
+            }
+        }
+        const float inv = total > 0.f ? 1.f / total : 0.f;
+        final_o = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        final_lse = total > 0.f ? lse_max + logf(total) : -INFINITY;
+        if (tid == 0) atomicExch(p.tickets + head_slot, 0);
+    } else {
+        final_o = *reinterpret_cast<const float4*>(stage_o + row * kDim + col4 * 4);
+        final_lse = stage_lse[row];
+    }
+
+    const int64_t out_row = int64_t(b) * q_heads + kvh * kGroup + row;
+    if (p.partial) {
+        *reinterpret_cast<float4*>(p.partial_o + out_row * kDim + col4 * 4) = final_o;
+        if (col4 == 0) p.lse[out_row] = final_lse;
+    } else {
+        uint2 packed;
+        packed.x = tc::pack_bf16x2(final_o.x, final_o.y);
+        packed.y = tc::pack_bf16x2(final_o.z, final_o.w);
+        *reinterpret_cast<uint2*>(p.out + out_row * kDim + col4 * 4) = packed;
+        if (col4 == 0) p.lse[out_row] = final_lse == -INFINITY ? INFINITY : final_lse;
+    }
+}
+
+// Standalone merge of `parts` partial results (used after the multi-GPU all-gather).
+__global__ void __launch_bounds__(128) combine_partials_kernel(const float* __restrict__ partial_o,
+                                                               const float* __restrict__ partial_lse, int parts,
+                                                               int64_t rows, __nv_bfloat16* __restrict__ out,
+                                                               float* __restrict__ lse) {
+    const int64_t row = int64_t(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    const int col4 = threadIdx.x & 31;
+    if (row >= rows) return;
+    float lse_max = -INFINITY;
+    for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, partial_lse[s * rows + row]);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float total = 0.f;
+    if (lse_max != -INFINITY) {
+        for (int s = 0; s < parts; ++s) {
+            const float part_lse = partial_lse[s * rows + row];
+            const float4 v = reinterpret_cast<const float4*>(partial_o + (s * rows + row) * kDim)[col4];
+            const bool used = part_lse != -INFINITY;
+            const float weight = used ? __expf(part_lse - lse_max) : 0.f;
+            total += weight;
+            acc.x += used ? weight * v.x : 0.f;
+            acc.y += used ? weight * v.y : 0.f;
+            acc.z += used ? weight * v.z : 0.f;
+            acc.w += used ? weight * v.w : 0.f;
+        }
+    }
+    const float inv = total > 0.f ? 1.f / total : 0.f;
+    uint2 packed;
+    packed.x = tc::pack_bf16x2(acc.x * inv, acc.y * inv);
+    packed.y = tc::pack_bf16x2(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(out + row * kDim + col4 * 4) = packed;
+    if (col4 == 0) lse[row] = total > 0.f ? lse_max + logf(total) : INFINITY;
+}
+
+// ------------------------------------------------------------------------------- host side
+int auto_splits(const tc::DeviceInfo& info, int64_t batch, int64_t capacity, int64_t kv_heads) {
+    // Enough CTAs to fill every SM at the kernel's residency, never more splits than tiles.
+    const int64_t slots = int64_t(info.sms) * AB_DECODE_CTAS_PER_SM;
+    int64_t splits = slots / (batch * kv_heads);
+    const int64_t tiles = (capacity + kTileN - 1) / kTileN;
+    if (splits > tiles) splits = tiles;
+    if (splits > kMaxSplits) splits = kMaxSplits;
+    if (splits < 1) splits = 1;
+    return int(splits);
+}
+
+int check_geometry(int device, int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits,
+                   int64_t mapping, int append, tc::DeviceInfo* info, int* splits) {
+    int status = tc::require_sm100(device, info);
+    if (status != TC_OK) return status;
+    TC_REQUIRE(mapping == 0 || mapping == 1, "Expected mapping 0 (dedicated staging) or 1 (planner handoff)");
+    TC_REQUIRE(batch > 0 && batch <= 65535, "Q must be [B,1,Hq,128] with 1 <= B <= 65535");
+    TC_REQUIRE(kv_heads >= 1 && kv_heads <= 8, "caches must be [B,C,Hkv,128] with 1 <= Hkv <= 8");
+    TC_REQUIRE(capacity >= 4, "Full capacity cache must be [B,C>=4,Hkv,128]");
+    TC_REQUIRE(capacity <= (int64_t(1) << 30), "cache capacity overflows the kernel's int geometry");
+    TC_REQUIRE(batch * kv_heads <= tc::kTicketSlots, "B*Hkv exceeds the library's ticket block");
+    TC_REQUIRE(num_splits >= 0 && num_splits <= kMaxSplits, "num_splits must be 0 (auto) or in [1,128]");
+    (void)append;
+    *splits = num_splits > 0 ? int(num_splits) : auto_splits(*info, batch, capacity, kv_heads);
+    return TC_OK;
+}
+
+template <bool kHandoff>
+int launch(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams& p, cudaStream_t stream) {
+    auto kernel = &decode_splitkv_kernel<kHandoff>;
+    constexpr int shared = shared_bytes(kHandoff);
+    static thread_local int configured_device = -1;
+    int device = 0;
+    TC_CUDA(cudaGetDevice(&device));
+    if (configured_device != device) {
+        TC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared));
+        configured_device = device;
+    }
+    const dim3 grid(p.splits, p.kv_heads, p.batch);
+    kernel<<<grid, kThreads, shared, stream>>>(kmap, vmap, p);
+    TC_CUDA(cudaGetLastError());
+    return TC_OK;
+}
+
+struct MapKey {
+    const void* base;
+    int64_t batch, capacity, kv_heads;
+    int device;
+    bool operator==(const MapKey& other) const {
+        return base == other.base && batch == other.batch && capacity == other.capacity &&
+               kv_heads == other.kv_heads && device == other.device;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& key) const {
+        return std::hash<const void*>()(key.base) ^ (std::hash<int64_t>()(key.capacity) * 31) ^
+               (std::hash<int64_t>()(key.batch * 16 + key.kv_heads) * 131) ^ size_t(key.device);
+    }
+};
+
+// Encoding a tensor map costs a few microseconds of host time, comparable to the kernel itself at
+// short lengths, so maps are memoised per (pointer, geometry).
+int cache_map(int device, const void* base, int64_t batch, int64_t capacity, int64_t kv_heads, CUtensorMap* out) {
+    static std::mutex lock;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{base, batch, capacity, kv_heads, device};
+    std::lock_guard<std::mutex> guard(lock);
+    auto found = cache.find(key);
+    if (found == cache.end()) {
+        if (cache.size() > 4096) cache.clear();
+        CUtensorMap map;
+        int status = tc::make_rows_map(&map, base, false, kv_heads, capacity, batch, kDim, kv_heads * kDim,
+                                       capacity * kv_heads * kDim, kTileN, 2);
+        if (status != TC_OK) return status;
+        found = cache.emplace(key, map).first;
+    }
+    *out = found->second;
+    return TC_OK;
+}
+
+int decode_common(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                  const void* vnew, const int32_t* old_lengths, void* out, float* lse, float* partial_o,
+                  float* workspace_o, int64_t workspace_o_elems, float* workspace_lse, int64_t workspace_lse_elems,
+                  int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping, int append,
+                  int partial, int64_t shard_start) {
+    tc::DeviceInfo info;
+    int splits = 1;
+    int status = check_geometry(device, batch, capacity, kv_heads, num_splits, mapping, append, &info, &splits);
+    if (status != TC_OK) return status;
+    TC_REQUIRE(q && kcache && vcache && knew && vnew && old_lengths && lse && (partial ? (void*)partial_o : out),
+               "null tensor pointer");
+    TC_REQUIRE(shard_start >= 0, "kv_shard_start must be non-negative");
+    const int64_t q_heads = kv_heads * kGroup;
+    const int64_t rows = batch * q_heads;
+    const size_t q_bytes = size_t(rows) * kDim * 2, cache_bytes = size_t(batch) * capacity * kv_heads * kDim * 2;
+    const size_t new_bytes = size_t(batch) * kv_heads * kDim * 2;
+    TC_REQUIRE(cache_bytes <= (size_t(1) << 40), "cache allocation is outside the supported range");
+    const int64_t need_o = splits > 1 ? int64_t(splits) * rows * kDim : 0, need_lse = splits > 1 ? int64_t(splits) * rows : 0;
+    TC_REQUIRE(workspace_o_elems >= need_o && workspace_lse_elems >= need_lse,
+               "Preallocated complete split workspace is too small");
+    TC_REQUIRE(!need_o || (workspace_o && workspace_lse), "null split workspace");
+    const void* pointers[10] = {q, kcache, vcache, knew, vnew, old_lengths, partial ? (void*)partial_o : out, lse,
+                                need_o ? workspace_o : nullptr, need_lse ? workspace_lse : nullptr};
+    const size_t sizes[10] = {q_bytes, cache_bytes, cache_bytes, new_bytes, new_bytes, size_t(batch) * 4,
+                              partial ? size_t(rows) * kDim * 4 : q_bytes, size_t(rows) * 4, size_t(need_o) * 4,
+                              size_t(need_lse) * 4};
+    for (int i = 0; i < 10; ++i)
+        for (int j = i + 1; j < 10; ++j)
+            TC_REQUIRE(!pointers[i] || !pointers[j] || !tc::ranges_overlap(pointers[i], sizes[i], pointers[j], sizes[j]),
+                       "All nonempty ABI tensor allocations must be disjoint");
+    for (int i = 0; i < 10; ++i)
+        TC_REQUIRE(!pointers[i] || reinterpret_cast<uintptr_t>(pointers[i]) % 16 == 0 || i == 5 || i == 7,
+                   "16-byte aligned storage required");
+    TC_REQUIRE(reinterpret_cast<uintptr_t>(old_lengths) % 4 == 0 && reinterpret_cast<uintptr_t>(lse) % 4 == 0,
+               "misaligned old_lengths or LSE");
+
+    tc::DeviceGuard guard(device);
+    TC_CUDA(guard.status);
+    tc::DeviceScratch scratch;
+    status = tc::device_scratch(device, &scratch);
+    if (status != TC_OK) return status;
+    CUtensorMap kmap, vmap;
+    status = cache_map(device, kcache, batch, capacity, kv_heads, &kmap);
+    if (status != TC_OK) return status;
+    status = cache_map(device, vcache, batch, capacity, kv_heads, &vmap);
+    if (status != TC_OK) return status;
+
+    DecodeParams p{};
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.kcache = static_cast<__nv_bfloat16*>(kcache);
+    p.vcache = static_cast<__nv_bfloat16*>(vcache);
+    p.knew = static_cast<const __nv_bfloat16*>(knew);
+    p.vnew = static_cast<const __nv_bfloat16*>(vnew);
+    p.old_lengths = old_lengths;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.lse = lse;
+    p.partial_o = partial_o;
+    p.ws_o = workspace_o;
+    p.ws_lse = workspace_lse;
+    p.tickets = scratch.tickets;
+    p.status = scratch.status;
+    p.batch = int(batch);
+    p.capacity = int(capacity);
+    p.kv_heads = int(kv_heads);
+    p.splits = splits;
+    p.append = append ? 1 : 0;
+    p.partial = partial;
+    p.shard_start = shard_start;
+    p.scale = 1.f / std::sqrt(128.f);
+    p.scale_log2 = p.scale * float(M_LOG2E);
+    return mapping == 1 ? launch<true>(kmap, vmap, p, static_cast<cudaStream_t>(stream))
+                        : launch<false>(kmap, vmap, p, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+
+extern "C" {
+
+int tc_decode_workspace_spec(int device, int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits,
+                             int64_t mapping, int append, int64_t spec[3]) {
+    tc::DeviceInfo info;
+    int splits = 1;
+    int status = check_geometry(device, batch, capacity, kv_heads, num_splits, mapping, append, &info, &splits);
+    if (status != TC_OK) return status;
+    TC_REQUIRE(spec, "null spec");
+    const int64_t rows = batch * kv_heads * kGroup;
+    spec[0] = splits;
+    spec[1] = splits > 1 ? splits * rows * kDim : 0;
+    spec[2] = splits > 1 ? splits * rows : 0;
+    return TC_OK;
+}
+
+int tc_decode_forward_out(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                          const void* vnew, const int32_t* old_lengths, void* out, float* lse, float* workspace_o,
+                          int64_t workspace_o_elems, float* workspace_lse, int64_t workspace_lse_elems, int64_t batch,
+                          int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping, int append) {
+    return decode_common(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, nullptr, workspace_o,
+                         workspace_o_elems, workspace_lse, workspace_lse_elems, batch, capacity, kv_heads, num_splits,
+                         mapping, append, 0, 0);
+}
+
+int tc_decode_partial_out(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                          const void* vnew, const int32_t* old_lengths, float* partial_o, float* partial_lse,
+                          float* workspace_o, int64_t workspace_o_elems, float* workspace_lse,
+                          int64_t workspace_lse_elems, int64_t batch, int64_t capacity, int64_t kv_heads,
+                          int64_t num_splits, int64_t mapping, int append, int64_t kv_shard_start) {
+    return decode_common(device, stream, q, kcache, vcache, knew, vnew, old_lengths, nullptr, partial_lse, partial_o,
+                         workspace_o, workspace_o_elems, workspace_lse, workspace_lse_elems, batch, capacity, kv_heads,
+                         num_splits, mapping, append, 1, kv_shard_start);
+}
+
+int tc_combine_partials(int device, void* stream, const float* partial_o, const float* partial_lse, int64_t parts,
+                        int64_t rows, void* out, float* lse) {
+    tc::DeviceInfo info;
+    int status = tc::require_sm100(device, &info);
+    if (status != TC_OK) return status;
+    TC_REQUIRE(partial_o && partial_lse && out && lse, "null tensor pointer");
+    TC_REQUIRE(parts >= 1 && parts <= 1024 && rows >= 1 && rows <= (int64_t(1) << 24), "parts or rows out of range");
+    TC_REQUIRE(reinterpret_cast<uintptr_t>(partial_o) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0,
+               "16-byte aligned partial O and 8-byte aligned O required");
+    tc::DeviceGuard guard(device);
+    TC_CUDA(guard.status);
+    const unsigned blocks = unsigned((rows + 3) / 4);
+    combine_partials_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        partial_o, partial_lse, int(parts), rows, static_cast<__nv_bfloat16*>(out), lse);
+    TC_CUDA(cudaGetLastError());
+    return TC_OK;
+}
+
+int tc_decode_resources(int device, int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits,
+                        int64_t mapping, int append, int64_t* values, int64_t capacity_values, int64_t* count) {
+    tc::DeviceInfo info;
+    int splits = 1;
+    int status = check_geometry(device, batch, capacity, kv_heads, num_splits, mapping, append, &info, &splits);
+    if (status != TC_OK) return status;
+    TC_REQUIRE(append, "Resource reporting requires fused KV append");
+    TC_REQUIRE(values && count && capacity_values >= 34, "resources needs room for 34 values");
+    tc::DeviceGuard guard(device);
+    TC_CUDA(guard.status);
+    const int64_t rows = batch * kv_heads * kGroup;
+    const int64_t header[12] = {splits, kGroup, kv_heads, kGroup, 1, batch * kv_heads * splits,
+                                splits > 1 ? batch * kv_heads : 0, splits > 1 ? splits * rows * kDim : 0,
+                                splits > 1 ? splits * rows : 0, kGroup, kTileN, 1};
+    for (int i = 0; i < 12; ++i) values[i] = header[i];
+    status = mapping == 1 ? tc::kernel_resources(&decode_splitkv_kernel<true>, kThreads, shared_bytes(true), values + 12)
+                          : tc::kernel_resources(&decode_splitkv_kernel<false>, kThreads, shared_bytes(false), values + 12);
+    if (status != TC_OK) return status;
+    status = tc::kernel_resources(&combine_partials_kernel, 128, 0, values + 20);
+    if (status != TC_OK) return status;
+    const int64_t tail[6] = {capacity, capacity - 1, capacity - 1 + (append ? 1 : 0), append ? 1 : 0, mapping == 0,
+                             V10_FAMILY_CODE};
+    for (int i = 0; i < 6; ++i) values[28 + i] = tail[i];
+    *count = 34;
+    return TC_OK;
+}
+
+}  // extern "C"

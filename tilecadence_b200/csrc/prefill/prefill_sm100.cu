@@ -1,0 +1,503 @@
+// Causal GQA prefill (four query heads per KV head, D = 128, BF16) for sm_100a: O and LSE.
+//
+// Path replaced: tilecadence/cuda/prefill/prefill.cu:21-43,122-152 (CTA mapping, host checks,
+// launch), long_prefill_rowblock.cuh:117-605 (the row-block kernel: QK^T, online softmax with a
+// gated rescale :68-115, PV, O staged over the CTA's own Q :513-524, both heads' LSE staged in the
+// released terminal K span :539-587) and common.cuh:36-78 (tensor checks).
+//
+// One CTA owns a 128-row query tile of the two query heads that share a KV head pair slot, so one
+// K/V tile in shared memory feeds both heads. The two dense contractions run on the 5th-generation
+// tensor cores: S_h = Q_h K^T as a shared x shared tcgen05.mma into TMEM, O_h += P_h V as a
+// TMEM x shared tcgen05.mma with P written back over its own S columns as BF16. TMEM holds
+// S0 | S1 | O0 | O1 (4 x 128 fp32 columns = all 512 columns). Roles:
+//   warps 0-3  softmax for head 0 (one query row per thread, TMEM lane = row)
+//   warps 4-7  softmax for head 1
+//   warp  8    TMA producer: Q once, then a 2-stage K ring and a 2-stage V ring (128-byte swizzle)
+//   warp  9    tcgen05.mma issuer (one elected thread) and TMEM owner
+// The issue order QK0 QK1 | PV0 QK0' | PV1 QK1' ... keeps the tensor pipe busy with one head
+// while the other head's softmax runs. Key tiles go from the diagonal down to 0, the ring index is
+// chosen so that the final tile always uses stage 0: that stage is the "terminal K" donor whose
+// bytes receive the two 512-byte LSE arrays in the epilogue.
+#include "config.cuh"
+#include "tc_host.cuh"
+#include "tc_ptx.cuh"
+
+#include <cmath>
+
+namespace {
+
+constexpr int kBlockM = PREFILL_BLOCK_M;
+constexpr int kBlockN = PREFILL_BLOCK_N;
+constexpr int kDim = 128;
+constexpr int kGroup = 4;
+constexpr int kStages = PREFILL_KV_STAGES;
+constexpr int kTileBytes = 128 * kDim * 2;    // one 128-row operand tile
+constexpr int kHalfBytes = kTileBytes / 2;    // 64 of the 128 head-dim elements, all rows
+constexpr int kQOffset = 0;
+constexpr int kKOffset = 2 * kTileBytes;
+constexpr int kVOffset = kKOffset + kStages * kTileBytes;
+constexpr int kBarrierOffset = kVOffset + kStages * kTileBytes;
+constexpr int kBarrierBytes = 256;
+constexpr int kStagingBytes = 1024;           // dedicated LSE staging when the handoff is disabled
+constexpr int kSoftmaxThreads = 128;
+constexpr int kThreads = 2 * kSoftmaxThreads + 64;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr uint32_t kTmemColumns = 512;
+constexpr float kRescaleThreshold = 8.f;      // log2 units: P stays below 2^8
+
+static_assert(kBlockM == 128 && kBlockN == 128 && PREFILL_GROUP_HEADS == 2 && kStages == 2, "fixed tile schedule");
+static_assert(PREFILL_TERMINAL_K_OFFSET_BYTES == kKOffset && PREFILL_TERMINAL_K_BYTES == kTileBytes,
+              "the planner's donor must be K stage 0");
+static_assert(PREFILL_LSE_HEAD0_OFFSET_BYTES % 128 == 0 && PREFILL_LSE_HEAD1_OFFSET_BYTES % 128 == 0, "alignment");
+static_assert(PREFILL_LSE_HEAD0_OFFSET_BYTES >= kKOffset && PREFILL_LSE_HEAD0_OFFSET_BYTES + 512 <= kKOffset + kTileBytes &&
+                  PREFILL_LSE_HEAD1_OFFSET_BYTES >= kKOffset &&
+                  PREFILL_LSE_HEAD1_OFFSET_BYTES + 512 <= kKOffset + kTileBytes,
+              "LSE regions must lie inside the terminal K stage");
+static_assert(PREFILL_LSE_HEAD0_OFFSET_BYTES + 512 <= PREFILL_LSE_HEAD1_OFFSET_BYTES ||
+                  PREFILL_LSE_HEAD1_OFFSET_BYTES + 512 <= PREFILL_LSE_HEAD0_OFFSET_BYTES,
+              "LSE regions must not overlap");
+
+constexpr int shared_bytes(bool handoff) { return 1024 + kBarrierOffset + kBarrierBytes + (handoff ? 0 : kStagingBytes); }
+
+struct Barriers {
+    uint64_t q_full;
+    uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+    uint64_t s_full[2], p_full[2], o_done[2];
+    uint32_t tmem_base;
+    int32_t abort;
+};
+static_assert(sizeof(Barriers) <= kBarrierBytes, "barrier block");
+
+struct PrefillParams {
+    float* lse;
+    int32_t* status;
+    int batch, tokens, q_heads, kv_heads, m_blocks;
+    float scale, scale_log2;
+};
+
+__device__ __forceinline__ void wg_barrier(int head) {
+    asm volatile("bar.sync %0, %1;" ::"r"(head + 1), "n"(kSoftmaxThreads) : "memory");
+}
+
+template <bool kHandoff>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+               const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap,
+               const PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + kBarrierOffset);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // Longest query tiles first; neighbouring CTAs share a KV head so K/V tiles hit in L2.
+    const int per_block = p.batch * p.kv_heads * 2;
+    const int m_block = p.m_blocks - 1 - int(blockIdx.x) / per_block;
+    const int rest = int(blockIdx.x) % per_block;
+    const int pair = rest & 1;
+    const int kvh = (rest >> 1) % p.kv_heads;
+    const int b = rest / (2 * p.kv_heads);
+    const int head0 = kvh * kGroup + pair * 2;
+    const int m0 = m_block * kBlockM;
+    const int n_tiles = m_block + 1;  // key tiles m_block, m_block-1, ..., 0
+
+    if (threadIdx.x == 0) {
+        tc::mbar_init(&bars->q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            tc::mbar_init(&bars->k_full[s], 1);
+            tc::mbar_init(&bars->k_empty[s], 1);
+            tc::mbar_init(&bars->v_full[s], 1);
+            tc::mbar_init(&bars->v_empty[s], 1);
+        }
+        for (int h = 0; h < 2; ++h) {
+            tc::mbar_init(&bars->s_full[h], 1);
+            tc::mbar_init(&bars->p_full[h], kSoftmaxThreads);
+            tc::mbar_init(&bars->o_done[h], 1);
+        }
+        bars->abort = 0;
+        tc::mbar_fence_init();
+    }
+    if (warp == kMmaWarp) {
+        tc::tmem_alloc(&bars->tmem_base, kTmemColumns);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem = bars->tmem_base;
+
+    if (warp == kProducerWarp) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tc::tma_prefetch_desc(&qmap);
+            tc::tma_prefetch_desc(&kmap);
+            tc::tma_prefetch_desc(&vmap);
+            const uint64_t keep = tc::policy_evict_last(), stream = tc::policy_evict_first();
+            tc::mbar_arrive_expect_tx(&bars->q_full, 2 * kTileBytes);
+            for (int h = 0; h < 2; ++h) {
+                uint8_t* dst = smem + kQOffset + h * kTileBytes;
+                tc::tma_load_4d(dst, &qmap, &bars->q_full, 0, head0 + h, m0, b, stream);
+                tc::tma_load_4d(dst + kHalfBytes, &qmap, &bars->q_full, 64, head0 + h, m0, b, stream);
+            }
+            for (int it = 0; it < n_tiles; ++it) {
+                const int stage = (n_tiles - 1 - it) % kStages;
+                const uint32_t parity = (uint32_t(it / kStages) & 1) ^ 1;
+                const int n0 = (m_block - it) * kBlockN;
+                if (!tc::mbar_wait(&bars->k_empty[stage], parity)) { atomicCAS(p.status, 0, 11); break; }
+                uint8_t* kdst = smem + kKOffset + stage * kTileBytes;
+                tc::mbar_arrive_expect_tx(&bars->k_full[stage], kTileBytes);
+                tc::tma_load_4d(kdst, &kmap, &bars->k_full[stage], 0, kvh, n0, b, keep);
+                tc::tma_load_4d(kdst + kHalfBytes, &kmap, &bars->k_full[stage], 64, kvh, n0, b, keep);
+                if (!tc::mbar_wait(&bars->v_empty[stage], parity)) { atomicCAS(p.status, 0, 12); break; }
+                uint8_t* vdst = smem + kVOffset + stage * kTileBytes;
+                tc::mbar_arrive_expect_tx(&bars->v_full[stage], kTileBytes);
+                tc::tma_load_4d(vdst, &vmap, &bars->v_full[stage], 0, kvh, n0, b, keep);
+                tc::tma_load_4d(vdst + kHalfBytes, &vmap, &bars->v_full[stage], 64, kvh, n0, b, keep);
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = tc::umma_idesc(128, 128, 1, 0, 0);
+            constexpr uint32_t idesc_pv = tc::umma_idesc(128, 128, 1, 0, 1);
+            const uint32_t q_addr = tc::smem_u32(smem + kQOffset);
+            const uint32_t k_addr = tc::smem_u32(smem + kKOffset);
+            const uint32_t v_addr = tc::smem_u32(smem + kVOffset);
+            bool ok = true;
+            // S_h = Q_h K^T: both operands K-major, 8 steps of 16 along D (4 per 64-element half).
+            auto issue_qk = [&](int h, int stage) {
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off = uint32_t(ks >> 2) * kHalfBytes + uint32_t(ks & 3) * 32;
+                    tc::umma_ss(tmem + uint32_t(h) * 128,
+                                tc::umma_desc_sw128(q_addr + h * kTileBytes + off, 16, 1024),
+                                tc::umma_desc_sw128(k_addr + stage * kTileBytes + off, 16, 1024), idesc_qk, ks > 0);
+                }
+                tc::umma_commit(&bars->s_full[h]);
+            };
+            // O_h += P_h V: P from TMEM (8 columns per 16 keys), V MN-major (row = key, 128 bytes per
+            // 64 d; the two d halves are 16 KiB apart, 8-key groups 1 KiB apart).
+            auto issue_pv = [&](int h, int stage, bool first) {
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    tc::umma_ts(tmem + 256 + uint32_t(h) * 128, tmem + uint32_t(h) * 128 + uint32_t(ks) * 8,
+                                tc::umma_desc_sw128(v_addr + stage * kTileBytes + ks * 2048, kHalfBytes, 1024),
+                                idesc_pv, !(first && ks == 0));
+                }
+                tc::umma_commit(&bars->o_done[h]);
+            };
+            ok = tc::mbar_wait(&bars->q_full, 0);
+            if (ok) {
+                const int stage = (n_tiles - 1) % kStages;
+                ok = tc::mbar_wait(&bars->k_full[stage], 0);
+                if (ok) {
+                    tc::tc_fence_after_sync();
+                    issue_qk(0, stage);
+                    issue_qk(1, stage);
+                    tc::umma_commit(&bars->k_empty[stage]);
+                }
+            }
+            for (int it = 0; ok && it < n_tiles; ++it) {
+                const int stage = (n_tiles - 1 - it) % kStages;
+                const uint32_t parity = uint32_t(it / kStages) & 1;
+                const bool more = it + 1 < n_tiles;
+                const int next_stage = (n_tiles - 2 - it) % kStages;
+                const uint32_t next_parity = uint32_t((it + 1) / kStages) & 1;
+                if (!(ok = tc::mbar_wait(&bars->v_full[stage], parity))) break;
+                if (more && !(ok = tc::mbar_wait(&bars->k_full[next_stage], next_parity))) break;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (!(ok = tc::mbar_wait(&bars->p_full[h], uint32_t(it) & 1))) break;
+                    tc::tc_fence_after_sync();
+                    issue_pv(h, stage, it == 0);
+                    if (more) issue_qk(h, next_stage);
+                }
+                if (!ok) break;
+                tc::umma_commit(&bars->v_empty[stage]);
+                if (more) tc::umma_commit(&bars->k_empty[next_stage]);
+            }
+            if (!ok) {
+                atomicCAS(p.status, 0, 13);
+                bars->abort = 1;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax warpgroups
+        const int h = warp >> 2;                        // head slot
+        const int row = threadIdx.x & (kSoftmaxThreads - 1);
+        const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
+        const uint32_t s_tmem = tmem + lane_field + uint32_t(h) * 128;
+        const uint32_t o_tmem = tmem + lane_field + 256 + uint32_t(h) * 128;
+        const int head = head0 + h;
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+
+        for (int it = 0; it < n_tiles; ++it) {
+            if (!(ok = tc::mbar_wait(&bars->s_full[h], uint32_t(it) & 1))) break;
+            tc::tc_fence_after_sync();
+            float s[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tc::tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+            tc::tmem_wait_ld();
+            if (it == 0) {
+                // Diagonal tile: key column j is visible to query row i only if j <= i.
+#pragma unroll
+                for (int j = 0; j < 128; ++j) s[j] = j > row ? -INFINITY : s[j];
+            }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 128; j += 4) {
+                mx[0] = fmaxf(mx[0], s[j]);
+                mx[1] = fmaxf(mx[1], s[j + 1]);
+                mx[2] = fmaxf(mx[2], s[j + 2]);
+                mx[3] = fmaxf(mx[3], s[j + 3]);
+            }
+            const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            if (it == 0) {
+                m_used = tile_max;  // finite: column `row` of the diagonal tile is always visible
+            } else {
+                // Gated rescale: O and l are only brought to a new reference maximum when the row
+                // maximum grew by more than 2^kRescaleThreshold, and only if some row of the warp
+                // needs it (the TMEM accesses are warp-collective).
+                const float m_new = fmaxf(m_used, tile_max);
+                const bool grow = (m_new - m_used) * p.scale_log2 > kRescaleThreshold;
+                if (__any_sync(0xffffffffu, grow)) {
+                    if (!(ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1))) break;
+                    tc::tc_fence_after_sync();
+                    const float m_target = grow ? m_new : m_used;
+                    const float alpha = tc::fast_exp2((m_used - m_target) * p.scale_log2);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t acc[32];
+                        tc::tmem_ld32(o_tmem + c * 32, acc);
+                        tc::tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) * alpha);
+                        tc::tmem_st32(o_tmem + c * 32, acc);
+                    }
+                    tc::tmem_wait_st();
+                    l *= alpha;
+                    m_used = m_target;
+                }
+            }
+            const float bias = m_used * p.scale_log2;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t packed[64];
+#pragma unroll
+            for (int j = 0; j < 128; j += 4) {
+                const float p0 = tc::fast_exp2(fmaf(s[j], p.scale_log2, -bias));
+                const float p1 = tc::fast_exp2(fmaf(s[j + 1], p.scale_log2, -bias));
+                const float p2 = tc::fast_exp2(fmaf(s[j + 2], p.scale_log2, -bias));
+                const float p3 = tc::fast_exp2(fmaf(s[j + 3], p.scale_log2, -bias));
+                sum[0] += p0; sum[1] += p1; sum[2] += p2; sum[3] += p3;
+                packed[j / 2] = tc::pack_bf16x2(p0, p1);
+                packed[j / 2 + 1] = tc::pack_bf16x2(p2, p3);
+            }
+            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            // P overwrites the first 64 columns of this head's S block.
+            tc::tmem_st32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&packed[0]));
+            tc::tmem_st32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&packed[32]));
+            tc::tmem_wait_st();
+            tc::tc_fence_before_sync();
+            tc::mbar_arrive(&bars->p_full[h]);
+        }
+
+        // ------------------------------------------------------------------ epilogue
+        if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(n_tiles - 1) & 1);
+        if (!ok) {
+            atomicCAS(p.status, 0, 14 + h);
+            bars->abort = 1;
+        }
+        tc::tc_fence_after_sync();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        // O (bf16) is staged over this head's own Q tile in the TMA store layout; LSE goes to the
+        // planner's region in the released terminal K stage (or to the dedicated area).
+        uint8_t* o_stage = smem + kQOffset + h * kTileBytes;
+        float* lse_stage = reinterpret_cast<float*>(
+            kHandoff ? smem + (h == 0 ? PREFILL_LSE_HEAD0_OFFSET_BYTES : PREFILL_LSE_HEAD1_OFFSET_BYTES)
+                     : smem + kBarrierOffset + kBarrierBytes + h * 512);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint32_t acc[32];
+            tc::tmem_ld32(o_tmem + c * 32, acc);
+            tc::tmem_wait_ld();
+            uint8_t* half = o_stage + (c >> 1) * kHalfBytes + row * 128;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint4 word;
+                word.x = tc::pack_bf16x2(__uint_as_float(acc[i * 8 + 0]) * inv, __uint_as_float(acc[i * 8 + 1]) * inv);
+                word.y = tc::pack_bf16x2(__uint_as_float(acc[i * 8 + 2]) * inv, __uint_as_float(acc[i * 8 + 3]) * inv);
+                word.z = tc::pack_bf16x2(__uint_as_float(acc[i * 8 + 4]) * inv, __uint_as_float(acc[i * 8 + 5]) * inv);
+                word.w = tc::pack_bf16x2(__uint_as_float(acc[i * 8 + 6]) * inv, __uint_as_float(acc[i * 8 + 7]) * inv);
+                const int chunk = (c & 1) * 4 + i;
+                *reinterpret_cast<uint4*>(half + ((chunk ^ (row & 7)) << 4)) = word;
+            }
+        }
+        const float row_lse = l > 0.f ? fmaf(m_used, p.scale, logf(l)) : INFINITY;
+        lse_stage[row] = row_lse;
+        tc::fence_proxy_async_smem();
+        wg_barrier(h);  // one barrier publishes the O tile and the LSE array of this head
+        const int rows_here = min(kBlockM, p.tokens - m0);
+        float* lse_out = p.lse + (int64_t(b) * p.q_heads + head) * p.tokens + m0;
+        const bool bulk_lse = rows_here == kBlockM && (p.tokens & 3) == 0;
+        if (row == 0 && !bars->abort) {
+            tc::tma_store_4d(&omap, o_stage, 0, head, m0, b);
+            tc::tma_store_4d(&omap, o_stage + kHalfBytes, 64, head, m0, b);
+            if (bulk_lse) tc::bulk_store_1d(lse_out, lse_stage, kBlockM * 4);
+            tc::bulk_commit();
+            tc::bulk_wait_all();
+        }
+        if (!bulk_lse && row < rows_here) lse_out[row] = row_lse;
+    }
+
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc::tc_fence_after_sync();
+        tc::tmem_dealloc(tmem, kTmemColumns);
+    }
+}
+
+// ------------------------------------------------------------------------------- host side
+int check_geometry(int device, int64_t batch, int64_t tokens, int64_t q_heads, int64_t num_splits, int64_t mapping,
+                   int causal, tc::DeviceInfo* info) {
+    int status = tc::require_sm100(device, info);
+    if (status != TC_OK) return status;
+    TC_REQUIRE(num_splits == 0 && (mapping == 0 || mapping == 1), "prefill requires num_splits=0 and mapping 0 or 1");
+    TC_REQUIRE(causal, "Full causal no-past prefill requires causal=True");
+    TC_REQUIRE(q_heads >= 4 && q_heads <= 32 && q_heads % 4 == 0, "Q must be [B,T,Hq,128] with Hq a multiple of 4 up to 32");
+    TC_REQUIRE(batch == 1 || batch == 4, "The shared-LSE schedule requires batch 1 or 4");
+    TC_REQUIRE(tokens >= 128 && tokens <= 32768, "The shared-LSE schedule requires 128-32768 tokens");
+    TC_REQUIRE(info->smem_optin >= shared_bytes(false), "device lacks the opt-in shared memory this schedule needs");
+    return TC_OK;
+}
+
+int check_strides(const char* name, const int64_t strides[3], int64_t batch, int64_t tokens, int64_t heads) {
+    TC_REQUIRE(strides, "null strides");
+    const int64_t sizes[3] = {batch, tokens, heads};
+    for (int axis = 0; axis < 3; ++axis) {
+        TC_REQUIRE(strides[axis] >= 0, "%s: negative strides are outside this ABI", name);
+        if (sizes[axis] > 1)
+            TC_REQUIRE(strides[axis] % 8 == 0 && strides[axis] >= 128,
+                       "%s: strides must be multiples of 8 elements with a contiguous last dimension", name);
+    }
+    return TC_OK;
+}
+
+size_t span_bytes(const int64_t strides[3], int64_t batch, int64_t tokens, int64_t heads) {
+    return size_t((batch - 1) * strides[0] + (tokens - 1) * strides[1] + (heads - 1) * strides[2] + kDim) * 2;
+}
+
+template <bool kHandoff>
+int launch(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& omap,
+           const PrefillParams& p, cudaStream_t stream) {
+    auto kernel = &prefill_kernel<kHandoff>;
+    constexpr int shared = shared_bytes(kHandoff);
+    static thread_local int configured_device = -1;
+    int device = 0;
+    TC_CUDA(cudaGetDevice(&device));
+    if (configured_device != device) {
+        TC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared));
+        configured_device = device;
+    }
+    const unsigned grid = unsigned(p.m_blocks) * p.batch * p.kv_heads * 2;
+    kernel<<<grid, kThreads, shared, stream>>>(qmap, kmap, vmap, omap, p);
+    TC_CUDA(cudaGetLastError());
+    return TC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tc_prefill_workspace_spec(int device, int64_t batch, int64_t tokens, int64_t q_heads, int64_t num_splits,
+                              int64_t mapping, int causal, int64_t spec[3]) {
+    tc::DeviceInfo info;
+    int status = check_geometry(device, batch, tokens, q_heads, num_splits, mapping, causal, &info);
+    if (status != TC_OK) return status;
+    TC_REQUIRE(spec, "null spec");
+    spec[0] = 1;
+    spec[1] = 0;
+    spec[2] = 0;
+    return TC_OK;
+}
+
+int tc_prefill_forward_out(int device, void* stream, const void* q, const int64_t q_strides[3], const void* k,
+                           const int64_t k_strides[3], const void* v, const int64_t v_strides[3], void* out,
+                           float* lse, int64_t workspace_o_elems, int64_t workspace_lse_elems, int64_t batch,
+                           int64_t tokens, int64_t q_heads, int64_t num_splits, int64_t mapping, double scale,
+                           int causal) {
+    tc::DeviceInfo info;
+    int status = check_geometry(device, batch, tokens, q_heads, num_splits, mapping, causal, &info);
+    if (status != TC_OK) return status;
+    const int64_t kv_heads = q_heads / kGroup;
+    TC_REQUIRE(q && k && v && out && lse, "null tensor pointer");
+    TC_REQUIRE(workspace_o_elems == 0 && workspace_lse_elems == 0, "Generated long prefill uses no split workspace");
+    TC_REQUIRE(std::isfinite(scale) && scale > 0, "Finite positive model attention scale required");
+    if ((status = check_strides("q", q_strides, batch, tokens, q_heads)) != TC_OK) return status;
+    if ((status = check_strides("k", k_strides, batch, tokens, kv_heads)) != TC_OK) return status;
+    if ((status = check_strides("v", v_strides, batch, tokens, kv_heads)) != TC_OK) return status;
+    for (const void* pointer : {q, k, v, static_cast<const void*>(out)})
+        TC_REQUIRE(reinterpret_cast<uintptr_t>(pointer) % 16 == 0, "Aligned native Q/K/V/O base required");
+    TC_REQUIRE(reinterpret_cast<uintptr_t>(lse) % 16 == 0, "Aligned LSE base required");
+    const size_t out_bytes = size_t(batch) * tokens * q_heads * kDim * 2, lse_bytes = size_t(batch) * q_heads * tokens * 4;
+    const void* inputs[3] = {q, k, v};
+    const size_t input_bytes[3] = {span_bytes(q_strides, batch, tokens, q_heads), span_bytes(k_strides, batch, tokens, kv_heads),
+                                   span_bytes(v_strides, batch, tokens, kv_heads)};
+    for (int i = 0; i < 3; ++i)
+        TC_REQUIRE(!tc::ranges_overlap(out, out_bytes, inputs[i], input_bytes[i]) &&
+                       !tc::ranges_overlap(lse, lse_bytes, inputs[i], input_bytes[i]),
+                   "Writable output aliases actual strided input storage span");
+    TC_REQUIRE(!tc::ranges_overlap(out, out_bytes, lse, lse_bytes), "O/LSE overlap");
+
+    tc::DeviceGuard guard(device);
+    TC_CUDA(guard.status);
+    tc::DeviceScratch scratch;
+    if ((status = tc::device_scratch(device, &scratch)) != TC_OK) return status;
+    CUtensorMap qmap, kmap, vmap, omap;
+    if ((status = tc::make_rows_map(&qmap, q, false, q_heads, tokens, batch, q_strides[2], q_strides[1], q_strides[0], kBlockM, 2)) != TC_OK) return status;
+    if ((status = tc::make_rows_map(&kmap, k, false, kv_heads, tokens, batch, k_strides[2], k_strides[1], k_strides[0], kBlockN, 2)) != TC_OK) return status;
+    if ((status = tc::make_rows_map(&vmap, v, false, kv_heads, tokens, batch, v_strides[2], v_strides[1], v_strides[0], kBlockN, 2)) != TC_OK) return status;
+    if ((status = tc::make_rows_map(&omap, out, false, q_heads, tokens, batch, kDim, q_heads * kDim, tokens * q_heads * kDim, kBlockM, 2)) != TC_OK) return status;
+
+    PrefillParams p{};
+    p.lse = lse;
+    p.status = scratch.status;
+    p.batch = int(batch);
+    p.tokens = int(tokens);
+    p.q_heads = int(q_heads);
+    p.kv_heads = int(kv_heads);
+    p.m_blocks = int((tokens + kBlockM - 1) / kBlockM);
+    p.scale = float(scale);
+    p.scale_log2 = float(scale) * float(M_LOG2E);
+    TC_REQUIRE(std::isfinite(p.scale_log2) && p.scale > 0.f, "attention scale is not a positive finite FP32 value");
+    return mapping == 1 ? launch<true>(qmap, kmap, vmap, omap, p, static_cast<cudaStream_t>(stream))
+                        : launch<false>(qmap, kmap, vmap, omap, p, static_cast<cudaStream_t>(stream));
+}
+
+int tc_prefill_resources(int device, const int64_t q_strides[3], const int64_t k_strides[3],
+                         const int64_t v_strides[3], int64_t batch, int64_t tokens, int64_t q_heads,
+                         int64_t num_splits, int64_t mapping, int causal, int64_t* values, int64_t capacity,
+                         int64_t* count) {
+    tc::DeviceInfo info;
+    int status = check_geometry(device, batch, tokens, q_heads, num_splits, mapping, causal, &info);
+    if (status != TC_OK) return status;
+    TC_REQUIRE(q_strides && k_strides && v_strides && values && count && capacity >= 46, "resources needs room for 46 values");
+    tc::DeviceGuard guard(device);
+    TC_CUDA(guard.status);
+    const int64_t tiles = (tokens + kBlockM - 1) / kBlockM;
+    const int64_t header[12] = {1, tokens, q_heads, kGroup, 1, batch * (q_heads / 2) * tiles, 0, 0, 0, kBlockM, kBlockN, 1};
+    for (int i = 0; i < 12; ++i) values[i] = header[i];
+    status = mapping == 1 ? tc::kernel_resources(&prefill_kernel<true>, kThreads, shared_bytes(true), values + 12)
+                          : tc::kernel_resources(&prefill_kernel<false>, kThreads, shared_bytes(false), values + 12);
+    if (status != TC_OK) return status;
+    for (int i = 20; i < 28; ++i) values[i] = 0;
+    const int64_t layout[18] = {0, tokens, tokens, q_heads, q_heads / kGroup, 1, MODEL_FAMILY_CODE,
+                                q_strides[0], q_strides[1], q_strides[2], k_strides[0], k_strides[1], k_strides[2],
+                                v_strides[0], v_strides[1], v_strides[2], q_strides[1], q_strides[2]};
+    for (int i = 0; i < 18; ++i) values[28 + i] = layout[i];
+    *count = 46;
+    return TC_OK;
+}
+
+}  // extern "C"

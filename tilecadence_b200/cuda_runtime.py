@@ -1,0 +1,448 @@
+"""Build and load the sm_100a C-ABI library behind the reference's operator interface.
+
+Mirrors ``tilecadence/cuda_runtime.py`` (``cuda_device`` :63-75, ``build_cuda`` :78-146): a
+directory emitted by :mod:`tilecadence_b200.operator` is compiled for the GPU and returned as an
+object with ``forward_out`` / ``workspace_spec`` / ``resources`` plus a build receipt. Differences
+that follow from the B200-only design:
+
+* the target is always ``compute_100a``/``sm_100a``; a device of any other generation is rejected;
+* the library is a plain shared object with ``extern "C"`` entry points loaded through ``ctypes``
+  (no torch C++ extension, no dispatcher namespace); tensors are validated here exactly as the
+  reference's host code does (``cuda/prefill/common.cuh:36-60``, ``cuda/decode/decode.cu:38-60,
+  158-179``) and passed down as raw pointers on torch's current stream;
+* builds are cached inside the package tree under ``_build/`` keyed by the hash of every source
+  file and flag, so a library compiled on a machine without a GPU is reused on the GPU box;
+* no FlashAttention / CUTLASS checkout is needed; ``flash_attention_root`` is accepted and ignored.
+
+There is no CPU path: if the library cannot be built or loaded the calls raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from hashlib import sha256
+import json
+import os
+from pathlib import Path
+import shutil
+import subprocess
+import threading
+
+PACKAGE_ROOT = Path(__file__).resolve().parent
+CSRC = PACKAGE_ROOT / "csrc"
+INCLUDE = PACKAGE_ROOT.parent / "include"
+BUILD_DIR = PACKAGE_ROOT / "_build"
+TARGET = "sm_100a"
+CUDA_FLAGS = (
+    "-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-Xcompiler", "-fPIC", "-shared",
+)
+SOURCE_SUFFIXES = (".cu", ".cuh", ".h", ".hpp", ".cpp")
+PHASES = ("prefill", "decode", "exchange")
+
+_lock = threading.Lock()
+_loaded: dict[str, "Library"] = {}
+
+
+def file_sha256(path):
+    with Path(path).open("rb") as stream:
+        digest = sha256()
+        for chunk in iter(lambda: stream.read(1024 * 1024), b""):
+            digest.update(chunk)
+        return digest.hexdigest()
+
+
+def find_nvcc():
+    home = os.environ.get("CUDA_HOME") or os.environ.get("CUDA_PATH") or "/usr/local/cuda"
+    candidate = Path(home) / "bin" / "nvcc"
+    if candidate.is_file():
+        return candidate
+    found = shutil.which("nvcc")
+    return Path(found) if found else None
+
+
+def cuda_device(device="cuda:0"):
+    """Validate the selected device: CUDA, visible, and compute capability 10.x."""
+    import torch
+
+    selected = torch.device(device)
+    if selected.type != "cuda" or not torch.version.cuda or not torch.cuda.is_available():
+        raise RuntimeError("An NVIDIA CUDA device and CUDA-enabled PyTorch are required")
+    index = torch.cuda.current_device() if selected.index is None else selected.index
+    selected = torch.device("cuda", index)
+    capability = torch.cuda.get_device_capability(selected)
+    if capability[0] != 10:
+        raise RuntimeError(f"The kernels are written for sm_100a only; device reports sm_{capability[0]}{capability[1]}")
+    return selected, capability
+
+
+def staged_sources(phase):
+    """Flat {name: path} view of what an emitted directory for one phase contains."""
+    files = {"tilecadence_b200.h": INCLUDE / "tilecadence_b200.h"}
+    for directory in ("common", phase):
+        for path in sorted((CSRC / directory).iterdir()):
+            if path.is_file() and path.suffix in SOURCE_SUFFIXES:
+                files[path.name] = path
+    return files
+
+
+def _compile(units, include_dirs, files, verbose=False):
+    """Compile ``units`` into one cached shared object; needs nvcc but no GPU.
+
+    The cache key covers the named source files and the flags only, so a library built on a
+    machine without a GPU is found again on the GPU machine from the same sources.
+    """
+    compiler = "unknown"
+    nvcc = find_nvcc()
+    if nvcc is not None:
+        compiler = subprocess.check_output([str(nvcc), "--version"], text=True).strip().splitlines()[-1]
+    identity = {
+        "source_sha256": {name: file_sha256(path) for name, path in sorted(files.items())},
+        "target": TARGET,
+        "cuda_flags": list(CUDA_FLAGS),
+    }
+    key = sha256(json.dumps(identity, sort_keys=True).encode()).hexdigest()[:20]
+    identity["cuda_compiler"] = compiler
+    name = "tilecadence_" + key
+    library = BUILD_DIR / f"lib{name}.so"
+    with _lock:
+        if not library.is_file():
+            if nvcc is None:
+                raise RuntimeError("Set CUDA_HOME to an installed CUDA Toolkit with nvcc: no prebuilt library "
+                                   f"matches these sources ({library.name})")
+            BUILD_DIR.mkdir(parents=True, exist_ok=True)
+            temporary = library.with_name(f"{library.stem}.{os.getpid()}.tmp.so")
+            command = [str(nvcc), *CUDA_FLAGS]
+            if verbose:
+                command.append("-Xptxas=-v")
+            for directory in include_dirs:
+                command += ["-I", str(directory)]
+            command += [*map(str, units), "-o", str(temporary)]
+            result = subprocess.run(command, capture_output=True, text=True)
+            if result.returncode != 0:
+                raise RuntimeError(f"nvcc failed:\n{result.stdout}\n{result.stderr}")
+            if verbose:
+                print(result.stderr)
+            os.replace(temporary, library)
+    identity.update(module=name, module_path=str(library), module_sha256=file_sha256(library))
+    return library, identity
+
+
+def compile_directory(source_dir, verbose=False):
+    """Compile every .cu of a flat emitted directory. Returns ``(library_path, identity)``."""
+    source_dir = Path(source_dir).resolve()
+    files = {path.name: path for path in sorted(source_dir.iterdir())
+             if path.is_file() and path.suffix in SOURCE_SUFFIXES}
+    units = [path for path in files.values() if path.suffix == ".cu"]
+    if not units:
+        raise ValueError(f"No generated CUDA translation unit in {source_dir}")
+    return _compile(units, [source_dir], files, verbose)
+
+
+def compile_tree(verbose=False):
+    """Compile every phase from the in-tree sources (default offsets) into one library."""
+    files = {"tilecadence_b200.h": INCLUDE / "tilecadence_b200.h"}
+    units = []
+    for folder in sorted(path for path in CSRC.iterdir() if path.is_dir()):
+        for path in sorted(folder.iterdir()):
+            if path.is_file() and path.suffix in SOURCE_SUFFIXES:
+                files[f"{folder.name}/{path.name}"] = path
+                if path.suffix == ".cu":
+                    units.append(path)
+    return _compile(units, [CSRC / "common", INCLUDE], files, verbose)
+
+
+class Library:
+    """ctypes view of one compiled C-ABI library."""
+
+    SIGNATURES = {
+        "tc_last_error": (ctypes.c_char_p, ()),
+        "tc_abi_version": (ctypes.c_int, ()),
+        "tc_device_status": (ctypes.c_int, (ctypes.c_int, ctypes.POINTER(ctypes.c_int32))),
+        "tc_prefill_workspace_spec": (ctypes.c_int, (ctypes.c_int, *[ctypes.c_int64] * 5, ctypes.c_int,
+                                                     ctypes.POINTER(ctypes.c_int64))),
+        "tc_prefill_forward_out": (ctypes.c_int, (
+            ctypes.c_int, ctypes.c_void_p,
+            ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64), ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64),
+            ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64), ctypes.c_void_p, ctypes.c_void_p,
+            *[ctypes.c_int64] * 7, ctypes.c_double, ctypes.c_int)),
+        "tc_prefill_resources": (ctypes.c_int, (
+            ctypes.c_int, *[ctypes.POINTER(ctypes.c_int64)] * 3, *[ctypes.c_int64] * 5, ctypes.c_int,
+            ctypes.POINTER(ctypes.c_int64), ctypes.c_int64, ctypes.POINTER(ctypes.c_int64))),
+        "tc_decode_workspace_spec": (ctypes.c_int, (ctypes.c_int, *[ctypes.c_int64] * 5, ctypes.c_int,
+                                                    ctypes.POINTER(ctypes.c_int64))),
+        "tc_decode_forward_out": (ctypes.c_int, (
+            ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
+            ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int)),
+        "tc_decode_partial_out": (ctypes.c_int, (
+            ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
+            ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, ctypes.c_int64)),
+        "tc_combine_partials": (ctypes.c_int, (ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                               ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p)),
+        "tc_decode_resources": (ctypes.c_int, (ctypes.c_int, *[ctypes.c_int64] * 5, ctypes.c_int,
+                                               ctypes.POINTER(ctypes.c_int64), ctypes.c_int64,
+                                               ctypes.POINTER(ctypes.c_int64))),
+    }
+
+    def __init__(self, path):
+        self.path = Path(path)
+        self.handle = ctypes.CDLL(str(self.path))
+        self.symbols = set()
+        for name, (restype, argtypes) in self.SIGNATURES.items():
+            try:
+                function = getattr(self.handle, name)
+            except AttributeError:
+                continue
+            function.restype = restype
+            function.argtypes = list(argtypes)
+            self.symbols.add(name)
+        if "tc_last_error" not in self.symbols:
+            raise RuntimeError(f"{self.path} does not export the tilecadence_b200 C ABI")
+
+    def has(self, prefix):
+        return any(name.startswith(prefix) for name in self.symbols)
+
+    def call(self, name, *arguments):
+        if name not in self.symbols:
+            raise RuntimeError(f"{self.path.name} does not export {name}; this library was built for another phase")
+        status = getattr(self.handle, name)(*arguments)
+        if status != 0:
+            message = self.handle.tc_last_error().decode("utf-8", "replace")
+            raise RuntimeError(f"{name}: {message} (status {status})")
+
+    def device_status(self, device_index):
+        value = ctypes.c_int32(0)
+        self.call("tc_device_status", int(device_index), ctypes.byref(value))
+        return value.value
+
+
+def load_library(path):
+    path = str(Path(path).resolve())
+    with _lock:
+        if path not in _loaded:
+            _loaded[path] = Library(path)
+        return _loaded[path]
+
+
+def _strides(tensor):
+    return (ctypes.c_int64 * 3)(tensor.stride(0), tensor.stride(1), tensor.stride(2))
+
+
+def _stream(tensor):
+    import torch
+
+    return ctypes.c_void_p(torch.cuda.current_stream(tensor.device).cuda_stream)
+
+
+def _require(condition, message):
+    if not condition:
+        raise RuntimeError(message)
+
+
+def _pointer(tensor):
+    return ctypes.c_void_p(tensor.data_ptr())
+
+
+class PrefillOps:
+    """``forward_out`` / ``workspace_spec`` / ``resources`` with the reference's prefill schemas
+    (``tilecadence/cuda/prefill/binding.cpp:11-13``). ``q_heads`` defaults to the reference's 32;
+    a KV-head-group shard may pass its own count."""
+
+    phase = "prefill"
+
+    def __init__(self, library, q_heads=32):
+        self.library = library
+        self.q_heads = q_heads
+
+    def _check_inputs(self, q, k, v, causal):
+        import torch
+
+        heads = self.q_heads
+        _require(q.is_cuda and q.dim() == 4 and q.size(0) > 0 and q.size(1) > 0 and q.size(2) == heads
+                 and q.size(3) == 128, f"Q must be actual CUDA BNHD[B,T,{heads},128]")
+        for tensor in (q, k, v):
+            _require(tensor.device == q.device and tensor.dtype == torch.bfloat16 and not tensor.requires_grad,
+                     "Same-device inference BF16 Q/K/V required")
+            _require(tensor.dim() == 4 and tensor.stride(3) == 1, "BNHD inputs must have contiguous last dimension only")
+            _require(tensor.data_ptr() % 16 == 0, "Aligned native Q/K/V base required")
+            for axis in range(3):
+                _require(tensor.size(axis) == 1 or (tensor.stride(axis) >= 0 and tensor.stride(axis) % 8 == 0),
+                         "Native vector row/head alignment requires strides divisible by8 elements")
+        _require(k.size(0) == q.size(0) and k.size(1) > 0 and k.size(2) == heads // 4 and k.size(3) == 128
+                 and v.shape == k.shape, f"Actual visible K/V must be BNHD[B,Tk,{heads // 4},128]")
+        _require(bool(causal) and q.size(1) > 1 and q.size(1) == k.size(1), "Full causal no-past prefill requires Tq=Tk>1")
+
+    def workspace_spec(self, q, k, v, num_splits, mapping, causal):
+        self._check_inputs(q, k, v, causal)
+        spec = (ctypes.c_int64 * 3)()
+        self.library.call("tc_prefill_workspace_spec", q.device.index, q.size(0), q.size(1), q.size(2),
+                          int(num_splits), int(mapping), int(bool(causal)), spec)
+        return list(spec)
+
+    def forward_out(self, q, k, v, out, lse, workspace_o, workspace_lse, num_splits, mapping, scale, causal):
+        import torch
+
+        self._check_inputs(q, k, v, causal)
+        _require(out.device == q.device and out.dtype == q.dtype and out.shape == q.shape and out.is_contiguous()
+                 and not out.requires_grad, "Common complete output must be contiguous BNHD with Q shape")
+        _require(lse.device == q.device and lse.dtype == torch.float32 and lse.is_contiguous() and not lse.requires_grad
+                 and tuple(lse.shape) == (q.size(0), q.size(2), q.size(1)),
+                 f"Complete natural-log LSE must be FP32[B,{q.size(2)},Tq]")
+        _require(workspace_o.numel() == 0 and workspace_lse.numel() == 0, "Generated long prefill uses no split workspace")
+        self.library.call(
+            "tc_prefill_forward_out", q.device.index, _stream(q), _pointer(q), _strides(q), _pointer(k), _strides(k),
+            _pointer(v), _strides(v), _pointer(out), _pointer(lse), 0, 0, q.size(0), q.size(1), q.size(2),
+            int(num_splits), int(mapping), float(scale), int(bool(causal)))
+
+    def resources(self, q, k, v, num_splits, mapping, causal):
+        self._check_inputs(q, k, v, causal)
+        values = (ctypes.c_int64 * 64)()
+        count = ctypes.c_int64(0)
+        self.library.call("tc_prefill_resources", q.device.index, _strides(q), _strides(k), _strides(v), q.size(0),
+                          q.size(1), q.size(2), int(num_splits), int(mapping), int(bool(causal)), values, 64,
+                          ctypes.byref(count))
+        return list(values[:count.value])
+
+
+class DecodeOps:
+    """``forward_out`` / ``workspace_spec`` / ``resources`` with the reference's decode schemas
+    (``tilecadence/cuda/decode/binding.cpp:17-24``), plus the sharded ``partial_out`` and
+    ``combine_partials`` used by the multi-GPU driver."""
+
+    phase = "decode"
+
+    def __init__(self, library, q_heads=32):
+        self.library = library
+        self.q_heads = q_heads
+
+    def _check_q_cache_lengths(self, q, cache, lengths):
+        import torch
+
+        heads = self.q_heads
+        _require(q.is_cuda and cache.is_cuda and lengths.is_cuda and q.device == cache.device
+                 and q.device == lengths.device, "Q/cache/old_lengths must be CUDA on the same device")
+        _require(q.dim() == 4 and q.size(0) > 0 and q.size(1) == 1 and q.size(2) == heads and q.size(3) == 128,
+                 f"Q must be [B,1,{heads},128]")
+        _require(cache.dim() == 4 and cache.size(0) == q.size(0) and cache.size(1) >= 4 and cache.size(2) == heads // 4
+                 and cache.size(3) == 128, f"Full capacity cache must be [B,C>=4,{heads // 4},128]")
+        _require(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and q.is_contiguous()
+                 and cache.is_contiguous() and not q.requires_grad and not cache.requires_grad,
+                 "Contiguous BF16 inference Q and FULL capacity cache required")
+        _require(lengths.dtype == torch.int32 and lengths.is_contiguous() and lengths.dim() == 1
+                 and lengths.size(0) == q.size(0) and not lengths.requires_grad,
+                 "old_lengths must be contiguous CUDA int32[B]")
+        for tensor in (q, cache):
+            _require(tensor.data_ptr() % 16 == 0, "16-byte aligned Q/cache required")
+
+    def workspace_spec(self, q, kcache, old_lengths, num_splits, mapping, append):
+        self._check_q_cache_lengths(q, kcache, old_lengths)
+        spec = (ctypes.c_int64 * 3)()
+        self.library.call("tc_decode_workspace_spec", q.device.index, q.size(0), kcache.size(1), kcache.size(2),
+                          int(num_splits), int(mapping), int(bool(append)), spec)
+        return list(spec)
+
+    def _check_call(self, q, kcache, vcache, knew, vnew, old_lengths, workspace_o, workspace_lse):
+        import torch
+
+        self._check_q_cache_lengths(q, kcache, old_lengths)
+        _require(vcache.device == q.device and vcache.shape == kcache.shape and vcache.dtype == q.dtype
+                 and vcache.is_contiguous() and not vcache.requires_grad, "Vcache must match FULL contiguous BF16 Kcache")
+        for tensor in (knew, vnew):
+            _require(tensor.device == q.device and tensor.dtype == q.dtype
+                     and tuple(tensor.shape) == (q.size(0), 1, kcache.size(2), 128) and tensor.is_contiguous()
+                     and not tensor.requires_grad, "knew/vnew must be contiguous BF16[B,1,Hkv,128]")
+        for workspace in (workspace_o, workspace_lse):
+            _require(workspace.is_cuda and workspace.device == q.device and workspace.dtype == torch.float32
+                     and workspace.is_contiguous() and not workspace.requires_grad,
+                     "Contiguous CUDA FP32 workspace required")
+
+    def forward_out(self, q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse,
+                    num_splits, mapping, append):
+        import torch
+
+        self._check_call(q, kcache, vcache, knew, vnew, old_lengths, workspace_o, workspace_lse)
+        _require(out.device == q.device and out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous()
+                 and not out.requires_grad, "Invalid complete output")
+        _require(lse.device == q.device and lse.dtype == torch.float32 and lse.is_contiguous()
+                 and tuple(lse.shape) == (q.size(0), q.size(2), 1) and not lse.requires_grad, "Invalid full float32 LSE")
+        self.library.call(
+            "tc_decode_forward_out", q.device.index, _stream(q), _pointer(q), _pointer(kcache), _pointer(vcache),
+            _pointer(knew), _pointer(vnew), _pointer(old_lengths), _pointer(out), _pointer(lse),
+            _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse), workspace_lse.numel(),
+            q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping), int(bool(append)))
+
+    def partial_out(self, q, kcache, vcache, knew, vnew, old_lengths, partial_o, partial_lse, workspace_o,
+                    workspace_lse, num_splits, mapping, append, kv_shard_start):
+        import torch
+
+        self._check_call(q, kcache, vcache, knew, vnew, old_lengths, workspace_o, workspace_lse)
+        rows = q.size(0) * q.size(2)
+        _require(partial_o.device == q.device and partial_o.dtype == torch.float32 and partial_o.is_contiguous()
+                 and partial_o.numel() == rows * 128, "partial O must be contiguous FP32[B,Hq,128]")
+        _require(partial_lse.device == q.device and partial_lse.dtype == torch.float32 and partial_lse.is_contiguous()
+                 and partial_lse.numel() == rows, "partial LSE must be contiguous FP32[B,Hq]")
+        self.library.call(
+            "tc_decode_partial_out", q.device.index, _stream(q), _pointer(q), _pointer(kcache), _pointer(vcache),
+            _pointer(knew), _pointer(vnew), _pointer(old_lengths), _pointer(partial_o), _pointer(partial_lse),
+            _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse), workspace_lse.numel(),
+            q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping), int(bool(append)),
+            int(kv_shard_start))
+
+    def combine_partials(self, partial_o, partial_lse, out, lse):
+        import torch
+
+        parts = partial_o.size(0)
+        rows = partial_lse.numel() // parts
+        _require(partial_o.is_cuda and partial_o.dtype == torch.float32 and partial_o.is_contiguous()
+                 and partial_lse.dtype == torch.float32 and partial_lse.is_contiguous()
+                 and partial_o.numel() == parts * rows * 128, "partials must be contiguous FP32 [parts,rows,128] / [parts,rows]")
+        _require(out.dtype == torch.bfloat16 and out.is_contiguous() and out.numel() == rows * 128
+                 and lse.dtype == torch.float32 and lse.is_contiguous() and lse.numel() == rows,
+                 "combined O must be BF16[rows,128] and LSE FP32[rows]")
+        self.library.call("tc_combine_partials", partial_o.device.index, _stream(partial_o), _pointer(partial_o),
+                          _pointer(partial_lse), parts, rows, _pointer(out), _pointer(lse))
+
+    def resources(self, q, kcache, old_lengths, num_splits, mapping, append):
+        self._check_q_cache_lengths(q, kcache, old_lengths)
+        values = (ctypes.c_int64 * 64)()
+        count = ctypes.c_int64(0)
+        self.library.call("tc_decode_resources", q.device.index, q.size(0), kcache.size(1), kcache.size(2),
+                          int(num_splits), int(mapping), int(bool(append)), values, 64, ctypes.byref(count))
+        return list(values[:count.value])
+
+
+def ops_for(library, phase=None, q_heads=32):
+    if phase is None:
+        phase = "prefill" if library.has("tc_prefill_") else "decode" if library.has("tc_decode_") else None
+    if phase == "prefill":
+        return PrefillOps(library, q_heads)
+    if phase == "decode":
+        return DecodeOps(library, q_heads)
+    raise RuntimeError(f"{library.path} exports neither the prefill nor the decode operator")
+
+
+def build_cuda(source_dir, flash_attention_root=None, device="cuda:0"):
+    """Return the operator object for an emitted directory and its reproducible build metadata."""
+    import torch
+
+    device, _ = cuda_device(device)
+    library_path, identity = compile_directory(source_dir)
+    library = load_library(library_path)
+    receipt = {
+        **identity,
+        "torch": torch.__version__,
+        "torch_cuda": torch.version.cuda,
+        "device_name": torch.cuda.get_device_name(device),
+        "device_index": device.index,
+    }
+    return ops_for(library), receipt
+
+
+def default_library():
+    """The combined library (every phase) built from the in-tree sources with default offsets."""
+    library_path, _ = compile_tree()
+    return load_library(library_path)
+
+
+def default_ops(phase, q_heads=32):
+    return ops_for(default_library(), phase, q_heads)
