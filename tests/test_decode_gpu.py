@@ -1,0 +1,186 @@
+"""Parity of the fused split-KV decode kernel with the CPU oracle, through the C ABI.
+
+Tolerances (the acceptance bar of this path): O max-abs error <= 2e-2 (BF16), LSE <= 1e-3
+relative, cache appends and untouched rows bit-exact. The checks follow the reference's own
+decode verification (``tilecadence/bench_operator.py:46-78``): two consecutive steps, history and
+both appended rows compared as raw 16-bit words, and bitwise equality between the two mappings.
+"""
+import pytest
+import torch
+
+from oracle import attention as oracle
+from tilecadence_b200 import cuda_runtime
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops(library):
+    return cuda_runtime.ops_for(library, "decode")
+
+
+def run_step(ops, device, q, kcache, vcache, knew, vnew, old, mapping=1, num_splits=0, append=True):
+    """Run one step on device copies; returns (O, LSE, kcache_after, vcache_after) on the host."""
+    dq, dk, dv, dkn, dvn = (t.to(device) for t in (q, kcache, vcache, knew, vnew))
+    dold = old.to(device=device, dtype=torch.int32)
+    out = torch.full_like(dq, float("nan"))
+    lse = torch.full((q.size(0), q.size(2), 1), float("nan"), device=device, dtype=torch.float32)
+    spec = ops.workspace_spec(dq, dk, dold, num_splits, mapping, append)
+    ws_o = torch.full((spec[1],), float("nan"), device=device, dtype=torch.float32)
+    ws_lse = torch.full((spec[2],), float("nan"), device=device, dtype=torch.float32)
+    ops.forward_out(dq, dk, dv, dkn, dvn, dold, out, lse, ws_o, ws_lse, num_splits, mapping, append)
+    torch.cuda.synchronize()
+    assert ops.library.device_status(device.index) == 0
+    return out.cpu(), lse.cpu(), dk.cpu(), dv.cpu(), spec
+
+
+def make_case(seed, batch, capacity, kv_heads=8, fill=None):
+    kcache, vcache, q, knew, vnew = oracle.seeded_normal(
+        seed, (batch, capacity, kv_heads, 128), (batch, capacity, kv_heads, 128), (batch, 1, kv_heads * 4, 128),
+        (batch, 1, kv_heads, 128), (batch, 1, kv_heads, 128))
+    if fill is not None:  # rows past the valid prefix hold NaN bit patterns: they must never matter
+        for b, length in enumerate(fill):
+            kcache[b, length:] = float("nan")
+            vcache[b, length:] = float("nan")
+    return q, kcache, vcache, knew, vnew
+
+
+def bits(tensor):
+    return tensor.contiguous().view(torch.int16)
+
+
+@pytest.mark.parametrize("batch,capacity,lengths", [
+    (1, 200, [130]),
+    (2, 200, [130, 7]),
+    (1, 64, [0]),                 # the appended row is the only visible key
+    (1, 65, [64]),                # append lands in the last, one-row tile at the end of capacity
+    (4, 1024, [1023, 0, 511, 64]),  # ragged batch, one sequence filling the cache
+    (1, 4096, [2500]),
+])
+def test_decode_matches_oracle(ops, gpu_device, batch, capacity, lengths):
+    q, kcache, vcache, knew, vnew = make_case(100 + capacity, batch, capacity, fill=lengths)
+    old = torch.tensor(lengths, dtype=torch.int32)
+    want_o, want_lse, want_k, want_v = oracle.decode_step(q, kcache, vcache, knew, vnew, old)
+    got_o, got_lse, got_k, got_v, _ = run_step(ops, gpu_device, q, kcache, vcache, knew, vnew, old)
+    oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+    assert torch.equal(bits(got_k), bits(want_k)) and torch.equal(bits(got_v), bits(want_v))
+
+
+def test_two_steps_like_the_reference_harness(ops, gpu_device):
+    """Config 4 geometry at reduced capacity: prefix, then two appended tokens (bench_operator.py:46-78)."""
+    batch, length = 1, 1000
+    prefix_k, prefix_v = oracle.seeded_normal(3, (batch, length, 8, 128), (batch, length, 8, 128))
+    steps = [oracle.seeded_normal(30 + s, (batch, 1, 32, 128), (batch, 1, 8, 128), (batch, 1, 8, 128)) for s in range(2)]
+    results = []
+    for mapping in (0, 1):
+        kcache = torch.zeros((batch, length + 2, 8, 128), dtype=torch.bfloat16)
+        vcache = torch.zeros_like(kcache)
+        kcache[:, :length], vcache[:, :length] = prefix_k, prefix_v
+        outputs = []
+        for step, (q, knew, vnew) in enumerate(steps):
+            old = torch.full((batch,), length + step, dtype=torch.int32)
+            want_o, want_lse, want_k, want_v = oracle.decode_step(q, kcache, vcache, knew, vnew, old)
+            got_o, got_lse, kcache, vcache, _ = run_step(ops, gpu_device, q, kcache, vcache, knew, vnew, old, mapping)
+            oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+            assert torch.equal(bits(kcache), bits(want_k)) and torch.equal(bits(vcache), bits(want_v))
+            outputs.append((got_o, got_lse))
+        for idx, (cache, prefix) in enumerate(((kcache, prefix_k), (vcache, prefix_v))):
+            assert torch.equal(bits(cache[:, :length]), bits(prefix))
+            assert torch.equal(bits(cache[:, length:length + 1]), bits(steps[0][idx + 1]))
+            assert torch.equal(bits(cache[:, length + 1:length + 2]), bits(steps[1][idx + 1]))
+        results.append(outputs)
+    for (o0, l0), (o1, l1) in zip(*results):  # the two mappings agree bit for bit
+        assert torch.equal(bits(o0), bits(o1)) and torch.equal(l0.view(torch.int32), l1.view(torch.int32))
+
+
+@pytest.mark.parametrize("num_splits", [1, 2, 5, 37, 128])
+def test_split_counts_agree(ops, gpu_device, num_splits):
+    q, kcache, vcache, knew, vnew = make_case(7, 2, 3000, fill=[2999, 100])
+    old = torch.tensor([2999, 100], dtype=torch.int32)
+    want_o, want_lse, want_k, want_v = oracle.decode_step(q, kcache, vcache, knew, vnew, old)
+    got_o, got_lse, got_k, got_v, spec = run_step(ops, gpu_device, q, kcache, vcache, knew, vnew, old,
+                                                  num_splits=num_splits)
+    assert spec[0] == num_splits and spec[1] == (0 if num_splits == 1 else num_splits * 2 * 32 * 128)
+    oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+    assert torch.equal(bits(got_k), bits(want_k)) and torch.equal(bits(got_v), bits(want_v))
+
+
+def test_without_append_the_cache_is_untouched(ops, gpu_device):
+    q, kcache, vcache, knew, vnew = make_case(8, 2, 300, fill=[300, 0])
+    old = torch.tensor([300, 0], dtype=torch.int32)  # second sequence sees no key at all
+    want_o, want_lse, _, _ = oracle.decode_step(q, kcache, vcache, knew, vnew, old, append=False)
+    got_o, got_lse, got_k, got_v, _ = run_step(ops, gpu_device, q, kcache, vcache, knew, vnew, old, append=False)
+    oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+    assert torch.isinf(got_lse[1]).all() and (got_lse[1] > 0).all() and (got_o[1] == 0).all()
+    assert torch.equal(bits(got_k), bits(kcache)) and torch.equal(bits(got_v), bits(vcache))
+
+
+def test_config4_full_size(ops, gpu_device):
+    """BASELINE config 4: capacity 32768, 8192 valid tokens, seed 3, two appended tokens."""
+    capacity, length = 32768, 8192
+    kcache = torch.zeros((1, capacity, 8, 128), dtype=torch.bfloat16)
+    vcache = torch.zeros_like(kcache)
+    generator = torch.Generator().manual_seed(3)
+    kcache[:, :length] = torch.randn((1, length, 8, 128), generator=generator).to(torch.bfloat16)
+    vcache[:, :length] = torch.randn((1, length, 8, 128), generator=generator).to(torch.bfloat16)
+    for step in range(2):
+        q, knew, vnew = (torch.randn(shape, generator=generator).to(torch.bfloat16)
+                         for shape in ((1, 1, 32, 128), (1, 1, 8, 128), (1, 1, 8, 128)))
+        old = torch.tensor([length + step], dtype=torch.int32)
+        want_o, want_lse, want_k, want_v = oracle.decode_step(q, kcache, vcache, knew, vnew, old)
+        got_o, got_lse, kcache, vcache, _ = run_step(ops, gpu_device, q, kcache, vcache, knew, vnew, old)
+        oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+        assert torch.equal(bits(kcache), bits(want_k)) and torch.equal(bits(vcache), bits(want_v))
+    assert not kcache[:, length + 2:].any() and not vcache[:, length + 2:].any()
+
+
+def test_sharded_partials_and_combine(ops, gpu_device):
+    """KV-sequence shards produce partials whose LSE-weighted merge equals the unsharded step."""
+    batch, capacity, shards = 4, 2048, 4
+    q, kcache, vcache, knew, vnew = make_case(9, batch, capacity)
+    old = torch.tensor([2047, 5, 1024, 600], dtype=torch.int32)
+    want_o, want_lse, want_k, want_v = oracle.decode_step(q, kcache, vcache, knew, vnew, old)
+    device = gpu_device
+    dq, dkn, dvn, dold = q.to(device), knew.to(device), vnew.to(device), old.to(device)
+    part_o = torch.empty((shards, batch * 32, 128), device=device, dtype=torch.float32)
+    part_lse = torch.empty((shards, batch * 32), device=device, dtype=torch.float32)
+    shard_len = capacity // shards
+    caches = []
+    for s in range(shards):
+        dk = kcache[:, s * shard_len:(s + 1) * shard_len].contiguous().to(device)
+        dv = vcache[:, s * shard_len:(s + 1) * shard_len].contiguous().to(device)
+        spec = ops.workspace_spec(dq, dk, dold, 0, 1, True)
+        ws_o = torch.empty((spec[1],), device=device, dtype=torch.float32)
+        ws_lse = torch.empty((spec[2],), device=device, dtype=torch.float32)
+        ops.partial_out(dq, dk, dv, dkn, dvn, dold, part_o[s], part_lse[s], ws_o, ws_lse, 0, 1, True, s * shard_len)
+        caches.append((dk, dv))
+    out = torch.empty((batch, 1, 32, 128), device=device, dtype=torch.bfloat16)
+    lse = torch.empty((batch, 32, 1), device=device, dtype=torch.float32)
+    ops.combine_partials(part_o, part_lse, out, lse)
+    torch.cuda.synchronize()
+    assert ops.library.device_status(device.index) == 0
+    oracle.check_outputs(out.cpu(), lse.cpu(), want_o, want_lse)
+    assert torch.equal(bits(torch.cat([k.cpu() for k, _ in caches], dim=1)), bits(want_k))
+    assert torch.equal(bits(torch.cat([v.cpu() for _, v in caches], dim=1)), bits(want_v))
+    # a shard that holds no visible key reports -inf and contributes nothing
+    assert torch.isinf(part_lse[3].view(batch, 32)[1]).all()
+
+
+def test_argument_checks(ops, gpu_device):
+    q, kcache, vcache, knew, vnew = (t.to(gpu_device) for t in make_case(1, 1, 128))
+    old = torch.zeros(1, dtype=torch.int32, device=gpu_device)
+    out, lse = torch.empty_like(q), torch.empty((1, 32, 1), device=gpu_device)
+    spec = ops.workspace_spec(q, kcache, old, 0, 1, True)
+    ws = [torch.empty(n, device=gpu_device) for n in spec[1:]]
+    with pytest.raises(RuntimeError, match="workspace is too small"):
+        ops.forward_out(q, kcache, vcache, knew, vnew, old, out, lse, ws[0][:1], ws[1], 0, 1, True)
+    with pytest.raises(RuntimeError, match="disjoint"):
+        ops.forward_out(q, kcache, kcache, knew, vnew, old, out, lse, *ws, 0, 1, True)
+    with pytest.raises(RuntimeError, match="old_lengths"):
+        ops.forward_out(q, kcache, vcache, knew, vnew, old.long(), out, lse, *ws, 0, 1, True)
+    with pytest.raises(RuntimeError, match="mapping"):
+        ops.workspace_spec(q, kcache, old, 0, 2, True)
+    with pytest.raises(RuntimeError, match="Contiguous BF16"):
+        ops.workspace_spec(q.float(), kcache, old, 0, 1, True)
+    resources = ops.resources(q, kcache, old, 0, 1, True)
+    assert len(resources) == 34 and resources[12] == 160 and resources[19] >= 1 and resources[0] == spec[0]

@@ -1,0 +1,122 @@
+"""Parity of the tcgen05 causal GQA prefill kernel with the CPU oracle, through the C ABI.
+
+Tolerances: O max-abs error <= 2e-2 (BF16), LSE <= 1e-3 relative. Follows the reference's prefill
+verification (``tilecadence/bench_operator.py:29-43``): both mappings run on the same inputs and
+must agree bit for bit.
+"""
+import pytest
+import torch
+
+from oracle import attention as oracle
+from tilecadence_b200 import cuda_runtime
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops(library):
+    return cuda_runtime.ops_for(library, "prefill")
+
+
+def run_prefill(ops, device, q, k, v, mapping=1, scale=128 ** -0.5):
+    dq, dk, dv = q.to(device), k.to(device), v.to(device)
+    out = torch.full(dq.shape, float("nan"), device=device, dtype=torch.bfloat16)
+    lse = torch.full((q.size(0), q.size(2), q.size(1)), float("nan"), device=device, dtype=torch.float32)
+    empty = torch.empty(0, device=device, dtype=torch.float32)
+    assert ops.workspace_spec(dq, dk, dv, 0, mapping, True) == [1, 0, 0]
+    ops.forward_out(dq, dk, dv, out, lse, empty, empty, 0, mapping, scale, True)
+    torch.cuda.synchronize()
+    assert ops.library.device_status(device.index) == 0
+    return out.cpu(), lse.cpu()
+
+
+def bits(tensor, integer=torch.int16):
+    return tensor.contiguous().view(integer)
+
+
+@pytest.mark.parametrize("batch,tokens", [(1, 128), (1, 256), (1, 193), (4, 384), (1, 1537), (1, 2048)])
+def test_prefill_matches_oracle(ops, gpu_device, batch, tokens):
+    q, k, v = oracle.seeded_normal(2000 + tokens, (batch, tokens, 32, 128), (batch, tokens, 8, 128),
+                                   (batch, tokens, 8, 128))
+    want_o, want_lse = oracle.attention(q, k, v, causal=True)
+    got_o, got_lse = run_prefill(ops, gpu_device, q, k, v)
+    oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+
+
+def test_mappings_agree_bitwise(ops, gpu_device):
+    q, k, v = oracle.seeded_normal(5, (1, 640, 32, 128), (1, 640, 8, 128), (1, 640, 8, 128))
+    o0, l0 = run_prefill(ops, gpu_device, q, k, v, mapping=0)
+    o1, l1 = run_prefill(ops, gpu_device, q, k, v, mapping=1)
+    assert torch.isfinite(o1.float()).all() and torch.isfinite(l1).all()
+    assert torch.equal(bits(o0), bits(o1)) and torch.equal(bits(l0, torch.int32), bits(l1, torch.int32))
+
+
+def test_strided_inputs_and_custom_scale(ops, gpu_device):
+    """Q/K/V views into a packed QKV projection (row stride 48*128) and a non-default scale."""
+    (packed,) = oracle.seeded_normal(6, (1, 512, 48, 128))
+    q, k, v = packed[:, :, :32], packed[:, :, 32:40], packed[:, :, 40:]
+    want_o, want_lse = oracle.attention(q, k, v, causal=True, scale=0.05)
+    device_packed = packed.to(gpu_device)
+    dq, dk, dv = device_packed[:, :, :32], device_packed[:, :, 32:40], device_packed[:, :, 40:]
+    out = torch.empty((1, 512, 32, 128), device=gpu_device, dtype=torch.bfloat16)
+    lse = torch.empty((1, 32, 512), device=gpu_device, dtype=torch.float32)
+    empty = torch.empty(0, device=gpu_device, dtype=torch.float32)
+    ops.forward_out(dq, dk, dv, out, lse, empty, empty, 0, 1, 0.05, True)
+    torch.cuda.synchronize()
+    oracle.check_outputs(out.cpu(), lse.cpu(), want_o, want_lse)
+
+
+def test_head_group_shard(library, gpu_device):
+    """A KV-head-group shard (8 query heads over 2 KV heads) equals the same heads of the full run."""
+    q, k, v = oracle.seeded_normal(7, (1, 256, 32, 128), (1, 256, 8, 128), (1, 256, 8, 128))
+    want_o, want_lse = oracle.attention(q, k, v, causal=True)
+    shard_ops = cuda_runtime.ops_for(library, "prefill", q_heads=8)
+    got_o, got_lse = run_prefill(shard_ops, gpu_device, q[:, :, 8:16].contiguous(), k[:, :, 2:4].contiguous(),
+                                 v[:, :, 2:4].contiguous())
+    oracle.check_outputs(got_o, got_lse, want_o[:, :, 8:16], want_lse[:, 8:16])
+
+
+def test_config2_full_size(ops, gpu_device):
+    """BASELINE config 2: batch 1, 8192 tokens, 32 query / 8 KV heads, seed 1."""
+    q, k, v = oracle.seeded_normal(1, (1, 8192, 32, 128), (1, 8192, 8, 128), (1, 8192, 8, 128))
+    got_o, got_lse = run_prefill(ops, gpu_device, q, k, v)
+    torch.set_num_threads(max(1, torch.get_num_threads()))
+    want_o, want_lse = oracle.attention(q, k, v, causal=True, row_block=512)
+    oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+
+
+def test_long_sequence_rows_against_oracle(ops, gpu_device):
+    """32768 tokens, batch 1: every row's LSE is finite and a sample of rows matches the oracle."""
+    tokens = 32768
+    q, k, v = oracle.seeded_normal(2, (1, tokens, 32, 128), (1, tokens, 8, 128), (1, tokens, 8, 128))
+    got_o, got_lse = run_prefill(ops, gpu_device, q, k, v)
+    assert torch.isfinite(got_lse).all() and torch.isfinite(got_o.float()).all()
+    for r0 in (0, 12345, tokens - 64):
+        rows = slice(r0, r0 + 64)
+        for g in (0, 5):
+            qh = q[0, rows, g * 4:(g + 1) * 4].float().permute(1, 0, 2)
+            scores = (qh @ k[0, :r0 + 64, g].float().T) * 128 ** -0.5
+            cols = torch.arange(r0 + 64)[None, :]
+            scores.masked_fill_(cols > torch.arange(r0, r0 + 64)[:, None], float("-inf"))
+            want_lse = scores.logsumexp(-1)
+            want_o = (scores.softmax(-1) @ v[0, :r0 + 64, g].float()).permute(1, 0, 2)
+            oracle.check_outputs(got_o[0, rows, g * 4:(g + 1) * 4], got_lse[0, g * 4:(g + 1) * 4, rows], want_o, want_lse)
+
+
+def test_argument_checks(ops, gpu_device):
+    q, k, v = (t.to(gpu_device) for t in oracle.seeded_normal(1, (1, 128, 32, 128), (1, 128, 8, 128), (1, 128, 8, 128)))
+    out, lse = torch.empty_like(q), torch.empty((1, 32, 128), device=gpu_device)
+    empty = torch.empty(0, device=gpu_device)
+    with pytest.raises(RuntimeError, match="causal"):
+        ops.forward_out(q, k, v, out, lse, empty, empty, 0, 1, 0.1, False)
+    with pytest.raises(RuntimeError, match="num_splits=0"):
+        ops.workspace_spec(q, k, v, 2, 1, True)
+    with pytest.raises(RuntimeError, match="scale"):
+        ops.forward_out(q, k, v, out, lse, empty, empty, 0, 1, float("nan"), True)
+    with pytest.raises(RuntimeError, match="aliases"):
+        ops.forward_out(q, k, v, q, lse, empty, empty, 0, 1, 0.1, True)
+    with pytest.raises(RuntimeError, match="batch 1 or 4"):
+        ops.workspace_spec(q.expand(2, -1, -1, -1).contiguous(), k.expand(2, -1, -1, -1).contiguous(),
+                           v.expand(2, -1, -1, -1).contiguous(), 0, 1, True)
+    resources = ops.resources(q, k, v, 0, 1, True)
+    assert len(resources) == 46 and resources[12] == 320 and resources[19] == 1

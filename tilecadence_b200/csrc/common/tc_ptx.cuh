@@ -51,16 +51,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait. Each try_wait already blocks for a hardware-defined interval, so the limit
-// corresponds to well over a second before giving up.
-#ifndef TC_WAIT_LIMIT
-#define TC_WAIT_LIMIT (1u << 22)
+// Bounded wait: gives up after TC_WAIT_LIMIT_NS of wall-clock time (read from %globaltimer every
+// few polls) and returns false, so a lost signal ends the kernel with an error status instead of
+// hanging the GPU.
+#ifndef TC_WAIT_LIMIT_NS
+#define TC_WAIT_LIMIT_NS 2000000000ull
 #endif
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    for (uint32_t poll = 1;; ++poll) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((poll & 15u) == 0 && global_timer_ns() - start > TC_WAIT_LIMIT_NS) return false;
     }
-    return false;
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {
