@@ -48,7 +48,7 @@ int tc_device_status(int device, int32_t* status);
  * workspace_spec replaces `workspace_spec(q,k,v,num_splits,mapping,causal) -> int[3]`
  * (tilecadence/cuda/prefill/binding.cpp:12, prefill.cu:106-120): spec = {1, 0, 0}.
  * num_splits must be 0, mapping 0 or 1, causal non-zero, batch 1 or 4, 128 <= tokens <= 32768
- * (prefill.cu:69-74,109-114). q_heads is 32 in the reference; a multiple of 8 up to 32 is accepted
+ * (prefill.cu:69-74,109-114). q_heads is 32 in the reference; a multiple of 4 up to 32 is accepted
  * so that a rank can hold a KV-head-group shard.
  */
 int tc_prefill_workspace_spec(int device, int64_t batch, int64_t tokens, int64_t q_heads, int64_t num_splits,
@@ -60,7 +60,7 @@ int tc_prefill_workspace_spec(int device, int64_t batch, int64_t tokens, int64_t
  * dimension contiguous, 16-byte aligned bases); out contiguous like q; lse contiguous [B,Hq,T].
  * workspace_*_elems must be 0 (single split). mapping 1 stages the per-row LSE of both heads in the
  * released terminal K stage at the planner's offsets; mapping 0 uses a dedicated staging area. Both
- * give bit-identical results. dtype_fp16 = 0 selects BF16 (the reference's only prefill type).
+ * give bit-identical results.
  */
 int tc_prefill_forward_out(int device, void* stream, const void* q, const int64_t q_strides[3], const void* k,
                            const int64_t k_strides[3], const void* v, const int64_t v_strides[3], void* out,
@@ -116,11 +116,12 @@ int tc_decode_partial_out(int device, void* stream, const void* q, void* kcache,
 
 /* LSE-weighted merge of `parts` partial results: the arithmetic of the split combine the reference
  * launches after its decode kernel (decode.cu:131-140): LSE = ln sum_s exp(LSE_s),
- * O = sum_s exp(LSE_s - LSE) O_s. partial_o fp32 [parts, rows, 128], partial_lse fp32
- * [parts, rows]; out BF16 [rows,128], lse fp32 [rows]. Rows with no contribution give O = 0,
- * LSE = +inf. */
+ * O = sum_s exp(LSE_s - LSE) O_s. Part s has its O at partial_o + s*part_stride_o (fp32
+ * [rows,128]) and its LSE at partial_lse + s*part_stride_lse (fp32 [rows]); strides are in
+ * elements, so the parts may sit inside one gathered buffer. out BF16 [rows,128], lse fp32 [rows].
+ * Rows with no contribution give O = 0, LSE = +inf. */
 int tc_combine_partials(int device, void* stream, const float* partial_o, const float* partial_lse, int64_t parts,
-                        int64_t rows, void* out, float* lse);
+                        int64_t rows, int64_t part_stride_o, int64_t part_stride_lse, void* out, float* lse);
 
 /* Replaces `resources(q,kcache,old_lengths,num_splits,mapping,append) -> int[]`
  * (decode.cu:203-229): 12 header values, 8 attributes of the split kernel, 8 of the standalone

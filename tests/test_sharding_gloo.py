@@ -1,0 +1,90 @@
+"""Host logic of the multi-GPU drivers on CPU ranks (gloo, world size 2).
+
+The CUDA operators are replaced by a stand-in that computes the same partials with the CPU
+oracle, so what is under test is the orchestration: shard ownership, which rank appends, the packed
+all-gather layout and the merge order. The product path never uses such a stand-in.
+"""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import attention as oracle
+from tilecadence_b200 import sharding
+
+
+class OracleOps:
+    """Stand-in with the decode operator's interface, backed by the CPU oracle (tests only)."""
+
+    def workspace_spec(self, q, kcache, old_lengths, num_splits, mapping, append):
+        return [1, 0, 0]
+
+    def partial_out(self, q, kcache, vcache, knew, vnew, old_lengths, partial_o, partial_lse, ws_o, ws_lse,
+                    num_splits, mapping, append, kv_shard_start):
+        out, lse, kafter, vafter = oracle.decode_step(q, kcache, vcache, knew, vnew, old_lengths, append=append,
+                                                      shard_start=kv_shard_start, partial=True)
+        kcache.copy_(kafter)
+        vcache.copy_(vafter)
+        partial_o.copy_(out.reshape(partial_o.shape))
+        partial_lse.copy_(lse.reshape(partial_lse.shape))
+
+    def combine_partials(self, partial_o, partial_lse, out, lse):
+        merged, merged_lse = oracle.combine(partial_o, partial_lse)
+        out.copy_(merged.reshape(out.shape).to(out.dtype))
+        lse.copy_(merged_lse.reshape(lse.shape))
+
+
+def free_port():
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]
+
+
+def worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        batch, capacity = 2, 96
+        kcache, vcache, q, knew, vnew = oracle.seeded_normal(21, (batch, capacity, 8, 128), (batch, capacity, 8, 128),
+                                                             (batch, 1, 32, 128), (batch, 1, 8, 128), (batch, 1, 8, 128))
+        old = torch.tensor([70, 3], dtype=torch.int32)
+        want_o, want_lse, want_k, want_v = oracle.decode_step(q, kcache, vcache, knew, vnew, old)
+        start, length = sharding.kv_sequence_shard(rank, world, capacity)
+        kshard, vshard = kcache[:, start:start + length].clone(), vcache[:, start:start + length].clone()
+        driver = sharding.ShardedDecode(OracleOps(), rank, world, batch, capacity, torch.device("cpu"))
+        out = torch.empty((batch, 1, 32, 128), dtype=torch.bfloat16)
+        lse = torch.empty((batch, 32, 1), dtype=torch.float32)
+        driver.step(q, kshard, vshard, knew, vnew, old, out, lse)
+        oracle.check_outputs(out, lse, want_o, want_lse)
+        assert torch.equal(kshard.view(torch.int16), want_k[:, start:start + length].view(torch.int16))
+        assert torch.equal(vshard.view(torch.int16), want_v[:, start:start + length].view(torch.int16))
+        # rank 1 owns row 70 of sequence 0, rank 0 owns row 3 of sequence 1: each appended exactly one row
+        changed = (kshard.view(torch.int16) != kcache[:, start:start + length].view(torch.int16)).any(dim=(2, 3))
+        assert changed.sum().item() == 1 and changed[1 - rank, (70 if rank else 3) - start]
+        # sequence 1 has no visible key on rank 1: its partial LSE is -inf
+        _, gathered_lse = driver.views(driver.gathered)
+        assert torch.isinf(gathered_lse[1].view(batch, 32)[1]).all()
+        results[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_decode_two_ranks():
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(worker, args=(world, free_port(), results), nprocs=world, join=True)
+    assert dict(results) == {0: "ok", 1: "ok"}
+
+
+def test_shard_arithmetic():
+    assert sharding.kv_head_slice(1, 4) == (slice(2, 4), slice(8, 16))
+    assert sharding.kv_head_slice(0, 1) == (slice(0, 8), slice(0, 32))
+    assert sharding.kv_sequence_shard(3, 8, 32768) == (12288, 4096)
+    with pytest.raises(ValueError):
+        sharding.kv_head_slice(0, 3)
+    with pytest.raises(ValueError):
+        sharding.kv_sequence_shard(0, 3, 32768)

@@ -77,12 +77,6 @@ __device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk16) {
     return (chunk16 >> 3) * kHalfBytes + row * 128 + (((chunk16 & 7) ^ (row & 7)) << 4);
 }
 
-// Merge `count` normalised partials (natural-log LSE) for one row / four columns.
-struct Merged {
-    float4 o;
-    float lse;  // -inf when nothing contributed
-};
-
 template <bool kHandoff>
 __global__ void __launch_bounds__(kThreads, AB_DECODE_CTAS_PER_SM)
 decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
@@ -387,19 +381,20 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
 // Standalone merge of `parts` partial results (used after the multi-GPU all-gather).
 __global__ void __launch_bounds__(128) combine_partials_kernel(const float* __restrict__ partial_o,
                                                                const float* __restrict__ partial_lse, int parts,
-                                                               int64_t rows, __nv_bfloat16* __restrict__ out,
+                                                               int64_t rows, int64_t stride_o, int64_t stride_lse,
+                                                               __nv_bfloat16* __restrict__ out,
                                                                float* __restrict__ lse) {
     const int64_t row = int64_t(blockIdx.x) * 4 + (threadIdx.x >> 5);
     const int col4 = threadIdx.x & 31;
     if (row >= rows) return;
     float lse_max = -INFINITY;
-    for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, partial_lse[s * rows + row]);
+    for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, partial_lse[s * stride_lse + row]);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float total = 0.f;
     if (lse_max != -INFINITY) {
         for (int s = 0; s < parts; ++s) {
-            const float part_lse = partial_lse[s * rows + row];
-            const float4 v = reinterpret_cast<const float4*>(partial_o + (s * rows + row) * kDim)[col4];
+            const float part_lse = partial_lse[s * stride_lse + row];
+            const float4 v = reinterpret_cast<const float4*>(partial_o + s * stride_o + row * kDim)[col4];
             const bool used = part_lse != -INFINITY;
             const float weight = used ? __expf(part_lse - lse_max) : 0.f;
             total += weight;
@@ -610,19 +605,21 @@ int tc_decode_partial_out(int device, void* stream, const void* q, void* kcache,
 }
 
 int tc_combine_partials(int device, void* stream, const float* partial_o, const float* partial_lse, int64_t parts,
-                        int64_t rows, void* out, float* lse) {
+                        int64_t rows, int64_t part_stride_o, int64_t part_stride_lse, void* out, float* lse) {
     tc::DeviceInfo info;
     int status = tc::require_sm100(device, &info);
     if (status != TC_OK) return status;
     TC_REQUIRE(partial_o && partial_lse && out && lse, "null tensor pointer");
     TC_REQUIRE(parts >= 1 && parts <= 1024 && rows >= 1 && rows <= (int64_t(1) << 24), "parts or rows out of range");
-    TC_REQUIRE(reinterpret_cast<uintptr_t>(partial_o) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0,
-               "16-byte aligned partial O and 8-byte aligned O required");
+    TC_REQUIRE(reinterpret_cast<uintptr_t>(partial_o) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0 &&
+                   part_stride_o % 4 == 0,
+               "16-byte aligned partial O (base and part stride) and 8-byte aligned O required");
+    TC_REQUIRE(part_stride_o >= rows * kDim && part_stride_lse >= rows, "part strides smaller than one part");
     tc::DeviceGuard guard(device);
     TC_CUDA(guard.status);
     const unsigned blocks = unsigned((rows + 3) / 4);
     combine_partials_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        partial_o, partial_lse, int(parts), rows, static_cast<__nv_bfloat16*>(out), lse);
+        partial_o, partial_lse, int(parts), rows, part_stride_o, part_stride_lse, static_cast<__nv_bfloat16*>(out), lse);
     TC_CUDA(cudaGetLastError());
     return TC_OK;
 }

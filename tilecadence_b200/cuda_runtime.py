@@ -178,7 +178,7 @@ class Library:
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, ctypes.c_int64)),
         "tc_combine_partials": (ctypes.c_int, (ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
-                                               ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p)),
+                                               *[ctypes.c_int64] * 4, ctypes.c_void_p, ctypes.c_void_p)),
         "tc_decode_resources": (ctypes.c_int, (ctypes.c_int, *[ctypes.c_int64] * 5, ctypes.c_int,
                                                ctypes.POINTER(ctypes.c_int64), ctypes.c_int64,
                                                ctypes.POINTER(ctypes.c_int64))),
@@ -389,18 +389,22 @@ class DecodeOps:
             int(kv_shard_start))
 
     def combine_partials(self, partial_o, partial_lse, out, lse):
+        """Merge partial_o [parts, rows, 128] / partial_lse [parts, rows] (fp32; the part dimension may be
+        strided, e.g. views into one gathered buffer) into out BF16 [rows*128] and lse FP32 [rows]."""
         import torch
 
-        parts = partial_o.size(0)
-        rows = partial_lse.numel() // parts
-        _require(partial_o.is_cuda and partial_o.dtype == torch.float32 and partial_o.is_contiguous()
-                 and partial_lse.dtype == torch.float32 and partial_lse.is_contiguous()
-                 and partial_o.numel() == parts * rows * 128, "partials must be contiguous FP32 [parts,rows,128] / [parts,rows]")
+        parts, rows = partial_lse.size(0), partial_lse[0].numel()
+        _require(partial_o.is_cuda and partial_o.dtype == torch.float32 and partial_lse.dtype == torch.float32
+                 and partial_o.size(0) == parts and partial_o[0].numel() == rows * 128
+                 and partial_o[0].is_contiguous() and partial_lse[0].is_contiguous(),
+                 "partials must be FP32 [parts,rows,128] / [parts,rows] with contiguous parts")
         _require(out.dtype == torch.bfloat16 and out.is_contiguous() and out.numel() == rows * 128
                  and lse.dtype == torch.float32 and lse.is_contiguous() and lse.numel() == rows,
                  "combined O must be BF16[rows,128] and LSE FP32[rows]")
+        stride_o = partial_o.stride(0) if parts > 1 else rows * 128
+        stride_lse = partial_lse.stride(0) if parts > 1 else rows
         self.library.call("tc_combine_partials", partial_o.device.index, _stream(partial_o), _pointer(partial_o),
-                          _pointer(partial_lse), parts, rows, _pointer(out), _pointer(lse))
+                          _pointer(partial_lse), parts, rows, stride_o, stride_lse, _pointer(out), _pointer(lse))
 
     def resources(self, q, kcache, old_lengths, num_splits, mapping, append):
         self._check_q_cache_lengths(q, kcache, old_lengths)
