@@ -2,8 +2,8 @@
 // mbarrier, TMA (cp.async.bulk[.tensor]), tcgen05 (TMEM alloc, MMA, ld/st, commit),
 // ldmatrix / mma.sync for the HBM-bound decode path, and packed conversions.
 //
-// Every wait is bounded: a spin that exceeds its iteration limit returns false so the
-// caller can record an error status and leave the kernel cleanly instead of hanging.
+// Every wait is bounded: a spin that exceeds its time limit returns false so the caller can
+// record an error status and leave the kernel cleanly instead of hanging.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -51,6 +51,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking poll of a phase.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after TC_WAIT_LIMIT_NS of wall-clock time (read from %globaltimer every
 // few polls) and returns false, so a lost signal ends the kernel with an error status instead of
 // hanging the GPU.
@@ -69,6 +81,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((poll & 15u) == 0 && global_timer_ns() - start > TC_WAIT_LIMIT_NS) return false;
     }
+}
+
+// Programmatic dependent launch (no-ops when the kernel was launched without the attribute).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ int atomic_add_acq_rel(int* address, int value) {
+    int old;
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(address), "r"(value) : "memory");
+    return old;
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

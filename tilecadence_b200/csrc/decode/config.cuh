@@ -5,9 +5,13 @@
 #define V10_FAMILY_CODE 7901
 #define AB_DECODE_WARPS 4
 #define AB_DECODE_BLOCK_N 64
+#ifndef AB_DECODE_STAGES
 #define AB_DECODE_STAGES 3
+#endif
 #define AB_DECODE_STAGE_BYTES 32768
 #define AB_DECODE_TERMINAL_V_BYTES 16384
+#ifndef AB_DECODE_CTAS_PER_SM
 #define AB_DECODE_CTAS_PER_SM 2
+#endif
 #define AB_DECODE_O_OFFSET_BYTES 0
 #define AB_DECODE_LSE_OFFSET_BYTES 2048

@@ -37,6 +37,7 @@ constexpr int kStagingBytes = 2304;  // dedicated O/LSE staging when the handoff
 constexpr int kBarrierBytes = 256;
 
 static_assert(kStageBytes == 2 * kVBytes, "a stage holds one V tile followed by one K tile");
+static_assert(kMaxSplits % 32 == 0 && kGroup * kMaxSplits * 4 <= kVBytes, "split weights fit the terminal K stage");
 static_assert(kTileN == 16 * kConsumerWarps, "each consumer warp owns 16 keys of a tile");
 static_assert(AB_DECODE_TERMINAL_V_BYTES == kVBytes, "planner donor size must match the V tile");
 static_assert(AB_DECODE_O_OFFSET_BYTES % 16 == 0 && AB_DECODE_LSE_OFFSET_BYTES % 16 == 0, "vector export");
@@ -94,6 +95,22 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q_heads = p.kv_heads * kGroup;
 
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], kConsumerWarps);
+        }
+        tc::mbar_fence_init();
+        tc::tma_prefetch_desc(&kmap);
+        tc::tma_prefetch_desc(&vmap);
+    }
+    // Programmatic dependent launch: everything above touches only this CTA's shared memory and
+    // kernel parameters, so it may overlap the tail of the preceding kernel in the stream. Nothing
+    // below (lengths, caches, tickets) is read before that kernel has completed. The next kernel
+    // may start its own preamble as soon as every CTA of this grid is resident.
+    tc::grid_dependency_wait();
+    tc::grid_launch_dependents();
+
     // Device-side lengths: no host read. Values outside the contract are clamped so that no
     // address leaves the cache.
     int64_t old_len = p.old_lengths[b];
@@ -111,20 +128,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     const int tile_end = int((int64_t(split + 1) * tiles) / p.splits);
     const int n_tiles = tile_end - tile_begin;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            tc::mbar_init(&full[s], 1);
-            tc::mbar_init(&empty[s], kConsumerWarps);
-        }
-        tc::mbar_fence_init();
-    }
     __syncthreads();
 
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------------ producer warp
         if (lane == 0 && n_tiles > 0) {
-            tc::tma_prefetch_desc(&kmap);
-            tc::tma_prefetch_desc(&vmap);
             const uint64_t policy = tc::policy_evict_first();
             for (int it = 0; it < n_tiles; ++it) {
                 const int stage = (n_tiles - 1 - it) % kStages;  // the last tile always lands in stage 0
@@ -324,36 +332,65 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
         reinterpret_cast<uint4*>(p.ws_o + slot * (kGroup * kDim))[tid] = reinterpret_cast<const uint4*>(stage_o)[tid];
         if (tid == 0)
             *reinterpret_cast<uint4*>(p.ws_lse + slot * kGroup) = *reinterpret_cast<const uint4*>(stage_lse);
-        __threadfence();
+        // The barrier orders every thread's partial stores before thread 0's release; the last
+        // arriver's acquire, followed by the second barrier, orders them before the merge loads.
         consumer_barrier();
-        if (tid == 0) {
-            const int ticket = atomicAdd(p.tickets + head_slot, 1);
-            *flag = ticket == p.splits - 1;
-        }
+        if (tid == 0) *flag = tc::atomic_add_acq_rel(p.tickets + head_slot, 1) == p.splits - 1;
         consumer_barrier();
         if (!*flag) return;
-        __threadfence();
-        // Last CTA of this (batch, KV head): LSE-weighted merge of every split's partial.
+        // Last CTA of this (batch, KV head): LSE-weighted merge of every split's partial. Warp w owns
+        // output row w: its lanes first fetch that row's split LSEs together (one L2 round trip),
+        // reduce them with shuffles and park the weights in the released terminal K stage; then
+        // each lane accumulates its four columns over the splits, with the first batch of partial-O
+        // loads already in flight beside the LSE loads.
         const int64_t stride_lse = int64_t(p.batch) * p.kv_heads * kGroup;
         const float* lse_base = p.ws_lse + head_slot * kGroup + row;
         const float4* o_base = reinterpret_cast<const float4*>(p.ws_o + head_slot * (kGroup * kDim) + row * kDim) + col4;
         const int64_t stride_o4 = stride_lse * (kDim / 4);
+        float* weights = reinterpret_cast<float*>(terminal_k) + row * kMaxSplits;
+        constexpr int kBatch = 20;  // partial-O loads kept in flight per lane
+        float part_lse[kMaxSplits / 32];
+        float4 v[kBatch];
+#pragma unroll
+        for (int i = 0; i < kMaxSplits / 32; ++i) {
+            const int s = col4 + 32 * i;
+            part_lse[i] = s < p.splits ? __ldcg(lse_base + s * stride_lse) : -INFINITY;
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u)  // first batch goes out with the LSE loads: one L2 round trip
+            if (u < p.splits) v[u] = __ldcg(o_base + u * stride_o4);
         float lse_max = -INFINITY;
-        for (int s = 0; s < p.splits; ++s) lse_max = fmaxf(lse_max, __ldcg(lse_base + s * stride_lse));
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < kMaxSplits / 32; ++i) lse_max = fmaxf(lse_max, part_lse[i]);
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1)
+            lse_max = fmaxf(lse_max, __shfl_xor_sync(0xffffffffu, lse_max, offset));
         float total = 0.f;
-        if (lse_max != -INFINITY) {
-#pragma unroll 8
-            for (int s = 0; s < p.splits; ++s) {
-                const float part_lse = __ldcg(lse_base + s * stride_lse);
-                const float4 v = __ldcg(o_base + s * stride_o4);
-                const bool used = part_lse != -INFINITY;
-                const float weight = used ? __expf(part_lse - lse_max) : 0.f;
-                total += weight;
-                acc.x += used ? weight * v.x : 0.f;
-                acc.y += used ? weight * v.y : 0.f;
-                acc.z += used ? weight * v.z : 0.f;
-                acc.w += used ? weight * v.w : 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxSplits / 32; ++i) {
+            const float weight = part_lse[i] == -INFINITY ? 0.f : __expf(part_lse[i] - lse_max);
+            weights[col4 + 32 * i] = weight;
+            total += weight;
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) total += __shfl_xor_sync(0xffffffffu, total, offset);
+        __syncwarp();
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < p.splits; s0 += kBatch) {
+            if (s0 > 0) {
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u)
+                    if (s0 + u < p.splits) v[u] = __ldcg(o_base + (s0 + u) * stride_o4);
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const float w = s0 + u < p.splits ? weights[s0 + u] : 0.f;
+                if (w > 0.f) {  // a split that saw no key may hold anything: never multiply it
+                    acc.x = fmaf(w, v[u].x, acc.x);
+                    acc.y = fmaf(w, v[u].y, acc.y);
+                    acc.z = fmaf(w, v[u].z, acc.z);
+                    acc.w = fmaf(w, v[u].w, acc.w);
+                }
             }
         }
         const float inv = total > 0.f ? 1.f / total : 0.f;
@@ -414,8 +451,9 @@ __global__ void __launch_bounds__(128) combine_partials_kernel(const float* __re
 
 // ------------------------------------------------------------------------------- host side
 int auto_splits(const tc::DeviceInfo& info, int64_t batch, int64_t capacity, int64_t kv_heads) {
-    // Enough CTAs to fill every SM at the kernel's residency, never more splits than tiles.
-    const int64_t slots = int64_t(info.sms) * AB_DECODE_CTAS_PER_SM;
+    // About one CTA per SM (the second resident CTA slot is left to the next launch's preamble and to
+    // uneven split lengths); the merge tail grows with the split count, so more is not better.
+    const int64_t slots = int64_t(info.sms);
     int64_t splits = slots / (batch * kv_heads);
     const int64_t tiles = (capacity + kTileN - 1) / kTileN;
     if (splits > tiles) splits = tiles;
@@ -451,9 +489,17 @@ int launch(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams&
         TC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared));
         configured_device = device;
     }
-    const dim3 grid(p.splits, p.kv_heads, p.batch);
-    kernel<<<grid, kThreads, shared, stream>>>(kmap, vmap, p);
-    TC_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(p.splits, p.kv_heads, p.batch);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    TC_CUDA(cudaLaunchKernelEx(&config, kernel, kmap, vmap, p));
     return TC_OK;
 }
 

@@ -13,9 +13,13 @@
 //   warps 0-3  softmax for head 0 (one query row per thread, TMEM lane = row)
 //   warps 4-7  softmax for head 1
 //   warp  8    TMA producer: Q once, then a 2-stage K ring and a 2-stage V ring (128-byte swizzle)
-//   warp  9    tcgen05.mma issuer (one elected thread) and TMEM owner
-// The issue order QK0 QK1 | PV0 QK0' | PV1 QK1' ... keeps the tensor pipe busy with one head
-// while the other head's softmax runs. Key tiles go from the diagonal down to 0, the ring index is
+//   warps 9,10 tcgen05.mma issuers, one elected thread per head (warp 9 also owns TMEM)
+//   warp  11   idle: it completes the third warpgroup so that it can release registers
+//              (setmaxnreg) to the softmax warpgroups
+// Per head the issue order is PV(first 64 keys) | PV(last 64 keys) | next QK; each head has its
+// own issuer, so the tensor pipe works on one head while the other head's softmax runs. The
+// softmax is bound by the exponential unit (16 results per clock per SM against 8192 MMA flops),
+// so part of the 2^x evaluations run as a cubic polynomial on the packed-FP32 FMA pipes. Key tiles go from the diagonal down to 0, the ring index is
 // chosen so that the final tile always uses stage 0: that stage is the "terminal K" donor whose
 // bytes receive the two 512-byte LSE arrays in the epilogue.
 #include "config.cuh"
@@ -40,9 +44,13 @@ constexpr int kBarrierOffset = kVOffset + kStages * kTileBytes;
 constexpr int kBarrierBytes = 256;
 constexpr int kStagingBytes = 1024;           // dedicated LSE staging when the handoff is disabled
 constexpr int kSoftmaxThreads = 128;
-constexpr int kThreads = 2 * kSoftmaxThreads + 64;
+constexpr int kThreads = 3 * kSoftmaxThreads;   // two softmax warpgroups + one data/MMA warpgroup
+constexpr int kSoftmaxRegisters = 216, kDataRegisters = 72;  // 256*216 + 128*72 = 64512 <= 65536
+constexpr bool kSplitP = PREFILL_SPLIT_P != 0;  // signal the MMA issuer after each 64-key half of P
+constexpr int kEmulatedPairsPer8 = PREFILL_EXP_FMA_PAIRS_PER_8;  // of every 8 key pairs, how many use the FMA-pipe 2^x
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr uint32_t kTmemColumns = 512;
+constexpr uint32_t kSColumn = 0, kPColumn = 128, kOColumn = 256;  // S (shared) | P0 P1 | O0 O1
 constexpr float kRescaleThreshold = 8.f;      // log2 units: P stays below 2^8
 
 static_assert(kBlockM == 128 && kBlockN == 128 && PREFILL_GROUP_HEADS == 2 && kStages == 2, "fixed tile schedule");
@@ -62,7 +70,7 @@ constexpr int shared_bytes(bool handoff) { return 1024 + kBarrierOffset + kBarri
 struct Barriers {
     uint64_t q_full;
     uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-    uint64_t s_full[2], p_full[2], o_done[2];
+    uint64_t s_full[2], s_free[2], p_half[2][2], o_done[2], turn[2];
     uint32_t tmem_base;
     int32_t abort;
 };
@@ -77,6 +85,30 @@ struct PrefillParams {
 
 __device__ __forceinline__ void wg_barrier(int head) {
     asm volatile("bar.sync %0, %1;" ::"r"(head + 1), "n"(kSoftmaxThreads) : "memory");
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// 2^x for a pair of values on the FMA pipes instead of the exponential unit: split x into a
+// rounded integer n (magic-number add) and r = x - n in [-0.5, 0.5], evaluate a cubic fit of 2^r
+// (relative error 7.5e-5, far below the BF16 rounding P receives), and add n to the exponent
+// field. x must be >= -125 so the exponent cannot wrap.
+__device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
+    const float2 magic = make_float2(12582912.f, 12582912.f);  // 1.5 * 2^23
+    const float2 t = __fadd2_rn(x, magic);
+    const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+    const float2 r = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+    float2 poly = __ffma2_rn(r, make_float2(0.055171460f, 0.055171460f), make_float2(0.24261086f, 0.24261086f));
+    poly = __ffma2_rn(poly, r, make_float2(0.69326097f, 0.69326097f));
+    poly = __ffma2_rn(poly, r, make_float2(0.99992812f, 0.99992812f));
+    float2 result;
+    result.x = __uint_as_float(__float_as_uint(poly.x) + (__float_as_uint(t.x) << 23));
+    result.y = __uint_as_float(__float_as_uint(poly.y) + (__float_as_uint(t.y) << 23));
+    return result;
 }
 
 template <bool kHandoff>
@@ -105,14 +137,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         tc::mbar_init(&bars->q_full, 1);
         for (int s = 0; s < kStages; ++s) {
             tc::mbar_init(&bars->k_full[s], 1);
-            tc::mbar_init(&bars->k_empty[s], 1);
+            tc::mbar_init(&bars->k_empty[s], 2);  // one arrival per head's MMA issuer
             tc::mbar_init(&bars->v_full[s], 1);
-            tc::mbar_init(&bars->v_empty[s], 1);
+            tc::mbar_init(&bars->v_empty[s], 2);
         }
         for (int h = 0; h < 2; ++h) {
             tc::mbar_init(&bars->s_full[h], 1);
-            tc::mbar_init(&bars->p_full[h], kSoftmaxThreads);
+            tc::mbar_init(&bars->s_free[h], kSoftmaxThreads);
+            tc::mbar_init(&bars->p_half[h][0], kSoftmaxThreads);
+            tc::mbar_init(&bars->p_half[h][1], kSoftmaxThreads);
             tc::mbar_init(&bars->o_done[h], 1);
+            tc::mbar_init(&bars->turn[h], kSoftmaxThreads);
         }
         bars->abort = 0;
         tc::mbar_fence_init();
@@ -126,6 +161,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     tc::tc_fence_after_sync();
     const uint32_t tmem = bars->tmem_base;
 
+    // The third warpgroup only moves data and issues MMAs: it hands most of its registers to the
+    // two softmax warpgroups, which keep a whole 128-column score row per thread. Each role's code
+    // sits under its own setmaxnreg so that the register allocator sees the right budget.
+    if (warp >= 2 * (kSoftmaxThreads / 32)) {
+#if PREFILL_SETMAXNREG
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kDataRegisters));
+#endif
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -155,80 +197,91 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 tc::tma_load_4d(vdst + kHalfBytes, &vmap, &bars->v_full[stage], 64, kvh, n0, b, keep);
             }
         }
-    } else if (warp == kMmaWarp) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+        // ------------------------------------------------------------------ MMA issuers (one per head)
         if (lane == 0) {
+            const int h = warp - kMmaWarp;
             constexpr uint32_t idesc_qk = tc::umma_idesc(128, 128, 1, 0, 0);
             constexpr uint32_t idesc_pv = tc::umma_idesc(128, 128, 1, 0, 1);
-            const uint32_t q_addr = tc::smem_u32(smem + kQOffset);
+            const uint32_t q_addr = tc::smem_u32(smem + kQOffset) + h * kTileBytes;
             const uint32_t k_addr = tc::smem_u32(smem + kKOffset);
             const uint32_t v_addr = tc::smem_u32(smem + kVOffset);
-            bool ok = true;
-            // S_h = Q_h K^T: both operands K-major, 8 steps of 16 along D (4 per 64-element half).
-            auto issue_qk = [&](int h, int stage) {
+            const uint32_t s_col = tmem + kSColumn, p_col = tmem + kPColumn + uint32_t(h) * 64;
+            const uint32_t o_col = tmem + kOColumn + uint32_t(h) * 128;
+            auto stage_of = [&](int it) { return (n_tiles - 1 - it) % kStages; };
+            auto parity_of = [&](int it) { return uint32_t(it / kStages) & 1; };
+            // S = Q_h K^T into the shared score buffer: both operands K-major, 8 steps of 16 along D
+            // (4 per 64-element half).
+            auto issue_qk = [&](int it) {
+                const uint32_t kb = k_addr + stage_of(it) * kTileBytes;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint32_t off = uint32_t(ks >> 2) * kHalfBytes + uint32_t(ks & 3) * 32;
-                    tc::umma_ss(tmem + uint32_t(h) * 128,
-                                tc::umma_desc_sw128(q_addr + h * kTileBytes + off, 16, 1024),
-                                tc::umma_desc_sw128(k_addr + stage * kTileBytes + off, 16, 1024), idesc_qk, ks > 0);
+                    tc::umma_ss(s_col, tc::umma_desc_sw128(q_addr + off, 16, 1024),
+                                tc::umma_desc_sw128(kb + off, 16, 1024), idesc_qk, ks > 0);
                 }
                 tc::umma_commit(&bars->s_full[h]);
+                tc::umma_commit(&bars->k_empty[stage_of(it)]);  // second arrival comes from the other head
             };
-            // O_h += P_h V: P from TMEM (8 columns per 16 keys), V MN-major (row = key, 128 bytes per
-            // 64 d; the two d halves are 16 KiB apart, 8-key groups 1 KiB apart).
-            auto issue_pv = [&](int h, int stage, bool first) {
+            // O_h += P_h V for one half (64 keys) of the tile: P from TMEM (8 columns per 16 keys), V
+            // MN-major (row = key, 128 bytes per 64 d; the d halves 16 KiB apart, 8-key groups 1 KiB).
+            auto issue_pv_half = [&](int it, int half) {
+                const uint32_t vb = v_addr + stage_of(it) * kTileBytes;
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    tc::umma_ts(tmem + 256 + uint32_t(h) * 128, tmem + uint32_t(h) * 128 + uint32_t(ks) * 8,
-                                tc::umma_desc_sw128(v_addr + stage * kTileBytes + ks * 2048, kHalfBytes, 1024),
-                                idesc_pv, !(first && ks == 0));
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    const int ks = half * 4 + k4;
+                    tc::umma_ts(o_col, p_col + uint32_t(ks) * 8, tc::umma_desc_sw128(vb + ks * 2048, kHalfBytes, 1024),
+                                idesc_pv, !(it == 0 && ks == 0));
                 }
+            };
+            auto issue_pv = [&](int it) {
+                if (!tc::mbar_wait(&bars->v_full[stage_of(it)], parity_of(it))) return false;
+                if (!tc::mbar_wait(&bars->p_half[h][0], uint32_t(it) & 1)) return false;
+                tc::tc_fence_after_sync();
+                issue_pv_half(it, 0);
+                if (!tc::mbar_wait(&bars->p_half[h][1], uint32_t(it) & 1)) return false;
+                tc::tc_fence_after_sync();
+                issue_pv_half(it, 1);
                 tc::umma_commit(&bars->o_done[h]);
+                tc::umma_commit(&bars->v_empty[stage_of(it)]);
+                return true;
             };
-            ok = tc::mbar_wait(&bars->q_full, 0);
-            if (ok) {
-                const int stage = (n_tiles - 1) % kStages;
-                ok = tc::mbar_wait(&bars->k_full[stage], 0);
-                if (ok) {
-                    tc::tc_fence_after_sync();
-                    issue_qk(0, stage);
-                    issue_qk(1, stage);
-                    tc::umma_commit(&bars->k_empty[stage]);
-                }
-            }
+            // The score buffer is used by the heads in strict alternation (0,1,0,1,...): a score MMA
+            // may overwrite it once the other head's softmax warpgroup has pulled its tile into
+            // registers. Because P has its own columns, the score MMA of tile it+1 does not wait for
+            // PV of tile it, so each head's next S is ready long before its warpgroup comes back.
+            bool ok = tc::mbar_wait(&bars->q_full, 0);
             for (int it = 0; ok && it < n_tiles; ++it) {
-                const int stage = (n_tiles - 1 - it) % kStages;
-                const uint32_t parity = uint32_t(it / kStages) & 1;
-                const bool more = it + 1 < n_tiles;
-                const int next_stage = (n_tiles - 2 - it) % kStages;
-                const uint32_t next_parity = uint32_t((it + 1) / kStages) & 1;
-                if (!(ok = tc::mbar_wait(&bars->v_full[stage], parity))) break;
-                if (more && !(ok = tc::mbar_wait(&bars->k_full[next_stage], next_parity))) break;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    if (!(ok = tc::mbar_wait(&bars->p_full[h], uint32_t(it) & 1))) break;
-                    tc::tc_fence_after_sync();
-                    issue_pv(h, stage, it == 0);
-                    if (more) issue_qk(h, next_stage);
+                if (!(ok = tc::mbar_wait(&bars->k_full[stage_of(it)], parity_of(it)))) break;
+                if (h == 0) {
+                    if (it > 0 && !(ok = tc::mbar_wait(&bars->s_free[1], uint32_t(it - 1) & 1))) break;
+                } else {
+                    if (!(ok = tc::mbar_wait(&bars->s_free[0], uint32_t(it) & 1))) break;
                 }
-                if (!ok) break;
-                tc::umma_commit(&bars->v_empty[stage]);
-                if (more) tc::umma_commit(&bars->k_empty[next_stage]);
+                tc::tc_fence_after_sync();
+                issue_qk(it);
+                if (it > 0 && !(ok = issue_pv(it - 1))) break;
             }
+            if (ok) ok = issue_pv(n_tiles - 1);
             if (!ok) {
                 atomicCAS(p.status, 0, 13);
                 bars->abort = 1;
             }
         }
+    }
     } else {
+#if PREFILL_SETMAXNREG
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegisters));
+#endif
         // ------------------------------------------------------------------ softmax warpgroups
         const int h = warp >> 2;                        // head slot
         const int row = threadIdx.x & (kSoftmaxThreads - 1);
         const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
-        const uint32_t s_tmem = tmem + lane_field + uint32_t(h) * 128;
-        const uint32_t o_tmem = tmem + lane_field + 256 + uint32_t(h) * 128;
+        const uint32_t s_tmem = tmem + lane_field + kSColumn;
+        const uint32_t p_tmem = tmem + lane_field + kPColumn + uint32_t(h) * 64;
+        const uint32_t o_tmem = tmem + lane_field + kOColumn + uint32_t(h) * 128;
         const int head = head0 + h;
+        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
 
@@ -239,19 +292,33 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
 #pragma unroll
             for (int c = 0; c < 4; ++c) tc::tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
             tc::tmem_wait_ld();
+            tc::tc_fence_before_sync();
+            tc::mbar_arrive(&bars->s_free[h]);  // the score buffer may be overwritten by the other head
             if (it == 0) {
                 // Diagonal tile: key column j is visible to query row i only if j <= i.
 #pragma unroll
                 for (int j = 0; j < 128; ++j) s[j] = j > row ? -INFINITY : s[j];
             }
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            float mx[4];
+#if PREFILL_MAX3
 #pragma unroll
-            for (int j = 0; j < 128; j += 4) {
-                mx[0] = fmaxf(mx[0], s[j]);
-                mx[1] = fmaxf(mx[1], s[j + 1]);
-                mx[2] = fmaxf(mx[2], s[j + 2]);
-                mx[3] = fmaxf(mx[3], s[j + 3]);
+            for (int q = 0; q < 4; ++q) mx[q] = max3(s[q * 32], s[q * 32 + 1], s[q * 32 + 2]);
+#pragma unroll
+            for (int j = 3; j + 1 < 32; j += 2) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) mx[q] = max3(mx[q], s[q * 32 + j], s[q * 32 + j + 1]);
             }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) mx[q] = fmaxf(mx[q], s[q * 32 + 31]);
+#else
+#pragma unroll
+            for (int q = 0; q < 4; ++q) mx[q] = s[q * 32];
+#pragma unroll
+            for (int j = 1; j < 32; ++j) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) mx[q] = fmaxf(mx[q], s[q * 32 + j]);
+            }
+#endif
             const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
             if (it == 0) {
                 m_used = tile_max;  // finite: column `row` of the diagonal tile is always visible
@@ -261,9 +328,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 // needs it (the TMEM accesses are warp-collective).
                 const float m_new = fmaxf(m_used, tile_max);
                 const bool grow = (m_new - m_used) * p.scale_log2 > kRescaleThreshold;
+                // PV of the previous tile must have finished before its P columns are overwritten
+                // (and before O may be rescaled); it was issued long ago, so this rarely waits.
+                if (!(ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1))) break;
+                tc::tc_fence_after_sync();
                 if (__any_sync(0xffffffffu, grow)) {
-                    if (!(ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1))) break;
-                    tc::tc_fence_after_sync();
                     const float m_target = grow ? m_new : m_used;
                     const float alpha = tc::fast_exp2((m_used - m_target) * p.scale_log2);
 #pragma unroll
@@ -280,26 +349,65 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     m_used = m_target;
                 }
             }
-            const float bias = m_used * p.scale_log2;
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t packed[64];
-#pragma unroll
-            for (int j = 0; j < 128; j += 4) {
-                const float p0 = tc::fast_exp2(fmaf(s[j], p.scale_log2, -bias));
-                const float p1 = tc::fast_exp2(fmaf(s[j + 1], p.scale_log2, -bias));
-                const float p2 = tc::fast_exp2(fmaf(s[j + 2], p.scale_log2, -bias));
-                const float p3 = tc::fast_exp2(fmaf(s[j + 3], p.scale_log2, -bias));
-                sum[0] += p0; sum[1] += p1; sum[2] += p2; sum[3] += p3;
-                packed[j / 2] = tc::pack_bf16x2(p0, p1);
-                packed[j / 2 + 1] = tc::pack_bf16x2(p2, p3);
+#if PREFILL_PINGPONG
+            // The exponential unit is the scarcest resource, so the two heads take turns at it: while
+            // one warpgroup exponentiates, the other head's P is being consumed by the tensor pipe
+            // and its next S tile is produced. Head 0 goes first on every tile.
+            if (h == 1 || it > 0) {
+                if (!(ok = tc::mbar_wait(&bars->turn[h], uint32_t(h == 1 ? it : it - 1) & 1))) break;
             }
-            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-            // P overwrites the first 64 columns of this head's S block.
-            tc::tmem_st32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&packed[0]));
-            tc::tmem_st32(s_tmem + 32, *reinterpret_cast<uint32_t(*)[32]>(&packed[32]));
+#endif
+            const float neg_bias = -m_used * p.scale_log2;
+            const float2 bias2 = make_float2(neg_bias, neg_bias);
+            float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            // Four chunks of 32 keys. Each chunk: x = s*scale - bias on packed pairs, 2^x partly on the
+            // exponential unit and partly on the FMA pipes, BF16 pack, store over the S columns.
+            // Two mbarriers tell the MMA warp when each 64-key half of P is complete.
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+#if PREFILL_PACKED_MATH
+                    float2 x = __ffma2_rn(make_float2(s[c * 32 + j], s[c * 32 + j + 1]), scale2, bias2);
+#else
+                    float2 x = make_float2(fmaf(s[c * 32 + j], p.scale_log2, neg_bias), fmaf(s[c * 32 + j + 1], p.scale_log2, neg_bias));
+#endif
+                    float2 e;
+                    if ((j >> 1) % 8 < kEmulatedPairsPer8) {
+                        x.x = fmaxf(x.x, -125.f);
+                        x.y = fmaxf(x.y, -125.f);
+                        e = exp2_pair_fma(x);
+                    } else {
+                        e.x = tc::fast_exp2(x.x);
+                        e.y = tc::fast_exp2(x.y);
+                    }
+#if PREFILL_PACKED_MATH
+                    sum2[(j >> 1) & 1] = __fadd2_rn(sum2[(j >> 1) & 1], e);
+#else
+                    sum2[(j >> 1) & 1].x += e.x;
+                    sum2[(j >> 1) & 1].y += e.y;
+#endif
+                    packed[j >> 1] = tc::pack_bf16x2(e.x, e.y);
+                }
+                if (c == 3) {
+#if PREFILL_PINGPONG
+                    tc::mbar_arrive(&bars->turn[1 - h]);  // all exponentials issued: the other head may start
+#endif
+                }
+                if (kSplitP && c == 2) {
+                    // Chunks 0 and 1 were stored a whole chunk of arithmetic ago, so this wait is short.
+                    tc::tmem_wait_st();
+                    tc::tc_fence_before_sync();
+                    tc::mbar_arrive(&bars->p_half[h][0]);
+                }
+                tc::tmem_st16(p_tmem + c * 16, packed);
+            }
             tc::tmem_wait_st();
             tc::tc_fence_before_sync();
-            tc::mbar_arrive(&bars->p_full[h]);
+            if (!kSplitP) tc::mbar_arrive(&bars->p_half[h][0]);
+            tc::mbar_arrive(&bars->p_half[h][1]);
+            l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
         }
 
         // ------------------------------------------------------------------ epilogue
