@@ -390,11 +390,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
 #endif
                     packed[j >> 1] = tc::pack_bf16x2(e.x, e.y);
                 }
-                if (c == 3) {
 #if PREFILL_PINGPONG
-                    tc::mbar_arrive(&bars->turn[1 - h]);  // all exponentials issued: the other head may start
+                // Hand the exponential unit over a little before this head's last exponentials drain:
+                // the other warpgroup needs about a hundred cycles to wake up.
+                if (c == PREFILL_TURN_CHUNK) tc::mbar_arrive(&bars->turn[1 - h]);
 #endif
-                }
                 if (kSplitP && c == 2) {
                     // Chunks 0 and 1 were stored a whole chunk of arithmetic ago, so this wait is short.
                     tc::tmem_wait_st();
