@@ -103,6 +103,25 @@ int tc_decode_forward_out(int device, void* stream, const void* q, void* kcache,
                           int64_t workspace_lse_elems, int64_t batch, int64_t capacity, int64_t kv_heads,
                           int64_t num_splits, int64_t mapping, int append);
 
+/* Allocation-free decode step. It has no counterpart in the reference; it exists for callers that
+ * are not allowed to allocate device memory at all: code running inside a fixed memory budget that
+ * was carved up at start-up (an inference server whose allocator owns every byte), code that must not
+ * disturb a caching allocator's state, or a call site where cudaMalloc's implicit synchronisation is
+ * unacceptable. Arguments and results are those of tc_decode_forward_out without the workspace: the
+ * split partials, the split tickets and the status word live in a 2.1 MiB array that is part of the
+ * library image (every GPU that loads the library holds it until the process exits). Limits: batch *
+ * query heads <= 128 rows and at most 32 splits; anything larger is rejected with TC_ERR_INVALID (use
+ * tc_decode_forward_out with your own workspace). num_splits 0 picks the usual split count, capped at 32.
+ * The call makes no cudaMalloc/cudaFree and uses no allocating library routine; it encodes its tensor
+ * maps on the stack and clears the tickets with cudaMemsetAsync on `stream`. The first call on a
+ * device looks up the array's device address (cudaGetSymbolAddress, once per device): make that first
+ * call before any stream capture. All calls on a device share the one array, which keeps the previous
+ * call's partials: two calls that overlap on the GPU (different streams) race; serialise them. */
+int tc_decode_forward_out_static(int device, void* stream, const void* q, void* kcache, void* vcache,
+                                 const void* knew, const void* vnew, const int32_t* old_lengths, void* out,
+                                 float* lse, int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits,
+                                 int64_t mapping, int append);
+
 /* KV-sequence-sharded variant for multi-GPU decode; no counterpart in the reference (it has no
  * distributed path). The caches hold global rows [kv_shard_start, kv_shard_start + capacity) of each
  * sequence; old_lengths stay global. The shard that owns row old_lengths[b] performs the append.

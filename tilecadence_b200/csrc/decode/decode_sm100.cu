@@ -613,6 +613,102 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
                         : launch<false>(kmap, vmap, p, static_cast<cudaStream_t>(stream));
 }
 
+
+// ------------------------------------------------------------------------------- allocation-free variant
+// Scratch for tc_decode_forward_out_static: split partials, split tickets and a status word in one
+// file-scope device array, so the call never allocates. In host code the array's name is only a
+// stand-in for the symbol; the device address comes from cudaGetSymbolAddress (once per device).
+constexpr int kStaticMaxRows = 128;    // batch * query heads (e.g. batch 4 x 32 heads)
+constexpr int kStaticMaxSplits = 32;
+constexpr size_t kStaticOFloats = size_t(kStaticMaxSplits) * kStaticMaxRows * kDim;
+constexpr size_t kStaticLseFloats = size_t(kStaticMaxSplits) * kStaticMaxRows;
+constexpr size_t kStaticTicketWords = kStaticMaxRows / kGroup;
+constexpr size_t kStaticWords = kStaticOFloats + kStaticLseFloats + kStaticTicketWords + 64;
+static __device__ __align__(256) float g_static_scratch[kStaticWords];  // 2.1 MiB per GPU that loads the library
+
+int static_scratch_address(int device, float** address) {
+    static std::mutex lock;
+    static std::unordered_map<int, float*> known;
+    std::lock_guard<std::mutex> guard(lock);
+    auto found = known.find(device);
+    if (found == known.end()) {
+        void* pointer = nullptr;  // `device` is current here: the caller holds a DeviceGuard
+        TC_CUDA(cudaGetSymbolAddress(&pointer, g_static_scratch));
+        TC_REQUIRE(pointer != nullptr, "cudaGetSymbolAddress returned a null scratch address");
+        found = known.emplace(device, static_cast<float*>(pointer)).first;
+    }
+    *address = found->second;
+    return TC_OK;
+}
+
+int decode_static(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                  const void* vnew, const int32_t* old_lengths, void* out, float* lse, int64_t batch,
+                  int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping, int append) {
+    tc::DeviceInfo info;
+    int splits = 1;
+    int status = check_geometry(device, batch, capacity, kv_heads, num_splits, mapping, append, &info, &splits);
+    if (status != TC_OK) return status;
+    TC_REQUIRE(q && kcache && vcache && knew && vnew && old_lengths && lse && out, "null tensor pointer");
+    const int64_t rows = batch * kv_heads * kGroup;
+    TC_REQUIRE(rows <= kStaticMaxRows,
+               "tc_decode_forward_out_static: batch * query heads = %lld exceeds the built-in scratch (max %d rows); "
+               "use tc_decode_forward_out with a caller workspace", static_cast<long long>(rows), kStaticMaxRows);
+    if (num_splits == 0 && splits > kStaticMaxSplits) splits = kStaticMaxSplits;
+    TC_REQUIRE(splits <= kStaticMaxSplits,
+               "tc_decode_forward_out_static: %d splits exceed the built-in scratch (max %d)", splits, kStaticMaxSplits);
+    const size_t q_bytes = size_t(rows) * kDim * 2, cache_bytes = size_t(batch) * capacity * kv_heads * kDim * 2;
+    const size_t new_bytes = size_t(batch) * kv_heads * kDim * 2;
+    const void* pointers[8] = {q, kcache, vcache, knew, vnew, old_lengths, out, lse};
+    const size_t sizes[8] = {q_bytes, cache_bytes, cache_bytes, new_bytes, new_bytes, size_t(batch) * 4, q_bytes,
+                             size_t(rows) * 4};
+    for (int i = 0; i < 8; ++i)
+        for (int j = i + 1; j < 8; ++j)
+            TC_REQUIRE(!tc::ranges_overlap(pointers[i], sizes[i], pointers[j], sizes[j]),
+                       "All nonempty ABI tensor allocations must be disjoint");
+    for (int i = 0; i < 7; ++i)
+        TC_REQUIRE(reinterpret_cast<uintptr_t>(pointers[i]) % 16 == 0 || i == 5, "16-byte aligned storage required");
+
+    tc::DeviceGuard guard(device);
+    TC_CUDA(guard.status);
+    float* scratch = nullptr;
+    if ((status = static_scratch_address(device, &scratch)) != TC_OK) return status;
+    int32_t* tickets = reinterpret_cast<int32_t*>(scratch + kStaticOFloats + kStaticLseFloats);
+    CUtensorMap kmap, vmap;  // encoded on the stack: this path keeps no host-side cache either
+    if ((status = tc::make_rows_map(&kmap, kcache, false, kv_heads, capacity, batch, kDim, kv_heads * kDim,
+                                    capacity * kv_heads * kDim, kTileN, 2)) != TC_OK) return status;
+    if ((status = tc::make_rows_map(&vmap, vcache, false, kv_heads, capacity, batch, kDim, kv_heads * kDim,
+                                    capacity * kv_heads * kDim, kTileN, 2)) != TC_OK) return status;
+    // The tickets must start at zero; the kernel leaves them at zero, but a launch that was cut short
+    // must not poison the next one, so they are cleared on the stream every time.
+    TC_CUDA(cudaMemsetAsync(tickets, 0, kStaticTicketWords * sizeof(int32_t), static_cast<cudaStream_t>(stream)));
+
+    DecodeParams p{};
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.kcache = static_cast<__nv_bfloat16*>(kcache);
+    p.vcache = static_cast<__nv_bfloat16*>(vcache);
+    p.knew = static_cast<const __nv_bfloat16*>(knew);
+    p.vnew = static_cast<const __nv_bfloat16*>(vnew);
+    p.old_lengths = old_lengths;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.lse = lse;
+    p.partial_o = nullptr;
+    p.ws_o = scratch;
+    p.ws_lse = scratch + kStaticOFloats;
+    p.tickets = tickets;
+    p.status = tickets + kStaticTicketWords;
+    p.batch = int(batch);
+    p.capacity = int(capacity);
+    p.kv_heads = int(kv_heads);
+    p.splits = splits;
+    p.append = append ? 1 : 0;
+    p.partial = 0;
+    p.shard_start = 0;
+    p.scale = 1.f / std::sqrt(128.f);
+    p.scale_log2 = p.scale * float(M_LOG2E);
+    return mapping == 1 ? launch<true>(kmap, vmap, p, static_cast<cudaStream_t>(stream))
+                        : launch<false>(kmap, vmap, p, static_cast<cudaStream_t>(stream));
+}
+
 }  // namespace
 
 extern "C" {
@@ -695,6 +791,14 @@ int tc_decode_resources(int device, int64_t batch, int64_t capacity, int64_t kv_
     for (int i = 0; i < 6; ++i) values[28 + i] = tail[i];
     *count = 34;
     return TC_OK;
+}
+
+int tc_decode_forward_out_static(int device, void* stream, const void* q, void* kcache, void* vcache,
+                                 const void* knew, const void* vnew, const int32_t* old_lengths, void* out,
+                                 float* lse, int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits,
+                                 int64_t mapping, int append) {
+    return decode_static(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, batch, capacity,
+                         kv_heads, num_splits, mapping, append);
 }
 
 }  // extern "C"

@@ -174,6 +174,8 @@ class Library:
         "tc_decode_forward_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int)),
+        "tc_decode_forward_out_static": (ctypes.c_int, (
+            ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, *[ctypes.c_int64] * 5, ctypes.c_int)),
         "tc_decode_partial_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, ctypes.c_int64)),
