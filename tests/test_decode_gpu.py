@@ -184,3 +184,21 @@ def test_argument_checks(ops, gpu_device):
         ops.workspace_spec(q.float(), kcache, old, 0, 1, True)
     resources = ops.resources(q, kcache, old, 0, 1, True)
     assert len(resources) == 34 and resources[12] == 160 and resources[19] >= 1 and resources[0] == spec[0]
+
+
+def test_bound_call_repeats_the_validated_call(ops, gpu_device):
+    q, kcache, vcache, knew, vnew = make_case(12, 1, 512)
+    old = torch.tensor([300], dtype=torch.int32)
+    want_o, want_lse, want_k, want_v = oracle.decode_step(q, kcache, vcache, knew, vnew, old)
+    dq, dk, dv, dkn, dvn, dold = (t.to(gpu_device) for t in (q, kcache, vcache, knew, vnew, old))
+    out, lse = torch.empty_like(dq), torch.empty((1, 32, 1), device=gpu_device)
+    spec = ops.workspace_spec(dq, dk, dold, 0, 1, True)
+    ws = [torch.empty(n, device=gpu_device) for n in spec[1:]]
+    invoke = ops.bind_forward_out(dq, dk, dv, dkn, dvn, dold, out, lse, *ws, 0, 1, True)
+    for _ in range(3):  # the append rewrites the same row with the same bits: repeatable
+        invoke()
+    torch.cuda.synchronize()
+    oracle.check_outputs(out.cpu(), lse.cpu(), want_o, want_lse)
+    assert torch.equal(bits(dk.cpu()), bits(want_k)) and torch.equal(bits(dv.cpu()), bits(want_v))
+    with pytest.raises(RuntimeError, match="Invalid complete output"):
+        ops.bind_forward_out(dq, dk, dv, dkn, dvn, dold, out.float(), lse, *ws, 0, 1, True)

@@ -296,6 +296,32 @@ class PrefillOps:
             _pointer(v), _strides(v), _pointer(out), _pointer(lse), 0, 0, q.size(0), q.size(1), q.size(2),
             int(num_splits), int(mapping), float(scale), int(bool(causal)))
 
+    def bind_forward_out(self, q, k, v, out, lse, workspace_o, workspace_lse, num_splits, mapping, scale, causal):
+        """Validate once and return a zero-argument callable that repeats this exact call (see
+        :meth:`DecodeOps.bind_forward_out`)."""
+        import torch
+
+        self._check_inputs(q, k, v, causal)
+        _require(out.device == q.device and out.dtype == q.dtype and out.shape == q.shape and out.is_contiguous()
+                 and not out.requires_grad, "Common complete output must be contiguous BNHD with Q shape")
+        _require(lse.device == q.device and lse.dtype == torch.float32 and lse.is_contiguous() and not lse.requires_grad
+                 and tuple(lse.shape) == (q.size(0), q.size(2), q.size(1)),
+                 f"Complete natural-log LSE must be FP32[B,{q.size(2)},Tq]")
+        _require(workspace_o.numel() == 0 and workspace_lse.numel() == 0, "Generated long prefill uses no split workspace")
+        keep = (q, k, v, out, lse)
+        tail = (_pointer(q), _strides(q), _pointer(k), _strides(k), _pointer(v), _strides(v), _pointer(out), _pointer(lse),
+                0, 0, q.size(0), q.size(1), q.size(2), int(num_splits), int(mapping), float(scale), int(bool(causal)))
+        function = self.library.handle.tc_prefill_forward_out
+        library, device = self.library, q.device
+        current_stream = torch.cuda.current_stream
+
+        def invoke(_keep=keep):
+            status = function(device.index, ctypes.c_void_p(current_stream(device).cuda_stream), *tail)
+            if status != 0:
+                raise RuntimeError("tc_prefill_forward_out: " + library.handle.tc_last_error().decode("utf-8", "replace"))
+
+        return invoke
+
     def resources(self, q, k, v, num_splits, mapping, causal):
         self._check_inputs(q, k, v, causal)
         values = (ctypes.c_int64 * 64)()
@@ -372,6 +398,38 @@ class DecodeOps:
             _pointer(knew), _pointer(vnew), _pointer(old_lengths), _pointer(out), _pointer(lse),
             _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse), workspace_lse.numel(),
             q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping), int(bool(append)))
+
+    def bind_forward_out(self, q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse,
+                         num_splits, mapping, append):
+        """Validate once and return a zero-argument callable that repeats this exact call.
+
+        A decode step on a short cache takes a few microseconds on the GPU, less than the tensor
+        checks cost in Python; a serving loop that reuses its buffers binds the call once. The
+        callable launches on torch's current stream at the time it is invoked.
+        """
+        import torch
+
+        self._check_call(q, kcache, vcache, knew, vnew, old_lengths, workspace_o, workspace_lse)
+        _require(out.device == q.device and out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous()
+                 and not out.requires_grad, "Invalid complete output")
+        _require(lse.device == q.device and lse.dtype == torch.float32 and lse.is_contiguous()
+                 and tuple(lse.shape) == (q.size(0), q.size(2), 1) and not lse.requires_grad, "Invalid full float32 LSE")
+        keep = (q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse)
+        head = (q.device.index,)
+        tail = (_pointer(q), _pointer(kcache), _pointer(vcache), _pointer(knew), _pointer(vnew), _pointer(old_lengths),
+                _pointer(out), _pointer(lse), _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse),
+                workspace_lse.numel(), q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping),
+                int(bool(append)))
+        function = self.library.handle.tc_decode_forward_out
+        library, device = self.library, q.device
+        current_stream = torch.cuda.current_stream
+
+        def invoke(_keep=keep):
+            status = function(*head, ctypes.c_void_p(current_stream(device).cuda_stream), *tail)
+            if status != 0:
+                raise RuntimeError("tc_decode_forward_out: " + library.handle.tc_last_error().decode("utf-8", "replace"))
+
+        return invoke
 
     def partial_out(self, q, kcache, vcache, knew, vnew, old_lengths, partial_o, partial_lse, workspace_o,
                     workspace_lse, num_splits, mapping, append, kv_shard_start):
