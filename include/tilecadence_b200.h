@@ -148,6 +148,19 @@ int tc_combine_partials(int device, void* stream, const float* partial_o, const 
 int tc_decode_resources(int device, int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits,
                         int64_t mapping, int append, int64_t* values, int64_t capacity_values, int64_t* count);
 
+/* ---------------------------------------------------------------------------------- two-tile exchange
+ * Complete attention for 64 queries x 64 keys per (batch, head), D = 128, FP16 or BF16, generated as
+ * straight-line code from a residency-exchange plan. Replaces `forward_out(q,k,v,out!,lse!,nonce,causal,
+ * nonce_is_zero,diagnostic_non_nan_asserted)` and `resources(q,causal) -> int[14]`
+ * (tilecadence/cuda/exchange/binding.cpp:32-72, schemas :79-81). q/k/v/out contiguous [B,64,H,128],
+ * lse fp32 [B,H,64]. The nonce arguments of the reference exist only for its opaque-recovery mode,
+ * which these plans never use. resources: block_m, block_n, head_dim, value_stripe_dim, threads,
+ * dynamic smem, static smem, registers/thread, local bytes/thread, binary version, PTX version,
+ * active CTAs/SM, required nonce elements (0), diagnostic guard (0). */
+int tc_exchange_forward_out(int device, void* stream, const void* q, const void* k, const void* v, void* out,
+                            float* lse, int64_t batch, int64_t heads, int dtype_fp16, int causal);
+int tc_exchange_resources(int device, int dtype_fp16, int causal, int64_t values[14]);
+
 #ifdef __cplusplus
 }
 #endif

@@ -181,6 +181,10 @@ class Library:
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, ctypes.c_int64)),
         "tc_combine_partials": (ctypes.c_int, (ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                *[ctypes.c_int64] * 4, ctypes.c_void_p, ctypes.c_void_p)),
+        "tc_exchange_forward_out": (ctypes.c_int, (ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 5,
+                                                   ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int)),
+        "tc_exchange_resources": (ctypes.c_int, (ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                 ctypes.POINTER(ctypes.c_int64))),
         "tc_decode_resources": (ctypes.c_int, (ctypes.c_int, *[ctypes.c_int64] * 5, ctypes.c_int,
                                                ctypes.POINTER(ctypes.c_int64), ctypes.c_int64,
                                                ctypes.POINTER(ctypes.c_int64))),
@@ -475,9 +479,62 @@ class DecodeOps:
         return list(values[:count.value])
 
 
+class ExchangeOps:
+    """``forward_out`` / ``forward`` / ``resources`` with the reference's two-tile schemas
+    (``tilecadence/cuda/exchange/binding.cpp:32-72,79-81``). q/k/v/out are contiguous [B,64,H,128] FP16 or
+    BF16, lse FP32 [B,H,64]. ``nonce`` is accepted for signature compatibility; these plans need none."""
+
+    phase = "exchange"
+
+    def __init__(self, library):
+        self.library = library
+
+    def _check(self, q, k, v):
+        import torch
+
+        _require(q.is_cuda and q.dim() == 4 and q.size(0) > 0 and q.size(1) == 64 and q.size(2) > 0 and q.size(3) == 128,
+                 "Q must be CUDA [B,64,H,128]")
+        _require(q.dtype in (torch.float16, torch.bfloat16), "FP16 or BF16 inputs required")
+        for tensor in (q, k, v):
+            _require(tensor.device == q.device and tensor.dtype == q.dtype and tensor.shape == q.shape
+                     and tensor.is_contiguous() and not tensor.requires_grad,
+                     "Q, K and V must be contiguous same-shape inference tensors on one device")
+
+    def forward_out(self, q, k, v, out, lse, nonce, causal, nonce_is_zero=True, diagnostic_non_nan_asserted=False):
+        import torch
+
+        self._check(q, k, v)
+        _require(bool(nonce_is_zero) and not diagnostic_non_nan_asserted, "These plans take a zero nonce and no diagnostic guard")
+        _require(out.device == q.device and out.dtype == q.dtype and out.shape == q.shape and out.is_contiguous()
+                 and not out.requires_grad, "Output must be contiguous with Q's shape and dtype")
+        _require(lse.device == q.device and lse.dtype == torch.float32 and lse.is_contiguous()
+                 and tuple(lse.shape) == (q.size(0), q.size(2), 64), "LSE must be FP32 [B,H,64]")
+        self.library.call("tc_exchange_forward_out", q.device.index, _stream(q), _pointer(q), _pointer(k), _pointer(v),
+                          _pointer(out), _pointer(lse), q.size(0), q.size(2), int(q.dtype == torch.float16),
+                          int(bool(causal)))
+
+    def forward(self, q, k, v, nonce, causal, nonce_is_zero=True, diagnostic_non_nan_asserted=False):
+        import torch
+
+        out = torch.empty_like(q)
+        lse = torch.empty((q.size(0), q.size(2), 64), device=q.device, dtype=torch.float32)
+        self.forward_out(q, k, v, out, lse, nonce, causal, nonce_is_zero, diagnostic_non_nan_asserted)
+        return [out, lse]
+
+    def resources(self, q, causal):
+        import torch
+
+        values = (ctypes.c_int64 * 14)()
+        self.library.call("tc_exchange_resources", q.device.index, int(q.dtype == torch.float16), int(bool(causal)), values)
+        return list(values)
+
+
 def ops_for(library, phase=None, q_heads=32):
     if phase is None:
-        phase = "prefill" if library.has("tc_prefill_") else "decode" if library.has("tc_decode_") else None
+        phase = ("prefill" if library.has("tc_prefill_") else "decode" if library.has("tc_decode_")
+                 else "exchange" if library.has("tc_exchange_") else None)
+    if phase == "exchange":
+        return ExchangeOps(library)
     if phase == "prefill":
         return PrefillOps(library, q_heads)
     if phase == "decode":
