@@ -39,6 +39,9 @@ import time
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the three benchmarked launches, from
+# the ncu captures summarised under profiles/ (prefill_kernel_config2.md, decode_splitkv_kernel_config4_config5.md).
+NCU_TRAFFIC_BYTES = {"prefill_c2": 121.3e6, "decode_c4": 33.61e6, "decode_c5": 541.5e6}
 HQ, HKV, DIM = 32, 8, 128
 SCALE = DIM ** -0.5
 PREFILL = dict(batch=1, tokens=8192, seed=1)
@@ -376,7 +379,9 @@ def run_ours(args, rank, world, local_rank):
                   "us_per_step_eager": eager_ms * 1e3, "us_per_step_graph": None if graph_ms is None else graph_ms * 1e3,
                   "hbm_gbs_per_gpu": gbs, "bytes_per_step_per_gpu": rank_bytes,
                   "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
-                               "frac": gbs / peaks["hbm"], "traffic": None, "peak_source": peaks["source"]},
+                               "frac": gbs / peaks["hbm"],
+                               "traffic": None if sharded else NCU_TRAFFIC_BYTES["decode_c4" if cbatch == 1 else "decode_c5"],
+                               "peak_source": peaks["source"]},
                   "cache_sets": sets}
         del caches
         torch.cuda.empty_cache()
@@ -412,7 +417,7 @@ def run_ours(args, rank, world, local_rank):
                        "decode_l2": "rotating cache sets larger than L2"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16"], "frac_of_sustained": achieved / peaks["bf16_sustained"],
-                         "traffic": None, "peak_source": peaks["source"] + " burst"},
+                         "traffic": NCU_TRAFFIC_BYTES["prefill_c2"], "peak_source": peaks["source"] + " burst"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                     "ms_per_step": e2e_ms / args.steps},
             "clocks": clocks, "gpu_launches": launches, "decode": decode,
