@@ -175,6 +175,11 @@ def run_ours(args, rank, world, local_rank):
 
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1; the contract is ONE JSON line
+    # on stdout, so everything but that line is sent to stderr.
+    sys.stdout.flush()
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     library = cuda_runtime.default_library()
@@ -426,7 +431,8 @@ def run_ours(args, rank, world, local_rank):
             line["prefill_sharded"] = prefill_sharded
         if cpu_baseline:
             line["cpu_baseline"] = cpu_baseline
-        print(json.dumps(line), flush=True)
+        json_out.write(json.dumps(line) + "\n")
+        json_out.flush()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

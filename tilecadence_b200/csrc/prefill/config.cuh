@@ -17,6 +17,9 @@
 #ifndef PREFILL_SETMAXNREG
 #define PREFILL_SETMAXNREG 1
 #endif
+#ifndef PREFILL_TURN_NAMED
+#define PREFILL_TURN_NAMED 1
+#endif
 #ifndef PREFILL_TURN_CHUNK
 #define PREFILL_TURN_CHUNK 3
 #endif

@@ -286,7 +286,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         bool ok = true;
 
         for (int it = 0; it < n_tiles; ++it) {
-            if (!(ok = tc::mbar_wait(&bars->s_full[h], uint32_t(it) & 1))) break;
+            if (ok) ok = tc::mbar_wait(&bars->s_full[h], uint32_t(it) & 1);  // after a failed wait: keep the barrier pattern, skip waits
             tc::tc_fence_after_sync();
             float s[128];
 #pragma unroll
@@ -330,7 +330,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 const bool grow = (m_new - m_used) * p.scale_log2 > kRescaleThreshold;
                 // PV of the previous tile must have finished before its P columns are overwritten
                 // (and before O may be rescaled); it was issued long ago, so this rarely waits.
-                if (!(ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1))) break;
+                if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1);
                 tc::tc_fence_after_sync();
                 if (__any_sync(0xffffffffu, grow)) {
                     const float m_target = grow ? m_new : m_used;
@@ -354,7 +354,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             // one warpgroup exponentiates, the other head's P is being consumed by the tensor pipe
             // and its next S tile is produced. Head 0 goes first on every tile.
             if (h == 1 || it > 0) {
-                if (!(ok = tc::mbar_wait(&bars->turn[h], uint32_t(h == 1 ? it : it - 1) & 1))) break;
+#if PREFILL_TURN_NAMED
+                // Hardware named barrier: the other warpgroup's 128 threads arrive without blocking when
+                // their exponentials are issued, this warpgroup's 128 threads wait. It wakes faster than
+                // an mbarrier wait; both sides execute it on every path so the counts always match.
+                asm volatile("bar.sync %0, 256;" ::"r"(3 + h) : "memory");
+#else
+                if (ok) ok = tc::mbar_wait(&bars->turn[h], uint32_t(h == 1 ? it : it - 1) & 1);
+#endif
             }
 #endif
             const float neg_bias = -m_used * p.scale_log2;
@@ -393,7 +400,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
 #if PREFILL_PINGPONG
                 // Hand the exponential unit over a little before this head's last exponentials drain:
                 // the other warpgroup needs about a hundred cycles to wake up.
+#if PREFILL_TURN_NAMED
+                if (c == PREFILL_TURN_CHUNK && (h == 0 || it + 1 < n_tiles))
+                    asm volatile("bar.arrive %0, 256;" ::"r"(3 + (1 - h)) : "memory");
+#else
                 if (c == PREFILL_TURN_CHUNK) tc::mbar_arrive(&bars->turn[1 - h]);
+#endif
 #endif
                 if (kSplitP && c == 2) {
                     // Chunks 0 and 1 were stored a whole chunk of arithmetic ago, so this wait is short.
@@ -453,7 +465,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             tc::tma_store_4d(&omap, o_stage + kHalfBytes, 64, head, m0, b);
             if (bulk_lse) tc::bulk_store_1d(lse_out, lse_stage, kBlockM * 4);
             tc::bulk_commit();
-            tc::bulk_wait_all();
+            tc::bulk_wait_read_all();  // shared memory must outlive the stores' reads; the writes finish on their own
         }
         if (!bulk_lse && row < rows_here) lse_out[row] = row_lse;
     }
