@@ -327,8 +327,9 @@ def run_ours(args, rank, world, local_rank):
         old = torch.full((cbatch,), valid, dtype=torch.int32, device=device)
         dout = torch.empty_like(dq)
         dlse = torch.empty((cbatch, HQ, 1), device=device, dtype=torch.float32)
+        driver = None
         if sharded:
-            driver = sharding.ShardedDecode(decode_ops, rank, world, cbatch, capacity, device)
+            driver = sharding.ShardedDecode(decode_ops, rank, world, cbatch, capacity, device, exchange=sharded)
             counter = [0]
 
             def step():
@@ -336,7 +337,7 @@ def run_ours(args, rank, world, local_rank):
                 counter[0] += 1
                 driver.step(dq, kc, vc, dkn, dvn, old, dout, dlse)
 
-            per_launch = 2
+            per_launch = 1 if sharded == "peer" else 2
             splits = None
         else:
             spec = decode_ops.workspace_spec(dq, caches[0][0], old, 0, 1, True)
@@ -388,18 +389,32 @@ def run_ours(args, rank, world, local_rank):
                                "traffic": None if sharded else NCU_TRAFFIC_BYTES["decode_c4" if cbatch == 1 else "decode_c5"],
                                "peak_source": peaks["source"]},
                   "cache_sets": sets}
+        if driver is not None:
+            torch.cuda.synchronize(device)
+            driver.close()
         del caches
         torch.cuda.empty_cache()
         return result
 
-    decode = {"c4": decode_case(DECODE_C4, sets=8, graph_steps=16, sharded=False)}
+    decode = {"c4": decode_case(DECODE_C4, sets=8, graph_steps=16, sharded=None)}
     decode["c4"]["workload"] = "config4 B1 capacity 32768, 8192 valid + 1 appended, replicas at N>1"
     if world > 1 and DECODE_C5["capacity"] % world == 0:
-        decode["c5"] = decode_case(DECODE_C5, sets=2, graph_steps=4, sharded=True)
-        decode["c5"]["workload"] = (f"config5 B4 32768 rows attended, KV sequence sharded over {world} GPUs, one NCCL "
-                                    "all-gather of packed partial O/LSE + LSE combine per step")
+        nccl_note = ("decode kernel, one NCCL all-gather of packed partial O/LSE, LSE combine kernel: three launches per "
+                     "step")
+        try:
+            decode["c5"] = decode_case(DECODE_C5, sets=2, graph_steps=4, sharded="peer")
+            decode["c5"]["workload"] = (f"config5 B4 32768 rows attended, KV sequence sharded over {world} GPUs, one "
+                                        "launch per step: partial O/LSE cross NVLink as peer stores inside the decode "
+                                        "kernel, which also merges them")
+        except RuntimeError as error:  # agreed on by all ranks (see sharding.PeerBlocks)
+            print(f"in-launch exchange unavailable, using the library route: {error}", file=sys.stderr)
+            decode["c5"] = None
+        decode["c5_nccl"] = decode_case(DECODE_C5, sets=2, graph_steps=4, sharded="nccl")
+        decode["c5_nccl"]["workload"] = f"config5 B4, KV sequence sharded over {world} GPUs, library route: {nccl_note}"
+        if decode["c5"] is None:
+            decode["c5"] = decode.pop("c5_nccl")
     else:
-        decode["c5"] = decode_case(DECODE_C5, sets=2, graph_steps=4, sharded=False)
+        decode["c5"] = decode_case(DECODE_C5, sets=2, graph_steps=4, sharded=None)
         decode["c5"]["workload"] = "config5 B4 32768 rows attended (new row lands at index 32767), one GPU"
 
     status = library.device_status(device.index)

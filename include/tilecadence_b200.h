@@ -142,6 +142,33 @@ int tc_decode_partial_out(int device, void* stream, const void* q, void* kcache,
 int tc_combine_partials(int device, void* stream, const float* partial_o, const float* partial_lse, int64_t parts,
                         int64_t rows, int64_t part_stride_o, int64_t part_stride_lse, void* out, float* lse);
 
+/* Fused variant of tc_decode_partial_out + all-gather + tc_combine_partials for the ranks of one
+ * node (one process per GPU, every GPU a peer of every other over NVLink); no counterpart in the
+ * reference. One launch per rank: the CTA that finishes a (batch, KV head) unit stores this rank's
+ * partial O and LSE into every rank's exchange block with plain peer stores, publishes the unit's
+ * epoch there with a system-scope release, waits (bounded: 2 s, then tc_device_status != 0) for the
+ * same epoch from every rank in its own block, and merges the `world` partials with the arithmetic
+ * of tc_combine_partials. Every rank ends with the full result in out (BF16 [B,1,Hq,128]) and lse
+ * (fp32 [B,Hq]). peer_blocks[r] is rank r's exchange block as mapped into this process
+ * (peer_blocks[rank] is this rank's own block). All ranks must make the same sequence of calls with
+ * the same batch, kv_heads and world on the same blocks. splits * Hkv * B CTAs must be resident at
+ * once (rejected otherwise). No TMA multicast and no collective library call is involved.
+ *
+ * Exchange blocks: tc_peer_block_bytes gives the size for (batch, kv_heads, world);
+ * tc_peer_block_create allocates and zeroes one on `device` and returns a 64-byte interprocess handle;
+ * the other ranks map it with tc_peer_block_open (never the creating process itself) and unmap it
+ * with tc_peer_block_close; the owner frees it with tc_peer_block_destroy after everyone unmapped. */
+int tc_decode_exchange_out(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                           const void* vnew, const int32_t* old_lengths, void* out, float* lse, float* workspace_o,
+                           int64_t workspace_o_elems, float* workspace_lse, int64_t workspace_lse_elems, int64_t batch,
+                           int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping, int append,
+                           int64_t kv_shard_start, int64_t world, int64_t rank, void* const* peer_blocks);
+int tc_peer_block_bytes(int64_t batch, int64_t kv_heads, int64_t world, int64_t* bytes);
+int tc_peer_block_create(int device, int64_t bytes, void** block, unsigned char* handle64);
+int tc_peer_block_open(int device, const unsigned char* handle64, void** block);
+int tc_peer_block_close(int device, void* block);
+int tc_peer_block_destroy(int device, void* block);
+
 /* Replaces `resources(q,kcache,old_lengths,num_splits,mapping,append) -> int[]`
  * (decode.cu:203-229): 12 header values, 8 attributes of the split kernel, 8 of the standalone
  * combine kernel, 6 tail values. */

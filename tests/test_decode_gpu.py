@@ -166,6 +166,34 @@ def test_sharded_partials_and_combine(ops, gpu_device):
     assert torch.isinf(part_lse[3].view(batch, 32)[1]).all()
 
 
+def test_in_launch_exchange_with_one_rank(ops, gpu_device):
+    """The fused exchange route with a world of one: three consecutive steps (both slot parities and a
+    reused slot) must equal the plain entry point bit for bit."""
+    from tilecadence_b200 import sharding
+
+    batch, capacity = 2, 1024
+    q, kcache, vcache, knew, vnew = make_case(21, batch, capacity)
+    device = gpu_device
+    dq, dkn, dvn = q.to(device), knew.to(device), vnew.to(device)
+    driver = sharding.ShardedDecode(ops, 0, 1, batch, capacity, device, exchange="peer")
+    try:
+        dk, dv = kcache.to(device), vcache.to(device)
+        ref_k, ref_v = kcache.clone(), vcache.clone()
+        for step, lengths in enumerate([[700, 3], [701, 4], [702, 5]]):
+            old = torch.tensor(lengths, dtype=torch.int32)
+            want_o, want_lse, ref_k, ref_v, _ = run_step(ops, device, q, ref_k, ref_v, knew, vnew, old)
+            out = torch.full_like(dq, float("nan"))
+            lse = torch.full((batch, 32, 1), float("nan"), device=device, dtype=torch.float32)
+            driver.step(dq, dk, dv, dkn, dvn, old.to(device), out, lse)
+            torch.cuda.synchronize()
+            assert ops.library.device_status(device.index) == 0
+            assert torch.equal(bits(out.cpu()), bits(want_o)), step
+            assert torch.equal(lse.cpu().view(torch.int32), want_lse.view(torch.int32)), step
+            assert torch.equal(bits(dk.cpu()), bits(ref_k)) and torch.equal(bits(dv.cpu()), bits(ref_v))
+    finally:
+        driver.close()
+
+
 def test_argument_checks(ops, gpu_device):
     q, kcache, vcache, knew, vnew = (t.to(gpu_device) for t in make_case(1, 1, 128))
     old = torch.zeros(1, dtype=torch.int32, device=gpu_device)

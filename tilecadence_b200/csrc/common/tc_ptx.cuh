@@ -93,6 +93,28 @@ __device__ __forceinline__ int atomic_add_acq_rel(int* address, int value) {
     return old;
 }
 
+// System-scope flag words: written into another GPU's memory over NVLink (plain peer stores) and
+// polled by the owner. The release makes every store this thread has observed (its own and, through
+// a preceding CTA barrier, its CTA's) visible before the flag; the acquire orders the owner's
+// later loads after it.
+__device__ __forceinline__ void store_release_sys(uint32_t* address, uint32_t value) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(address), "r"(value) : "memory");
+}
+__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* address) {
+    uint32_t value;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(address) : "memory");
+    return value;
+}
+// Bounded wait for a monotonically increasing flag word to reach `target` (wrap-safe comparison).
+__device__ __forceinline__ bool flag_wait_sys(const uint32_t* address, uint32_t target) {
+    if (int32_t(load_acquire_sys(address) - target) >= 0) return true;
+    const uint64_t start = global_timer_ns();
+    for (uint32_t poll = 1;; ++poll) {
+        if (int32_t(load_acquire_sys(address) - target) >= 0) return true;
+        if ((poll & 15u) == 0 && global_timer_ns() - start > TC_WAIT_LIMIT_NS) return false;
+    }
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -19,6 +19,7 @@
 #include "tc_ptx.cuh"
 
 #include <cmath>
+#include <cstring>
 
 namespace {
 
@@ -35,6 +36,25 @@ constexpr int kDim = 128;
 constexpr int kMaxSplits = 128;
 constexpr int kStagingBytes = 2304;  // dedicated O/LSE staging when the handoff is disabled
 constexpr int kBarrierBytes = 256;
+// Cross-GPU exchange of per-rank partials (KV sequence sharded over the ranks of one node). Every
+// rank owns one exchange block that all ranks map; its layout for `world` ranks and `units` =
+// batch * KV heads is
+//   slots  [2 epoch parities][world source ranks][units] x kPeerSlotFloats fp32
+//          (4 rows x 128 partial O, 4 partial LSE, padding to a 16-byte multiple)
+//   flags  [world source ranks][units] u32   last epoch whose slot the source has published
+//   epochs [units] u32                       calls completed by the owner (owner-private)
+constexpr int kMaxPeers = 8;
+constexpr int kPeerSlotFloats = kGroup * kDim + 16;
+constexpr int kPeerSlotBytes = kPeerSlotFloats * 4;
+__host__ __device__ constexpr size_t peer_flags_offset(int world, int units) {
+    return size_t(2) * world * units * kPeerSlotBytes;
+}
+__host__ __device__ constexpr size_t peer_epochs_offset(int world, int units) {
+    return peer_flags_offset(world, units) + size_t(world) * units * 4;
+}
+__host__ __device__ constexpr size_t peer_block_bytes(int world, int units) {
+    return (peer_epochs_offset(world, units) + size_t(units) * 4 + 255) / 256 * 256;
+}
 
 static_assert(kStageBytes == 2 * kVBytes, "a stage holds one V tile followed by one K tile");
 static_assert(kMaxSplits % 32 == 0 && kGroup * kMaxSplits * 4 <= kVBytes, "split weights fit the terminal K stage");
@@ -68,6 +88,8 @@ struct DecodeParams {
     int batch, capacity, kv_heads, splits, append, partial;
     int64_t shard_start;
     float scale, scale_log2;
+    uint8_t* peer_blocks[kMaxPeers];  // partial == 2: every rank's exchange block as mapped here
+    int world, rank;
 };
 
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
@@ -78,7 +100,36 @@ __device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk16) {
     return (chunk16 >> 3) * kHalfBytes + row * 128 + (((chunk16 & 7) ^ (row & 7)) << 4);
 }
 
-template <bool kHandoff>
+// LSE-weighted merge of `parts` normalised partial results for one output row (four columns per
+// thread): LSE = ln sum_s e^{LSE_s}, O = sum_s e^{LSE_s - LSE} O_s. A part that saw no key has
+// LSE = -inf and may hold anything: it is never multiplied. A row nobody saw gets O = 0, LSE = +inf.
+// Both the standalone combine kernel and the in-launch cross-GPU merge use this one function, so
+// the two routes give identical bits.
+template <class LoadLse, class LoadO>
+__device__ __forceinline__ void lse_weighted_merge(int parts, LoadLse load_lse, LoadO load_o, float4& o, float& lse) {
+    float lse_max = -INFINITY;
+    for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, load_lse(s));
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float total = 0.f;
+    if (lse_max != -INFINITY) {
+        for (int s = 0; s < parts; ++s) {
+            const float part_lse = load_lse(s);
+            const float4 v = load_o(s);
+            const bool used = part_lse != -INFINITY;
+            const float weight = used ? __expf(part_lse - lse_max) : 0.f;
+            total += weight;
+            acc.x += used ? weight * v.x : 0.f;
+            acc.y += used ? weight * v.y : 0.f;
+            acc.z += used ? weight * v.z : 0.f;
+            acc.w += used ? weight * v.w : 0.f;
+        }
+    }
+    const float inv = total > 0.f ? 1.f / total : 0.f;
+    o = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    lse = total > 0.f ? lse_max + logf(total) : INFINITY;
+}
+
+template <bool kHandoff, bool kPeer>
 __global__ void __launch_bounds__(kThreads, AB_DECODE_CTAS_PER_SM)
 decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                       const DecodeParams p) {
@@ -403,7 +454,51 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     }
 
     const int64_t out_row = int64_t(b) * q_heads + kvh * kGroup + row;
-    if (p.partial) {
+    if (kPeer) {
+        // Cross-GPU merge inside the same launch. This CTA holds this rank's partial for the
+        // (batch, KV head) unit. It stores the partial into every rank's exchange block (plain peer
+        // stores over NVLink, its own block included), publishes the unit's epoch in every block,
+        // waits (bounded) until every rank's partial of the same epoch has landed in its own block
+        // and merges them. Slots alternate with the epoch's parity: a rank can be at most one call
+        // ahead of the slowest reader, because it cannot finish call e+1 before that reader has
+        // published e+1, which the reader does only after it has merged call e.
+        const int world = p.world, units = p.batch * p.kv_heads, unit = int(head_slot);
+        uint8_t* mine = p.peer_blocks[p.rank];
+        uint32_t* epochs = reinterpret_cast<uint32_t*>(mine + peer_epochs_offset(world, units));
+        const uint32_t epoch = epochs[unit] + 1;  // only this CTA touches the word during this launch
+        const size_t slot_bytes = (size_t(epoch & 1) * world * units + unit) * kPeerSlotBytes;
+        const size_t rank_stride = size_t(units) * kPeerSlotBytes;
+        for (int r = 0; r < world; ++r) {
+            float* slot = reinterpret_cast<float*>(p.peer_blocks[r] + slot_bytes + p.rank * rank_stride);
+            *reinterpret_cast<float4*>(slot + row * kDim + col4 * 4) = final_o;
+            if (col4 == 0) slot[kGroup * kDim + row] = final_lse;
+        }
+        __threadfence_system();
+        consumer_barrier();
+        bool arrived = true;
+        if (tid < world) {
+            uint32_t* theirs = reinterpret_cast<uint32_t*>(p.peer_blocks[tid] + peer_flags_offset(world, units));
+            tc::store_release_sys(theirs + p.rank * units + unit, epoch);
+            const uint32_t* flags = reinterpret_cast<const uint32_t*>(mine + peer_flags_offset(world, units));
+            arrived = tc::flag_wait_sys(flags + tid * units + unit, epoch);
+        }
+        if (!arrived) atomicCAS(p.status, 0, 5);  // a rank never published: the result below is not valid
+        consumer_barrier();
+        const float* slots = reinterpret_cast<const float*>(mine + slot_bytes);
+        const int64_t stride = int64_t(units) * kPeerSlotFloats;
+        float4 merged;
+        float merged_lse;
+        lse_weighted_merge(
+            world, [&](int s) { return __ldcg(slots + s * stride + kGroup * kDim + row); },
+            [&](int s) { return __ldcg(reinterpret_cast<const float4*>(slots + s * stride + row * kDim) + col4); },
+            merged, merged_lse);
+        uint2 packed;
+        packed.x = tc::pack_bf16x2(merged.x, merged.y);
+        packed.y = tc::pack_bf16x2(merged.z, merged.w);
+        *reinterpret_cast<uint2*>(p.out + out_row * kDim + col4 * 4) = packed;
+        if (col4 == 0) p.lse[out_row] = merged_lse;
+        if (tid == 0) epochs[unit] = epoch;
+    } else if (p.partial) {
         *reinterpret_cast<float4*>(p.partial_o + out_row * kDim + col4 * 4) = final_o;
         if (col4 == 0) p.lse[out_row] = final_lse;
     } else {
@@ -424,29 +519,17 @@ __global__ void __launch_bounds__(128) combine_partials_kernel(const float* __re
     const int64_t row = int64_t(blockIdx.x) * 4 + (threadIdx.x >> 5);
     const int col4 = threadIdx.x & 31;
     if (row >= rows) return;
-    float lse_max = -INFINITY;
-    for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, partial_lse[s * stride_lse + row]);
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float total = 0.f;
-    if (lse_max != -INFINITY) {
-        for (int s = 0; s < parts; ++s) {
-            const float part_lse = partial_lse[s * stride_lse + row];
-            const float4 v = reinterpret_cast<const float4*>(partial_o + s * stride_o + row * kDim)[col4];
-            const bool used = part_lse != -INFINITY;
-            const float weight = used ? __expf(part_lse - lse_max) : 0.f;
-            total += weight;
-            acc.x += used ? weight * v.x : 0.f;
-            acc.y += used ? weight * v.y : 0.f;
-            acc.z += used ? weight * v.z : 0.f;
-            acc.w += used ? weight * v.w : 0.f;
-        }
-    }
-    const float inv = total > 0.f ? 1.f / total : 0.f;
+    float4 merged;
+    float merged_lse;
+    lse_weighted_merge(
+        parts, [&](int s) { return partial_lse[s * stride_lse + row]; },
+        [&](int s) { return reinterpret_cast<const float4*>(partial_o + s * stride_o + row * kDim)[col4]; }, merged,
+        merged_lse);
     uint2 packed;
-    packed.x = tc::pack_bf16x2(acc.x * inv, acc.y * inv);
-    packed.y = tc::pack_bf16x2(acc.z * inv, acc.w * inv);
+    packed.x = tc::pack_bf16x2(merged.x, merged.y);
+    packed.y = tc::pack_bf16x2(merged.z, merged.w);
     *reinterpret_cast<uint2*>(out + row * kDim + col4 * 4) = packed;
-    if (col4 == 0) lse[row] = total > 0.f ? lse_max + logf(total) : INFINITY;
+    if (col4 == 0) lse[row] = merged_lse;
 }
 
 // ------------------------------------------------------------------------------- host side
@@ -478,9 +561,9 @@ int check_geometry(int device, int64_t batch, int64_t capacity, int64_t kv_heads
     return TC_OK;
 }
 
-template <bool kHandoff>
+template <bool kHandoff, bool kPeer = false>
 int launch(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams& p, cudaStream_t stream) {
-    auto kernel = &decode_splitkv_kernel<kHandoff>;
+    auto kernel = &decode_splitkv_kernel<kHandoff, kPeer>;
     constexpr int shared = shared_bytes(kHandoff);
     static thread_local int configured_device = -1;
     int device = 0;
@@ -502,6 +585,11 @@ int launch(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams&
     TC_CUDA(cudaLaunchKernelEx(&config, kernel, kmap, vmap, p));
     return TC_OK;
 }
+
+struct PeerArgs {
+    void* const* blocks;  // world pointers: every rank's exchange block as mapped into this process
+    int world, rank;
+};
 
 struct MapKey {
     const void* base;
@@ -543,14 +631,27 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
                   const void* vnew, const int32_t* old_lengths, void* out, float* lse, float* partial_o,
                   float* workspace_o, int64_t workspace_o_elems, float* workspace_lse, int64_t workspace_lse_elems,
                   int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping, int append,
-                  int partial, int64_t shard_start) {
+                  int partial, int64_t shard_start, const PeerArgs* peer = nullptr) {
     tc::DeviceInfo info;
     int splits = 1;
     int status = check_geometry(device, batch, capacity, kv_heads, num_splits, mapping, append, &info, &splits);
     if (status != TC_OK) return status;
-    TC_REQUIRE(q && kcache && vcache && knew && vnew && old_lengths && lse && (partial ? (void*)partial_o : out),
+    TC_REQUIRE(q && kcache && vcache && knew && vnew && old_lengths && lse && (partial == 1 ? (void*)partial_o : out),
                "null tensor pointer");
     TC_REQUIRE(shard_start >= 0, "kv_shard_start must be non-negative");
+    TC_REQUIRE((partial == 2) == (peer != nullptr), "peer exchange arguments do not match the call");
+    if (peer) {
+        TC_REQUIRE(peer->world >= 1 && peer->world <= kMaxPeers && peer->rank >= 0 && peer->rank < peer->world,
+                   "peer exchange needs 1 <= world <= 8 and 0 <= rank < world");
+        TC_REQUIRE(peer->blocks, "null peer block table");
+        for (int r = 0; r < peer->world; ++r)
+            TC_REQUIRE(peer->blocks[r] && reinterpret_cast<uintptr_t>(peer->blocks[r]) % 16 == 0,
+                       "every rank's exchange block must be mapped and 16-byte aligned");
+        // Every CTA of the grid must be resident at once: a CTA that waits for another rank holds
+        // its slot, and the CTAs it indirectly waits for on that rank must never queue behind waiters.
+        TC_REQUIRE(int64_t(splits) * kv_heads * batch <= int64_t(info.sms) * AB_DECODE_CTAS_PER_SM,
+                   "peer exchange needs splits*Hkv*B CTAs to be co-resident; lower num_splits");
+    }
     const int64_t q_heads = kv_heads * kGroup;
     const int64_t rows = batch * q_heads;
     const size_t q_bytes = size_t(rows) * kDim * 2, cache_bytes = size_t(batch) * capacity * kv_heads * kDim * 2;
@@ -560,10 +661,10 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
     TC_REQUIRE(workspace_o_elems >= need_o && workspace_lse_elems >= need_lse,
                "Preallocated complete split workspace is too small");
     TC_REQUIRE(!need_o || (workspace_o && workspace_lse), "null split workspace");
-    const void* pointers[10] = {q, kcache, vcache, knew, vnew, old_lengths, partial ? (void*)partial_o : out, lse,
+    const void* pointers[10] = {q, kcache, vcache, knew, vnew, old_lengths, partial == 1 ? (void*)partial_o : out, lse,
                                 need_o ? workspace_o : nullptr, need_lse ? workspace_lse : nullptr};
     const size_t sizes[10] = {q_bytes, cache_bytes, cache_bytes, new_bytes, new_bytes, size_t(batch) * 4,
-                              partial ? size_t(rows) * kDim * 4 : q_bytes, size_t(rows) * 4, size_t(need_o) * 4,
+                              partial == 1 ? size_t(rows) * kDim * 4 : q_bytes, size_t(rows) * 4, size_t(need_o) * 4,
                               size_t(need_lse) * 4};
     for (int i = 0; i < 10; ++i)
         for (int j = i + 1; j < 10; ++j)
@@ -609,6 +710,13 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
     p.shard_start = shard_start;
     p.scale = 1.f / std::sqrt(128.f);
     p.scale_log2 = p.scale * float(M_LOG2E);
+    if (peer) {
+        p.world = peer->world;
+        p.rank = peer->rank;
+        for (int r = 0; r < peer->world; ++r) p.peer_blocks[r] = static_cast<uint8_t*>(peer->blocks[r]);
+        return mapping == 1 ? launch<true, true>(kmap, vmap, p, static_cast<cudaStream_t>(stream))
+                            : launch<false, true>(kmap, vmap, p, static_cast<cudaStream_t>(stream));
+    }
     return mapping == 1 ? launch<true>(kmap, vmap, p, static_cast<cudaStream_t>(stream))
                         : launch<false>(kmap, vmap, p, static_cast<cudaStream_t>(stream));
 }
@@ -781,8 +889,8 @@ int tc_decode_resources(int device, int64_t batch, int64_t capacity, int64_t kv_
                                 splits > 1 ? batch * kv_heads : 0, splits > 1 ? splits * rows * kDim : 0,
                                 splits > 1 ? splits * rows : 0, kGroup, kTileN, 1};
     for (int i = 0; i < 12; ++i) values[i] = header[i];
-    status = mapping == 1 ? tc::kernel_resources(&decode_splitkv_kernel<true>, kThreads, shared_bytes(true), values + 12)
-                          : tc::kernel_resources(&decode_splitkv_kernel<false>, kThreads, shared_bytes(false), values + 12);
+    status = mapping == 1 ? tc::kernel_resources(&decode_splitkv_kernel<true, false>, kThreads, shared_bytes(true), values + 12)
+                          : tc::kernel_resources(&decode_splitkv_kernel<false, false>, kThreads, shared_bytes(false), values + 12);
     if (status != TC_OK) return status;
     status = tc::kernel_resources(&combine_partials_kernel, 128, 0, values + 20);
     if (status != TC_OK) return status;
@@ -799,6 +907,71 @@ int tc_decode_forward_out_static(int device, void* stream, const void* q, void* 
                                  int64_t mapping, int append) {
     return decode_static(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, batch, capacity,
                          kv_heads, num_splits, mapping, append);
+}
+
+int tc_peer_block_bytes(int64_t batch, int64_t kv_heads, int64_t world, int64_t* bytes) {
+    TC_REQUIRE(bytes, "null bytes");
+    TC_REQUIRE(batch >= 1 && batch <= 65535 && kv_heads >= 1 && kv_heads <= 8 && world >= 1 && world <= kMaxPeers,
+               "peer exchange needs 1 <= B <= 65535, 1 <= Hkv <= 8, 1 <= world <= 8");
+    *bytes = int64_t(peer_block_bytes(int(world), int(batch * kv_heads)));
+    return TC_OK;
+}
+
+int tc_peer_block_create(int device, int64_t bytes, void** block, unsigned char* handle64) {
+    TC_REQUIRE(block && handle64 && bytes > 0, "null output or empty block");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the ABI");
+    tc::DeviceGuard guard(device);
+    TC_CUDA(guard.status);
+    void* pointer = nullptr;
+    TC_CUDA(cudaMalloc(&pointer, size_t(bytes)));
+    cudaError_t error = cudaMemset(pointer, 0, size_t(bytes));  // flags and epochs start at zero
+    cudaIpcMemHandle_t handle;
+    if (error == cudaSuccess) error = cudaIpcGetMemHandle(&handle, pointer);
+    if (error != cudaSuccess) {
+        cudaFree(pointer);
+        TC_CUDA(error);
+    }
+    std::memcpy(handle64, &handle, 64);
+    *block = pointer;
+    return TC_OK;
+}
+
+int tc_peer_block_open(int device, const unsigned char* handle64, void** block) {
+    TC_REQUIRE(block && handle64, "null handle or output");
+    tc::DeviceGuard guard(device);
+    TC_CUDA(guard.status);
+    cudaIpcMemHandle_t handle;
+    std::memcpy(&handle, handle64, 64);
+    TC_CUDA(cudaIpcOpenMemHandle(block, handle, cudaIpcMemLazyEnablePeerAccess));
+    return TC_OK;
+}
+
+int tc_peer_block_close(int device, void* block) {
+    TC_REQUIRE(block, "null block");
+    tc::DeviceGuard guard(device);
+    TC_CUDA(guard.status);
+    TC_CUDA(cudaIpcCloseMemHandle(block));
+    return TC_OK;
+}
+
+int tc_peer_block_destroy(int device, void* block) {
+    TC_REQUIRE(block, "null block");
+    tc::DeviceGuard guard(device);
+    TC_CUDA(guard.status);
+    TC_CUDA(cudaFree(block));
+    return TC_OK;
+}
+
+int tc_decode_exchange_out(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                           const void* vnew, const int32_t* old_lengths, void* out, float* lse, float* workspace_o,
+                           int64_t workspace_o_elems, float* workspace_lse, int64_t workspace_lse_elems, int64_t batch,
+                           int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping, int append,
+                           int64_t kv_shard_start, int64_t world, int64_t rank, void* const* peer_blocks) {
+    TC_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, "need 1 <= world <= 8, 0 <= rank < world");
+    const PeerArgs peer{peer_blocks, int(world), int(rank)};
+    return decode_common(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, nullptr, workspace_o,
+                         workspace_o_elems, workspace_lse, workspace_lse_elems, batch, capacity, kv_heads, num_splits,
+                         mapping, append, 2, kv_shard_start, &peer);
 }
 
 }  // extern "C"

@@ -179,6 +179,16 @@ class Library:
         "tc_decode_partial_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, ctypes.c_int64)),
+        "tc_decode_exchange_out": (ctypes.c_int, (
+            ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
+            ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, *[ctypes.c_int64] * 3,
+            ctypes.POINTER(ctypes.c_void_p))),
+        "tc_peer_block_bytes": (ctypes.c_int, (*[ctypes.c_int64] * 3, ctypes.POINTER(ctypes.c_int64))),
+        "tc_peer_block_create": (ctypes.c_int, (ctypes.c_int, ctypes.c_int64, ctypes.POINTER(ctypes.c_void_p),
+                                                ctypes.c_char_p)),
+        "tc_peer_block_open": (ctypes.c_int, (ctypes.c_int, ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p))),
+        "tc_peer_block_close": (ctypes.c_int, (ctypes.c_int, ctypes.c_void_p)),
+        "tc_peer_block_destroy": (ctypes.c_int, (ctypes.c_int, ctypes.c_void_p)),
         "tc_combine_partials": (ctypes.c_int, (ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                *[ctypes.c_int64] * 4, ctypes.c_void_p, ctypes.c_void_p)),
         "tc_exchange_forward_out": (ctypes.c_int, (ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 5,
@@ -388,15 +398,19 @@ class DecodeOps:
                      and workspace.is_contiguous() and not workspace.requires_grad,
                      "Contiguous CUDA FP32 workspace required")
 
-    def forward_out(self, q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse,
-                    num_splits, mapping, append):
+    @staticmethod
+    def _check_out(q, out, lse):
         import torch
 
-        self._check_call(q, kcache, vcache, knew, vnew, old_lengths, workspace_o, workspace_lse)
         _require(out.device == q.device and out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous()
                  and not out.requires_grad, "Invalid complete output")
         _require(lse.device == q.device and lse.dtype == torch.float32 and lse.is_contiguous()
                  and tuple(lse.shape) == (q.size(0), q.size(2), 1) and not lse.requires_grad, "Invalid full float32 LSE")
+
+    def forward_out(self, q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse,
+                    num_splits, mapping, append):
+        self._check_call(q, kcache, vcache, knew, vnew, old_lengths, workspace_o, workspace_lse)
+        self._check_out(q, out, lse)
         self.library.call(
             "tc_decode_forward_out", q.device.index, _stream(q), _pointer(q), _pointer(kcache), _pointer(vcache),
             _pointer(knew), _pointer(vnew), _pointer(old_lengths), _pointer(out), _pointer(lse),
@@ -451,6 +465,19 @@ class DecodeOps:
             _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse), workspace_lse.numel(),
             q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping), int(bool(append)),
             int(kv_shard_start))
+
+    def exchange_out(self, q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse,
+                     num_splits, mapping, append, kv_shard_start, rank, peer_blocks):
+        """Sharded decode step with the cross-GPU merge inside the launch; ``peer_blocks`` is the
+        ctypes array of every rank's exchange block (see :class:`tilecadence_b200.sharding.PeerBlocks`)."""
+        self._check_call(q, kcache, vcache, knew, vnew, old_lengths, workspace_o, workspace_lse)
+        self._check_out(q, out, lse)
+        self.library.call(
+            "tc_decode_exchange_out", q.device.index, _stream(q), _pointer(q), _pointer(kcache), _pointer(vcache),
+            _pointer(knew), _pointer(vnew), _pointer(old_lengths), _pointer(out), _pointer(lse),
+            _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse), workspace_lse.numel(),
+            q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping), int(bool(append)),
+            int(kv_shard_start), len(peer_blocks), int(rank), peer_blocks)
 
     def combine_partials(self, partial_o, partial_lse, out, lse):
         """Merge partial_o [parts, rows, 128] / partial_lse [parts, rows] (fp32; the part dimension may be
