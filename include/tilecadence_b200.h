@@ -142,6 +142,27 @@ int tc_decode_partial_out(int device, void* stream, const void* q, void* kcache,
 int tc_combine_partials(int device, void* stream, const float* partial_o, const float* partial_lse, int64_t parts,
                         int64_t rows, int64_t part_stride_o, int64_t part_stride_lse, void* out, float* lse);
 
+/* Decode step over indexed caches: the two indirections the reference's split kernel carries
+ * (ab_fused_splitkv.cuh:92-103: `cache_batch_idx`, and `block_table` + `page_block_size`) but its host
+ * code never sets. Everything not listed is as in tc_decode_forward_out.
+ *   block_table != NULL   paged caches: kcache/vcache are BF16 [cache_slots, slot_rows, Hkv, 128] (pages of
+ *                         slot_rows rows, a multiple of 64); row r of sequence b lives in page
+ *                         block_table[b*block_table_stride + r/slot_rows] at row r % slot_rows. The
+ *                         sequence capacity is pages_per_seq * slot_rows; old_lengths[b] must be below it.
+ *                         cache_batch_idx must be NULL.
+ *   block_table == NULL   cache_batch_idx (int32 [B], required) picks the cache slot of sequence b;
+ *                         caches are [cache_slots, slot_rows = capacity, Hkv, 128]; pages_per_seq is ignored.
+ * Table entries are read on the device; values outside [0, cache_slots) are clamped so that no access
+ * leaves the cache allocation. The appended row is written to its page. Two sequences must not map to
+ * the same page or slot. Size the split workspace with tc_decode_workspace_spec(batch, capacity, ...). */
+int tc_decode_indexed_forward_out(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                                  const void* vnew, const int32_t* old_lengths, void* out, float* lse,
+                                  float* workspace_o, int64_t workspace_o_elems, float* workspace_lse,
+                                  int64_t workspace_lse_elems, int64_t batch, int64_t cache_slots, int64_t slot_rows,
+                                  int64_t kv_heads, int64_t num_splits, int64_t mapping, int append,
+                                  const int32_t* block_table, int64_t block_table_stride, int64_t pages_per_seq,
+                                  const int32_t* cache_batch_idx);
+
 /* Fused variant of tc_decode_partial_out + all-gather + tc_combine_partials for the ranks of one
  * node (one process per GPU, every GPU a peer of every other over NVLink); no counterpart in the
  * reference. One launch per rank: the CTA that finishes a (batch, KV head) unit stores this rank's

@@ -104,6 +104,37 @@ def decode_step(q, kcache, vcache, knew, vnew, old_lengths, append=True, scale=D
     return out, lse, kcache, vcache
 
 
+def decode_step_indexed(q, kcache, vcache, knew, vnew, old_lengths, block_table=None, cache_batch_idx=None,
+                        append=True, scale=DEFAULT_SCALE):
+    """Decode step over indexed caches, by gathering each sequence's rows into a contiguous cache,
+    running :func:`decode_step` and scattering the caches back.
+
+    Follows the two indirections of ``tilecadence/cuda/decode/ab_fused_splitkv.cuh:92-103``:
+    with ``block_table`` int [B, pages] the caches are pages [P, page_size, Hkv, D] and row ``r`` of
+    sequence ``b`` is row ``r % page_size`` of page ``block_table[b, r // page_size]``; with
+    ``cache_batch_idx`` int [B] sequence ``b`` uses cache entry ``cache_batch_idx[b]``.
+    Returns (O, LSE, kcache_after, vcache_after) in the caches' own layout.
+    """
+    if (block_table is None) == (cache_batch_idx is None):
+        raise ValueError("pass exactly one of block_table / cache_batch_idx")
+    if block_table is not None:
+        index = block_table.long()
+        gather = lambda cache: cache[index].flatten(1, 2)  # [B, pages * page_size, Hkv, D]
+    else:
+        index = cache_batch_idx.long()
+        gather = lambda cache: cache[index]
+    out, lse, k_seq, v_seq = decode_step(q, gather(kcache), gather(vcache), knew, vnew, old_lengths, append, scale)
+    k_after, v_after = kcache.clone(), vcache.clone()
+    if block_table is not None:
+        page = kcache.shape[1]
+        k_after[index] = k_seq.unflatten(1, (-1, page))
+        v_after[index] = v_seq.unflatten(1, (-1, page))
+    else:
+        k_after[index] = k_seq
+        v_after[index] = v_seq
+    return out, lse, k_after, v_after
+
+
 def combine(partial_o, partial_lse):
     """Merge ``parts`` partial results: partial_o [parts, rows, D] fp32, partial_lse [parts, rows].
 

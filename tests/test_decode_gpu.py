@@ -166,6 +166,80 @@ def test_sharded_partials_and_combine(ops, gpu_device):
     assert torch.isinf(part_lse[3].view(batch, 32)[1]).all()
 
 
+def run_indexed(ops, device, q, kcache, vcache, knew, vnew, old, capacity, num_splits=0, **index):
+    dq, dk, dv, dkn, dvn = (t.to(device) for t in (q, kcache, vcache, knew, vnew))
+    dold = old.to(device)
+    out = torch.full_like(dq, float("nan"))
+    lse = torch.full((q.size(0), 32, 1), float("nan"), device=device, dtype=torch.float32)
+    spec = ops.indexed_workspace_spec(q.size(0), capacity, 8, device.index, num_splits)
+    ws = [torch.full((n,), float("nan"), device=device, dtype=torch.float32) for n in spec[1:3]]
+    ops.indexed_forward_out(dq, dk, dv, dkn, dvn, dold, out, lse, *ws, num_splits, 1, True,
+                            **{name: value.to(device) for name, value in index.items()})
+    torch.cuda.synchronize()
+    assert ops.library.device_status(device.index) == 0
+    return out.cpu(), lse.cpu(), dk.cpu(), dv.cpu()
+
+
+@pytest.mark.parametrize("page,pages_per_seq,lengths,num_splits", [
+    (64, 5, [130, 64, 0], 0),
+    (128, 8, [1023, 517, 128], 0),
+    (256, 40, [10239, 4097, 255], 0),
+    (64, 160, [10000, 9000, 8000], 1),  # one split walks 157 tiles of 157 pages: the table is read in batches of 32
+])
+def test_paged_cache_equals_contiguous_cache(ops, gpu_device, page, pages_per_seq, lengths, num_splits):
+    """Scattered pages (shuffled block table, spare pages holding NaN) give the bits of the same rows
+    in a contiguous cache, match the oracle, and only the appended rows change."""
+    batch, capacity = len(lengths), page * pages_per_seq
+    q, kcache, vcache, knew, vnew = make_case(300 + page, batch, capacity, fill=lengths)
+    old = torch.tensor(lengths, dtype=torch.int32)
+    generator = torch.Generator().manual_seed(page)
+    pool = batch * pages_per_seq + 3
+    table = torch.randperm(pool, generator=generator)[:batch * pages_per_seq].view(batch, pages_per_seq).to(torch.int32)
+    paged_k = torch.full((pool, page, 8, 128), float("nan"), dtype=torch.bfloat16)
+    paged_v = torch.full((pool, page, 8, 128), float("nan"), dtype=torch.bfloat16)
+    paged_k[table.long()] = kcache.unflatten(1, (pages_per_seq, page))
+    paged_v[table.long()] = vcache.unflatten(1, (pages_per_seq, page))
+    want_o, want_lse, want_k, want_v = oracle.decode_step_indexed(q, paged_k, paged_v, knew, vnew, old, block_table=table)
+    got_o, got_lse, got_k, got_v = run_indexed(ops, gpu_device, q, paged_k, paged_v, knew, vnew, old, capacity,
+                                               num_splits, block_table=table)
+    oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+    assert torch.equal(bits(got_k), bits(want_k)) and torch.equal(bits(got_v), bits(want_v))
+    flat_o, flat_lse, _, _, _ = run_step(ops, gpu_device, q, kcache, vcache, knew, vnew, old, num_splits=num_splits)
+    assert torch.equal(bits(got_o), bits(flat_o)) and torch.equal(got_lse.view(torch.int32), flat_lse.view(torch.int32))
+
+
+def test_cache_batch_index(ops, gpu_device):
+    batch, capacity, slots = 3, 512, 6
+    q, kcache, vcache, knew, vnew = make_case(41, slots, capacity)
+    q, knew, vnew = q[:batch], knew[:batch], vnew[:batch]
+    index = torch.tensor([4, 0, 5], dtype=torch.int32)
+    old = torch.tensor([511, 100, 0], dtype=torch.int32)
+    want_o, want_lse, want_k, want_v = oracle.decode_step_indexed(q, kcache, vcache, knew, vnew, old, cache_batch_idx=index)
+    got_o, got_lse, got_k, got_v = run_indexed(ops, gpu_device, q, kcache, vcache, knew, vnew, old, capacity,
+                                               cache_batch_idx=index)
+    oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+    assert torch.equal(bits(got_k), bits(want_k)) and torch.equal(bits(got_v), bits(want_v))
+    flat_o, flat_lse, _, _, _ = run_step(ops, gpu_device, q, kcache[index.long()], vcache[index.long()], knew, vnew, old)
+    assert torch.equal(bits(got_o), bits(flat_o)) and torch.equal(got_lse.view(torch.int32), flat_lse.view(torch.int32))
+
+
+def test_indexed_argument_checks(ops, gpu_device):
+    q, kcache, vcache, knew, vnew = (t.to(gpu_device) for t in make_case(1, 1, 128))
+    old = torch.tensor([5], dtype=torch.int32, device=gpu_device)
+    out, lse = torch.empty_like(q), torch.empty((1, 32, 1), device=gpu_device)
+    ws = [torch.empty(n, device=gpu_device) for n in ops.indexed_workspace_spec(1, 128, 8, gpu_device.index)[1:3]]
+    table = torch.zeros((1, 1), dtype=torch.int32, device=gpu_device)
+    index = torch.zeros((1,), dtype=torch.int32, device=gpu_device)
+    with pytest.raises(RuntimeError, match="exactly one"):
+        ops.indexed_forward_out(q, kcache, vcache, knew, vnew, old, out, lse, *ws, 0, 1, True)
+    with pytest.raises(RuntimeError, match="exactly one"):
+        ops.indexed_forward_out(q, kcache, vcache, knew, vnew, old, out, lse, *ws, 0, 1, True, table, index)
+    odd_k, odd_v = kcache[:, :96].contiguous(), vcache[:, :96].contiguous()
+    with pytest.raises(RuntimeError, match="multiple of 64"):
+        ops.indexed_forward_out(q, odd_k, odd_v, knew, vnew, old, out, lse, *ws, 0, 1, True, block_table=table)
+    torch.cuda.synchronize()
+
+
 def test_in_launch_exchange_with_one_rank(ops, gpu_device):
     """The fused exchange route with a world of one: three consecutive steps (both slot parities and a
     reused slot) must equal the plain entry point bit for bit."""

@@ -91,3 +91,29 @@ def test_combine_handles_empty_parts():
     assert torch.equal(merged[2], o[1, 2])
     torch.testing.assert_close(merged[3], o[:, 3].mean(dim=0))
     torch.testing.assert_close(merged_lse[3], torch.tensor(1.0 + np.log(3.0), dtype=torch.float32))
+
+
+def test_indexed_caches_equal_the_gathered_contiguous_step():
+    """Paged and batch-indexed decode in the oracle are the contiguous step on the gathered rows, and
+    only the appended row of the owning page / slot changes."""
+    batch, pages, page = 2, 7, 64
+    kcache, vcache, q, knew, vnew = oracle.seeded_normal(
+        5, (pages, page, 8, 128), (pages, page, 8, 128), (batch, 1, 32, 128), (batch, 1, 8, 128), (batch, 1, 8, 128))
+    table = torch.tensor([[3, 0, 5], [6, 1, 2]], dtype=torch.int32)
+    old = torch.tensor([130, 64], dtype=torch.int32)
+    out, lse, k_after, v_after = oracle.decode_step_indexed(q, kcache, vcache, knew, vnew, old, block_table=table)
+    gathered_k, gathered_v = kcache[table.long()].flatten(1, 2), vcache[table.long()].flatten(1, 2)
+    want_o, want_lse, _, _ = oracle.decode_step(q, gathered_k, gathered_v, knew, vnew, old)
+    assert torch.equal(out, want_o) and torch.equal(lse, want_lse)
+    changed = (k_after != kcache).any(dim=(2, 3)).nonzero().tolist()
+    assert changed == [[1, 0], [5, 2]]  # row 64 of sequence 1 -> page 1 row 0; row 130 of sequence 0 -> page 5 row 2
+    assert torch.equal(k_after[5, 2], knew[0, 0]) and torch.equal(v_after[1, 0], vnew[1, 0])
+
+    slots = torch.tensor([4, 1], dtype=torch.int32)
+    old = torch.tensor([10, 63], dtype=torch.int32)
+    out, lse, k_after, _ = oracle.decode_step_indexed(q, kcache, vcache, knew, vnew, old, cache_batch_idx=slots)
+    want_o, want_lse, _, _ = oracle.decode_step(q, kcache[slots.long()], vcache[slots.long()], knew, vnew, old)
+    assert torch.equal(out, want_o) and torch.equal(lse, want_lse)
+    assert (k_after != kcache).any(dim=(2, 3)).nonzero().tolist() == [[1, 63], [4, 10]]
+    with pytest.raises(ValueError):
+        oracle.decode_step_indexed(q, kcache, vcache, knew, vnew, old)

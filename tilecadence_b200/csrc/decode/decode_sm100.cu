@@ -90,7 +90,29 @@ struct DecodeParams {
     float scale, scale_log2;
     uint8_t* peer_blocks[kMaxPeers];  // partial == 2: every rank's exchange block as mapped here
     int world, rank;
+    // Indexed caches (ab_fused_splitkv.cuh:92-103). block_table != nullptr: the caches are pages
+    // [cache_slots, page_size, Hkv, 128] and row r of sequence b lives in page
+    // block_table[b * table_stride + r / page_size]; `capacity` is then pages_per_seq * page_size.
+    // Otherwise cache_batch_idx (if set) picks the cache slot of sequence b and page_size == capacity.
+    const int32_t* block_table;
+    const int32_t* cache_batch_idx;
+    int64_t table_stride;
+    int page_size, cache_slots;
 };
+
+// Cache slot (page, or batch entry of the cache tensor) and row inside it for logical row `row`.
+__device__ __forceinline__ void locate_row(const DecodeParams& p, int b, int slot_of_b, int row, int& slot, int& local) {
+    if (p.block_table) {
+        const int page = row / p.page_size;
+        int id = __ldg(p.block_table + int64_t(b) * p.table_stride + page);
+        id = id < 0 ? 0 : (id >= p.cache_slots ? p.cache_slots - 1 : id);  // never leave the allocation
+        slot = id;
+        local = row - page * p.page_size;
+    } else {
+        slot = slot_of_b;
+        local = row;
+    }
+}
 
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
 
@@ -173,6 +195,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     const int64_t append_local = old_len - p.shard_start;
     const bool do_append = p.append && append_local >= 0 && append_local < p.capacity;
     const int append_row = do_append ? int(append_local) : -1;
+    int slot_of_b = b;
+    if (p.cache_batch_idx) {
+        slot_of_b = __ldg(p.cache_batch_idx + b);
+        slot_of_b = slot_of_b < 0 ? 0 : (slot_of_b >= p.cache_slots ? p.cache_slots - 1 : slot_of_b);
+    }
 
     const int tiles = (n_valid + kTileN - 1) / kTileN;
     const int tile_begin = int((int64_t(split) * tiles) / p.splits);
@@ -183,22 +210,41 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
 
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------------ producer warp
-        if (lane == 0 && n_tiles > 0) {
-            const uint64_t policy = tc::policy_evict_first();
-            for (int it = 0; it < n_tiles; ++it) {
-                const int stage = (n_tiles - 1 - it) % kStages;  // the last tile always lands in stage 0
-                const uint32_t generation = uint32_t(it / kStages);
-                if (!tc::mbar_wait(&empty[stage], (generation & 1) ^ 1)) {
-                    atomicCAS(p.status, 0, 1);
-                    break;
+        const uint64_t policy = tc::policy_evict_first();
+        auto issue_tile = [&](int it, int slot, int row0) {
+            const int stage = (n_tiles - 1 - it) % kStages;  // the last tile always lands in stage 0
+            const uint32_t generation = uint32_t(it / kStages);
+            if (!tc::mbar_wait(&empty[stage], (generation & 1) ^ 1)) {
+                atomicCAS(p.status, 0, 1);
+                return false;
+            }
+            uint8_t* base = smem + stage * kStageBytes;
+            tc::mbar_arrive_expect_tx(&full[stage], kStageBytes);
+            tc::tma_load_4d(base, &vmap, &full[stage], 0, kvh, row0, slot, policy);
+            tc::tma_load_4d(base + kHalfBytes, &vmap, &full[stage], 64, kvh, row0, slot, policy);
+            tc::tma_load_4d(base + kVBytes, &kmap, &full[stage], 0, kvh, row0, slot, policy);
+            tc::tma_load_4d(base + kVBytes + kHalfBytes, &kmap, &full[stage], 64, kvh, row0, slot, policy);
+            return true;
+        };
+        if (!p.block_table) {
+            if (lane == 0) {
+                for (int it = 0; it < n_tiles; ++it)
+                    if (!issue_tile(it, slot_of_b, (tile_begin + it) * kTileN)) break;
+            }
+        } else {
+            // Paged cache: the whole warp looks up the pages of the next 32 tiles with one coalesced
+            // load, so the table's latency is paid once per 32 tiles and not once per tile.
+            bool ok = true;
+            for (int first = 0; first < n_tiles && ok; first += 32) {
+                int slot = 0, local = 0;
+                if (first + lane < n_tiles) locate_row(p, b, slot_of_b, (tile_begin + first + lane) * kTileN, slot, local);
+                const int count = min(32, n_tiles - first);
+                for (int j = 0; j < count && ok; ++j) {
+                    const int tile_slot = __shfl_sync(0xffffffffu, slot, j);
+                    const int tile_row0 = __shfl_sync(0xffffffffu, local, j);
+                    if (lane == 0) ok = issue_tile(first + j, tile_slot, tile_row0);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
                 }
-                uint8_t* base = smem + stage * kStageBytes;
-                const int row0 = (tile_begin + it) * kTileN;
-                tc::mbar_arrive_expect_tx(&full[stage], kStageBytes);
-                tc::tma_load_4d(base, &vmap, &full[stage], 0, kvh, row0, b, policy);
-                tc::tma_load_4d(base + kHalfBytes, &vmap, &full[stage], 64, kvh, row0, b, policy);
-                tc::tma_load_4d(base + kVBytes, &kmap, &full[stage], 0, kvh, row0, b, policy);
-                tc::tma_load_4d(base + kVBytes + kHalfBytes, &kmap, &full[stage], 64, kvh, row0, b, policy);
             }
         }
         return;
@@ -247,7 +293,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
                 (is_v ? p.vnew : p.knew) + (int64_t(b) * p.kv_heads + kvh) * kDim) + chunk);
             *reinterpret_cast<uint4*>((is_v ? vbase : kbase) + swizzled(r, chunk)) = value;
             __nv_bfloat16* cache = is_v ? p.vcache : p.kcache;
-            reinterpret_cast<uint4*>(cache + ((int64_t(b) * p.capacity + append_row) * p.kv_heads + kvh) * kDim)[chunk] =
+            int slot, local;
+            locate_row(p, b, slot_of_b, append_row, slot, local);
+            reinterpret_cast<uint4*>(cache + ((int64_t(slot) * p.page_size + local) * p.kv_heads + kvh) * kDim)[chunk] =
                 value;
             tc::fence_proxy_async_smem();
             __syncwarp();
@@ -591,6 +639,14 @@ struct PeerArgs {
     int world, rank;
 };
 
+struct IndexedCache {
+    const int32_t* block_table;     // [B, pages_per_seq] (row stride table_stride) or nullptr
+    int64_t table_stride, pages_per_seq;
+    const int32_t* cache_batch_idx;  // [B] or nullptr
+    int64_t cache_slots;             // pages, or batch entries of the cache tensors
+    int64_t slot_rows;               // rows per slot: the page size, or the capacity
+};
+
 struct MapKey {
     const void* base;
     int64_t batch, capacity, kv_heads;
@@ -631,7 +687,8 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
                   const void* vnew, const int32_t* old_lengths, void* out, float* lse, float* partial_o,
                   float* workspace_o, int64_t workspace_o_elems, float* workspace_lse, int64_t workspace_lse_elems,
                   int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping, int append,
-                  int partial, int64_t shard_start, const PeerArgs* peer = nullptr) {
+                  int partial, int64_t shard_start, const PeerArgs* peer = nullptr,
+                  const IndexedCache* indexed = nullptr) {
     tc::DeviceInfo info;
     int splits = 1;
     int status = check_geometry(device, batch, capacity, kv_heads, num_splits, mapping, append, &info, &splits);
@@ -654,7 +711,25 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
     }
     const int64_t q_heads = kv_heads * kGroup;
     const int64_t rows = batch * q_heads;
-    const size_t q_bytes = size_t(rows) * kDim * 2, cache_bytes = size_t(batch) * capacity * kv_heads * kDim * 2;
+    const int64_t cache_slots = indexed ? indexed->cache_slots : batch;
+    const int64_t slot_rows = indexed ? indexed->slot_rows : capacity;
+    if (indexed) {
+        TC_REQUIRE(!(indexed->block_table && indexed->cache_batch_idx),
+                   "a paged cache is indexed by its block table only: cache_batch_idx must be null");
+        TC_REQUIRE(partial == 0 && shard_start == 0, "indexed caches are not combined with KV-sequence sharding");
+        TC_REQUIRE(cache_slots >= 1 && cache_slots <= (int64_t(1) << 30) && slot_rows >= 4, "cache tensor geometry out of range");
+        if (indexed->block_table) {
+            TC_REQUIRE(slot_rows % kTileN == 0, "page size must be a multiple of 64 rows");
+            TC_REQUIRE(indexed->pages_per_seq >= 1 && indexed->table_stride >= indexed->pages_per_seq &&
+                           capacity == indexed->pages_per_seq * slot_rows,
+                       "block table must be [B, pages_per_seq] with capacity = pages_per_seq * page_size");
+            TC_REQUIRE(reinterpret_cast<uintptr_t>(indexed->block_table) % 4 == 0, "misaligned block table");
+        } else {
+            TC_REQUIRE(indexed->cache_batch_idx && slot_rows == capacity, "cache_batch_idx required");
+            TC_REQUIRE(reinterpret_cast<uintptr_t>(indexed->cache_batch_idx) % 4 == 0, "misaligned cache_batch_idx");
+        }
+    }
+    const size_t q_bytes = size_t(rows) * kDim * 2, cache_bytes = size_t(cache_slots) * slot_rows * kv_heads * kDim * 2;
     const size_t new_bytes = size_t(batch) * kv_heads * kDim * 2;
     TC_REQUIRE(cache_bytes <= (size_t(1) << 40), "cache allocation is outside the supported range");
     const int64_t need_o = splits > 1 ? int64_t(splits) * rows * kDim : 0, need_lse = splits > 1 ? int64_t(splits) * rows : 0;
@@ -682,9 +757,9 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
     status = tc::device_scratch(device, &scratch);
     if (status != TC_OK) return status;
     CUtensorMap kmap, vmap;
-    status = cache_map(device, kcache, batch, capacity, kv_heads, &kmap);
+    status = cache_map(device, kcache, cache_slots, slot_rows, kv_heads, &kmap);
     if (status != TC_OK) return status;
-    status = cache_map(device, vcache, batch, capacity, kv_heads, &vmap);
+    status = cache_map(device, vcache, cache_slots, slot_rows, kv_heads, &vmap);
     if (status != TC_OK) return status;
 
     DecodeParams p{};
@@ -697,6 +772,13 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
     p.out = static_cast<__nv_bfloat16*>(out);
     p.lse = lse;
     p.partial_o = partial_o;
+    p.page_size = int(slot_rows);
+    p.cache_slots = int(cache_slots);
+    if (indexed) {
+        p.block_table = indexed->block_table;
+        p.table_stride = indexed->table_stride;
+        p.cache_batch_idx = indexed->cache_batch_idx;
+    }
     p.ws_o = workspace_o;
     p.ws_lse = workspace_lse;
     p.tickets = scratch.tickets;
@@ -811,6 +893,8 @@ int decode_static(int device, void* stream, const void* q, void* kcache, void* v
     p.append = append ? 1 : 0;
     p.partial = 0;
     p.shard_start = 0;
+    p.page_size = int(capacity);
+    p.cache_slots = int(batch);
     p.scale = 1.f / std::sqrt(128.f);
     p.scale_log2 = p.scale * float(M_LOG2E);
     return mapping == 1 ? launch<true>(kmap, vmap, p, static_cast<cudaStream_t>(stream))
@@ -907,6 +991,22 @@ int tc_decode_forward_out_static(int device, void* stream, const void* q, void* 
                                  int64_t mapping, int append) {
     return decode_static(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, batch, capacity,
                          kv_heads, num_splits, mapping, append);
+}
+
+int tc_decode_indexed_forward_out(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                                  const void* vnew, const int32_t* old_lengths, void* out, float* lse,
+                                  float* workspace_o, int64_t workspace_o_elems, float* workspace_lse,
+                                  int64_t workspace_lse_elems, int64_t batch, int64_t cache_slots, int64_t slot_rows,
+                                  int64_t kv_heads, int64_t num_splits, int64_t mapping, int append,
+                                  const int32_t* block_table, int64_t block_table_stride, int64_t pages_per_seq,
+                                  const int32_t* cache_batch_idx) {
+    TC_REQUIRE(block_table || cache_batch_idx, "pass a block table or cache_batch_idx (or use tc_decode_forward_out)");
+    TC_REQUIRE(slot_rows >= 1 && pages_per_seq >= 0 && pages_per_seq <= (int64_t(1) << 24), "geometry out of range");
+    const IndexedCache indexed{block_table, block_table_stride, pages_per_seq, cache_batch_idx, cache_slots, slot_rows};
+    const int64_t capacity = block_table ? pages_per_seq * slot_rows : slot_rows;
+    return decode_common(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, nullptr, workspace_o,
+                         workspace_o_elems, workspace_lse, workspace_lse_elems, batch, capacity, kv_heads, num_splits,
+                         mapping, append, 0, 0, nullptr, &indexed);
 }
 
 int tc_peer_block_bytes(int64_t batch, int64_t kv_heads, int64_t world, int64_t* bytes) {

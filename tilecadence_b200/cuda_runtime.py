@@ -179,6 +179,10 @@ class Library:
         "tc_decode_partial_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, ctypes.c_int64)),
+        "tc_decode_indexed_forward_out": (ctypes.c_int, (
+            ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
+            ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 6, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64,
+            ctypes.c_int64, ctypes.c_void_p)),
         "tc_decode_exchange_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, *[ctypes.c_int64] * 3,
@@ -465,6 +469,52 @@ class DecodeOps:
             _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse), workspace_lse.numel(),
             q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping), int(bool(append)),
             int(kv_shard_start))
+
+    def indexed_forward_out(self, q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse,
+                            num_splits, mapping, append, block_table=None, cache_batch_idx=None):
+        """Decode step over paged caches (``block_table`` int32 [B, pages_per_seq]; caches
+        [pages, page_size, Hkv, 128]) or over caches whose batch entry is picked per sequence
+        (``cache_batch_idx`` int32 [B]). The workspace is sized as for a contiguous cache of the
+        sequence capacity: ``workspace_spec`` takes any tensor of shape [B, capacity, Hkv, 128]-like
+        geometry, see :meth:`indexed_workspace_spec`."""
+        import torch
+
+        _require((block_table is None) != (cache_batch_idx is None), "pass exactly one of block_table / cache_batch_idx")
+        _require(q.is_cuda and q.dtype == torch.bfloat16 and q.dim() == 4 and q.size(1) == 1 and q.size(3) == 128
+                 and q.size(2) == self.q_heads and q.is_contiguous(), "Q must be contiguous BF16[B,1,Hq,128]")
+        _require(kcache.device == q.device and kcache.dtype == q.dtype and kcache.dim() == 4 and kcache.size(3) == 128
+                 and kcache.size(2) * 4 == q.size(2) and kcache.is_contiguous() and vcache.shape == kcache.shape
+                 and vcache.device == q.device and vcache.dtype == q.dtype and vcache.is_contiguous(),
+                 "caches must be contiguous BF16[slots,rows,Hkv,128]")
+        for tensor in (knew, vnew):
+            _require(tensor.device == q.device and tensor.dtype == q.dtype and tensor.is_contiguous()
+                     and tuple(tensor.shape) == (q.size(0), 1, kcache.size(2), 128), "knew/vnew must be BF16[B,1,Hkv,128]")
+        _require(old_lengths.device == q.device and old_lengths.dtype == torch.int32 and old_lengths.is_contiguous()
+                 and tuple(old_lengths.shape) == (q.size(0),), "old_lengths must be contiguous int32[B]")
+        for workspace in (workspace_o, workspace_lse):
+            _require(workspace.is_cuda and workspace.device == q.device and workspace.dtype == torch.float32
+                     and workspace.is_contiguous(), "Contiguous CUDA FP32 workspace required")
+        self._check_out(q, out, lse)
+        index = block_table if block_table is not None else cache_batch_idx
+        _require(index.device == q.device and index.dtype == torch.int32 and index.size(0) == q.size(0)
+                 and index.dim() == (2 if block_table is not None else 1) and index.stride(-1) == 1,
+                 "block_table must be int32[B,pages] / cache_batch_idx int32[B] with a contiguous last dimension")
+        pages = block_table.size(1) if block_table is not None else 0
+        self.library.call(
+            "tc_decode_indexed_forward_out", q.device.index, _stream(q), _pointer(q), _pointer(kcache), _pointer(vcache),
+            _pointer(knew), _pointer(vnew), _pointer(old_lengths), _pointer(out), _pointer(lse),
+            _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse), workspace_lse.numel(),
+            q.size(0), kcache.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping), int(bool(append)),
+            _pointer(block_table) if block_table is not None else None,
+            block_table.stride(0) if block_table is not None else 0, pages,
+            _pointer(cache_batch_idx) if cache_batch_idx is not None else None)
+
+    def indexed_workspace_spec(self, batch, capacity, kv_heads, device_index, num_splits=0, mapping=1, append=True):
+        """``[splits, workspace_o elements, workspace_lse elements]`` for a sequence capacity."""
+        spec = (ctypes.c_int64 * 3)()
+        self.library.call("tc_decode_workspace_spec", int(device_index), int(batch), int(capacity), int(kv_heads),
+                          int(num_splits), int(mapping), int(bool(append)), spec)
+        return list(spec)
 
     def exchange_out(self, q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse,
                      num_splits, mapping, append, kv_shard_start, rank, peer_blocks):
