@@ -166,10 +166,11 @@ int tc_decode_indexed_forward_out(int device, void* stream, const void* q, void*
 /* Fused variant of tc_decode_partial_out + all-gather + tc_combine_partials for the ranks of one
  * node (one process per GPU, every GPU a peer of every other over NVLink); no counterpart in the
  * reference. One launch per rank: the CTA that finishes a (batch, KV head) unit stores this rank's
- * partial O and LSE into every rank's exchange block with plain peer stores, publishes the unit's
- * epoch there with a system-scope release, waits (bounded: 2 s, then tc_device_status != 0) for the
- * same epoch from every rank in its own block, and merges the `world` partials with the arithmetic
- * of tc_combine_partials. Every rank ends with the full result in out (BF16 [B,1,Hq,128]) and lse
+ * partial O and LSE into every rank's exchange block with plain peer stores, every 4-byte value
+ * paired with the call's epoch in one aligned 8-byte word, then polls its own block (bounded: 2 s,
+ * then tc_device_status != 0) until the words of every rank carry that epoch, and merges the `world`
+ * partials with the arithmetic of tc_combine_partials. No fence or separate flag sits between a
+ * store and its remote read. Every rank ends with the full result in out (BF16 [B,1,Hq,128]) and lse
  * (fp32 [B,Hq]). peer_blocks[r] is rank r's exchange block as mapped into this process
  * (peer_blocks[rank] is this rank's own block). All ranks must make the same sequence of calls with
  * the same batch, kv_heads and world on the same blocks. splits * Hkv * B CTAs must be resident at

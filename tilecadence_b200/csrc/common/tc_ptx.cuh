@@ -93,26 +93,26 @@ __device__ __forceinline__ int atomic_add_acq_rel(int* address, int value) {
     return old;
 }
 
-// System-scope flag words: written into another GPU's memory over NVLink (plain peer stores) and
-// polled by the owner. The release makes every store this thread has observed (its own and, through
-// a preceding CTA barrier, its CTA's) visible before the flag; the acquire orders the owner's
-// later loads after it.
-__device__ __forceinline__ void store_release_sys(uint32_t* address, uint32_t value) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(address), "r"(value) : "memory");
+// Flag-in-data words for low-latency exchange through another GPU's memory (plain peer stores over
+// NVLink): every aligned 8-byte word carries 4 bytes of payload and a 4-byte flag, and an aligned
+// 8-byte store is never torn, so a reader that sees the expected flag in a word also sees that word's
+// payload. No fence and no separate flag round trip is needed. The volatile forms bypass L1.
+__device__ __forceinline__ void store_flagged_2(void* address, uint32_t d0, uint32_t d1, uint32_t flag) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(address), "r"(d0), "r"(flag), "r"(d1), "r"(flag)
+                 : "memory");
 }
-__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* address) {
-    uint32_t value;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(address) : "memory");
-    return value;
+__device__ __forceinline__ void store_flagged_1(void* address, uint32_t d0, uint32_t flag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(address), "r"(d0), "r"(flag) : "memory");
 }
-// Bounded wait for a monotonically increasing flag word to reach `target` (wrap-safe comparison).
-__device__ __forceinline__ bool flag_wait_sys(const uint32_t* address, uint32_t target) {
-    if (int32_t(load_acquire_sys(address) - target) >= 0) return true;
-    const uint64_t start = global_timer_ns();
-    for (uint32_t poll = 1;; ++poll) {
-        if (int32_t(load_acquire_sys(address) - target) >= 0) return true;
-        if ((poll & 15u) == 0 && global_timer_ns() - start > TC_WAIT_LIMIT_NS) return false;
-    }
+__device__ __forceinline__ uint4 load_volatile_16(const void* address) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(address) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint2 load_volatile_8(const void* address) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(address) : "memory");
+    return v;
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -39,18 +39,16 @@ constexpr int kBarrierBytes = 256;
 // Cross-GPU exchange of per-rank partials (KV sequence sharded over the ranks of one node). Every
 // rank owns one exchange block that all ranks map; its layout for `world` ranks and `units` =
 // batch * KV heads is
-//   slots  [2 epoch parities][world source ranks][units] x kPeerSlotFloats fp32
-//          (4 rows x 128 partial O, 4 partial LSE, padding to a 16-byte multiple)
-//   flags  [world source ranks][units] u32   last epoch whose slot the source has published
-//   epochs [units] u32                       calls completed by the owner (owner-private)
+//   slots  [2 epoch parities][world source ranks][units] x kPeerSlotBytes
+//          flag-in-data words: thread t of the unit's 128 writes 32 bytes at t*32
+//          {o.x, epoch, o.y, epoch, o.z, epoch, o.w, epoch}; the four partial LSE follow at 4096 + row*8
+//          as {lse, epoch}
+//   epochs [units] u32   calls completed by the owner (owner-private)
 constexpr int kMaxPeers = 8;
-constexpr int kPeerSlotFloats = kGroup * kDim + 16;
-constexpr int kPeerSlotBytes = kPeerSlotFloats * 4;
-__host__ __device__ constexpr size_t peer_flags_offset(int world, int units) {
-    return size_t(2) * world * units * kPeerSlotBytes;
-}
+constexpr int kPeerLseOffset = kGroup * kDim * 8;
+constexpr int kPeerSlotBytes = kPeerLseOffset + 64;
 __host__ __device__ constexpr size_t peer_epochs_offset(int world, int units) {
-    return peer_flags_offset(world, units) + size_t(world) * units * 4;
+    return size_t(2) * world * units * kPeerSlotBytes;
 }
 __host__ __device__ constexpr size_t peer_block_bytes(int world, int units) {
     return (peer_epochs_offset(world, units) + size_t(units) * 4 + 255) / 256 * 256;
@@ -127,28 +125,42 @@ __device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk16) {
 // LSE = -inf and may hold anything: it is never multiplied. A row nobody saw gets O = 0, LSE = +inf.
 // Both the standalone combine kernel and the in-launch cross-GPU merge use this one function, so
 // the two routes give identical bits.
-template <class LoadLse, class LoadO>
+// kUnroll > 0 visits parts 0..kUnroll-1 with static indices (for operands held in registers) and
+// skips those >= parts; the arithmetic, spelled with explicit roundings, is the same either way.
+template <int kUnroll, class LoadLse, class LoadO>
 __device__ __forceinline__ void lse_weighted_merge(int parts, LoadLse load_lse, LoadO load_o, float4& o, float& lse) {
     float lse_max = -INFINITY;
-    for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, load_lse(s));
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float total = 0.f;
-    if (lse_max != -INFINITY) {
-        for (int s = 0; s < parts; ++s) {
-            const float part_lse = load_lse(s);
-            const float4 v = load_o(s);
-            const bool used = part_lse != -INFINITY;
-            const float weight = used ? __expf(part_lse - lse_max) : 0.f;
-            total += weight;
-            acc.x += used ? weight * v.x : 0.f;
-            acc.y += used ? weight * v.y : 0.f;
-            acc.z += used ? weight * v.z : 0.f;
-            acc.w += used ? weight * v.w : 0.f;
+    auto add = [&](int s) {
+        const float part_lse = load_lse(s);
+        const float4 v = load_o(s);
+        if (part_lse != -INFINITY) {
+            const float weight = __expf(__fsub_rn(part_lse, lse_max));
+            total = __fadd_rn(total, weight);
+            acc.x = __fmaf_rn(weight, v.x, acc.x);
+            acc.y = __fmaf_rn(weight, v.y, acc.y);
+            acc.z = __fmaf_rn(weight, v.z, acc.z);
+            acc.w = __fmaf_rn(weight, v.w, acc.w);
         }
+    };
+    if constexpr (kUnroll > 0) {
+#pragma unroll
+        for (int s = 0; s < kUnroll; ++s)
+            if (s < parts) lse_max = fmaxf(lse_max, load_lse(s));
+        if (lse_max != -INFINITY) {
+#pragma unroll
+            for (int s = 0; s < kUnroll; ++s)
+                if (s < parts) add(s);
+        }
+    } else {
+        for (int s = 0; s < parts; ++s) lse_max = fmaxf(lse_max, load_lse(s));
+        if (lse_max != -INFINITY)
+            for (int s = 0; s < parts; ++s) add(s);
     }
-    const float inv = total > 0.f ? 1.f / total : 0.f;
-    o = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-    lse = total > 0.f ? lse_max + logf(total) : INFINITY;
+    const float inv = total > 0.f ? __frcp_rn(total) : 0.f;
+    o = make_float4(__fmul_rn(acc.x, inv), __fmul_rn(acc.y, inv), __fmul_rn(acc.z, inv), __fmul_rn(acc.w, inv));
+    lse = total > 0.f ? __fadd_rn(lse_max, logf(total)) : INFINITY;
 }
 
 template <bool kHandoff, bool kPeer>
@@ -504,12 +516,13 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     const int64_t out_row = int64_t(b) * q_heads + kvh * kGroup + row;
     if (kPeer) {
         // Cross-GPU merge inside the same launch. This CTA holds this rank's partial for the
-        // (batch, KV head) unit. It stores the partial into every rank's exchange block (plain peer
-        // stores over NVLink, its own block included), publishes the unit's epoch in every block,
-        // waits (bounded) until every rank's partial of the same epoch has landed in its own block
-        // and merges them. Slots alternate with the epoch's parity: a rank can be at most one call
-        // ahead of the slowest reader, because it cannot finish call e+1 before that reader has
-        // published e+1, which the reader does only after it has merged call e.
+        // (batch, KV head) unit. Every thread stores its 16 bytes of the partial, each 4-byte value
+        // paired with the call's epoch, into every rank's exchange block (plain peer stores over
+        // NVLink, its own block included), then polls its own block until the words of every source
+        // rank carry this epoch (bounded), and merges. No fence, barrier or separate flag sits between
+        // the store and the remote read. Slots alternate with the epoch's parity: a rank can be at
+        // most one call ahead of the slowest reader, because it cannot finish call e+1 before that
+        // reader has stored its own e+1 partial, which it does only after it has merged call e.
         const int world = p.world, units = p.batch * p.kv_heads, unit = int(head_slot);
         uint8_t* mine = p.peer_blocks[p.rank];
         uint32_t* epochs = reinterpret_cast<uint32_t*>(mine + peer_epochs_offset(world, units));
@@ -517,34 +530,51 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
         const size_t slot_bytes = (size_t(epoch & 1) * world * units + unit) * kPeerSlotBytes;
         const size_t rank_stride = size_t(units) * kPeerSlotBytes;
         for (int r = 0; r < world; ++r) {
-            float* slot = reinterpret_cast<float*>(p.peer_blocks[r] + slot_bytes + p.rank * rank_stride);
-            *reinterpret_cast<float4*>(slot + row * kDim + col4 * 4) = final_o;
-            if (col4 == 0) slot[kGroup * kDim + row] = final_lse;
+            uint8_t* slot = p.peer_blocks[r] + slot_bytes + p.rank * rank_stride;
+            tc::store_flagged_2(slot + tid * 32, __float_as_uint(final_o.x), __float_as_uint(final_o.y), epoch);
+            tc::store_flagged_2(slot + tid * 32 + 16, __float_as_uint(final_o.z), __float_as_uint(final_o.w), epoch);
+            if (col4 == 0) tc::store_flagged_1(slot + kPeerLseOffset + row * 8, __float_as_uint(final_lse), epoch);
         }
-        __threadfence_system();
-        consumer_barrier();
-        bool arrived = true;
-        if (tid < world) {
-            uint32_t* theirs = reinterpret_cast<uint32_t*>(p.peer_blocks[tid] + peer_flags_offset(world, units));
-            tc::store_release_sys(theirs + p.rank * units + unit, epoch);
-            const uint32_t* flags = reinterpret_cast<const uint32_t*>(mine + peer_flags_offset(world, units));
-            arrived = tc::flag_wait_sys(flags + tid * units + unit, epoch);
+        float4 part_o[kMaxPeers];
+        float part_lse[kMaxPeers];
+#pragma unroll
+        for (int s = 0; s < kMaxPeers; ++s) {
+            part_o[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+            part_lse[s] = -INFINITY;
         }
-        if (!arrived) atomicCAS(p.status, 0, 5);  // a rank never published: the result below is not valid
-        consumer_barrier();
-        const float* slots = reinterpret_cast<const float*>(mine + slot_bytes);
-        const int64_t stride = int64_t(units) * kPeerSlotFloats;
+        uint32_t pending = (1u << world) - 1u;
+        const uint8_t* arrivals = mine + slot_bytes;
+        const uint64_t wait_start = tc::global_timer_ns();
+        for (uint32_t poll = 1; pending; ++poll) {
+#pragma unroll
+            for (int s = 0; s < kMaxPeers; ++s) {
+                if ((pending >> s) & 1u) {
+                    const uint8_t* slot = arrivals + s * rank_stride;
+                    const uint4 lo = tc::load_volatile_16(slot + tid * 32), hi = tc::load_volatile_16(slot + tid * 32 + 16);
+                    const uint2 l = tc::load_volatile_8(slot + kPeerLseOffset + row * 8);
+                    if (lo.y == epoch && lo.w == epoch && hi.y == epoch && hi.w == epoch && l.y == epoch) {
+                        part_o[s] = make_float4(__uint_as_float(lo.x), __uint_as_float(lo.z), __uint_as_float(hi.x),
+                                                __uint_as_float(hi.z));
+                        part_lse[s] = __uint_as_float(l.x);
+                        pending &= ~(1u << s);
+                    }
+                }
+            }
+            if (pending && (poll & 15u) == 0 && tc::global_timer_ns() - wait_start > TC_WAIT_LIMIT_NS) {
+                atomicCAS(p.status, 0, 5);  // a rank never delivered: the result below is not valid
+                break;
+            }
+        }
         float4 merged;
         float merged_lse;
-        lse_weighted_merge(
-            world, [&](int s) { return __ldcg(slots + s * stride + kGroup * kDim + row); },
-            [&](int s) { return __ldcg(reinterpret_cast<const float4*>(slots + s * stride + row * kDim) + col4); },
-            merged, merged_lse);
+        lse_weighted_merge<kMaxPeers>(
+            world, [&](int s) { return part_lse[s]; }, [&](int s) { return part_o[s]; }, merged, merged_lse);
         uint2 packed;
         packed.x = tc::pack_bf16x2(merged.x, merged.y);
         packed.y = tc::pack_bf16x2(merged.z, merged.w);
         *reinterpret_cast<uint2*>(p.out + out_row * kDim + col4 * 4) = packed;
         if (col4 == 0) p.lse[out_row] = merged_lse;
+        consumer_barrier();  // every thread has read the unit's epoch before it moves on
         if (tid == 0) epochs[unit] = epoch;
     } else if (p.partial) {
         *reinterpret_cast<float4*>(p.partial_o + out_row * kDim + col4 * 4) = final_o;
@@ -569,7 +599,7 @@ __global__ void __launch_bounds__(128) combine_partials_kernel(const float* __re
     if (row >= rows) return;
     float4 merged;
     float merged_lse;
-    lse_weighted_merge(
+    lse_weighted_merge<0>(
         parts, [&](int s) { return partial_lse[s * stride_lse + row]; },
         [&](int s) { return reinterpret_cast<const float4*>(partial_o + s * stride_o + row * kDim)[col4]; }, merged,
         merged_lse);
