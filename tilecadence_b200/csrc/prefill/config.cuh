@@ -29,6 +29,12 @@
 #ifndef PREFILL_SPLIT_P
 #define PREFILL_SPLIT_P 1
 #endif
+#ifndef PREFILL_WARP_ARRIVE
+#define PREFILL_WARP_ARRIVE 0
+#endif
+#ifndef PREFILL_SHADOW_CHUNKS
+#define PREFILL_SHADOW_CHUNKS 0
+#endif
 #ifndef PREFILL_EXP_FMA_PAIRS_PER_8
 #define PREFILL_EXP_FMA_PAIRS_PER_8 0
 #endif

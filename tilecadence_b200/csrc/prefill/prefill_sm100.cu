@@ -27,6 +27,7 @@
 #include "tc_ptx.cuh"
 
 #include <cmath>
+#include <type_traits>
 
 namespace {
 
@@ -47,7 +48,8 @@ constexpr int kSoftmaxThreads = 128;
 constexpr int kThreads = 3 * kSoftmaxThreads;   // two softmax warpgroups + one data/MMA warpgroup
 constexpr int kSoftmaxRegisters = 216, kDataRegisters = 72;  // 256*216 + 128*72 = 64512 <= 65536
 constexpr bool kSplitP = PREFILL_SPLIT_P != 0;  // signal the MMA issuer after each 64-key half of P
-constexpr int kEmulatedPairsPer8 = PREFILL_EXP_FMA_PAIRS_PER_8;  // of every 8 key pairs, how many use the FMA-pipe 2^x
+constexpr int kEmulatedPairsPer8 = PREFILL_EXP_FMA_PAIRS_PER_8;
+constexpr int kShadowChunks = PREFILL_SHADOW_CHUNKS;  // leading 32-key chunks exponentiated on the FMA pipes before the turn  // of every 8 key pairs, how many use the FMA-pipe 2^x
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kSColumn = 0, kPColumn = 128, kOColumn = 256;  // S (shared) | P0 P1 | O0 O1
@@ -82,6 +84,20 @@ struct PrefillParams {
     int batch, tokens, q_heads, kv_heads, m_blocks;
     float scale, scale_log2;
 };
+
+// Arrival of a softmax warp on a barrier the MMA issuer waits on. With PREFILL_WARP_ARRIVE one lane
+// arrives for the warp after a warp barrier (every lane has fenced its own tensor-memory accesses
+// first), so the barrier sees 4 arrivals instead of 128 serialised ones.
+constexpr int kArrivals = PREFILL_WARP_ARRIVE ? kSoftmaxThreads / 32 : kSoftmaxThreads;
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+#if PREFILL_WARP_ARRIVE
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive(bar);
+#else
+    (void)lane;
+    tc::mbar_arrive(bar);
+#endif
+}
 
 __device__ __forceinline__ void wg_barrier(int head) {
     asm volatile("bar.sync %0, %1;" ::"r"(head + 1), "n"(kSoftmaxThreads) : "memory");
@@ -143,9 +159,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         }
         for (int h = 0; h < 2; ++h) {
             tc::mbar_init(&bars->s_full[h], 1);
-            tc::mbar_init(&bars->s_free[h], kSoftmaxThreads);
-            tc::mbar_init(&bars->p_half[h][0], kSoftmaxThreads);
-            tc::mbar_init(&bars->p_half[h][1], kSoftmaxThreads);
+            tc::mbar_init(&bars->s_free[h], kArrivals);
+            tc::mbar_init(&bars->p_half[h][0], kArrivals);
+            tc::mbar_init(&bars->p_half[h][1], kArrivals);
             tc::mbar_init(&bars->o_done[h], 1);
             tc::mbar_init(&bars->turn[h], kSoftmaxThreads);
         }
@@ -293,7 +309,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             for (int c = 0; c < 4; ++c) tc::tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
             tc::tmem_wait_ld();
             tc::tc_fence_before_sync();
-            tc::mbar_arrive(&bars->s_free[h]);  // the score buffer may be overwritten by the other head
+            warp_arrive(&bars->s_free[h], lane);  // the score buffer may be overwritten by the other head
             if (it == 0) {
                 // Diagonal tile: key column j is visible to query row i only if j <= i.
 #pragma unroll
@@ -320,21 +336,68 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             }
 #endif
             const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            // Gated rescale: O and l are only brought to a new reference maximum when the row maximum
+            // grew by more than 2^kRescaleThreshold, and only if some row of the warp needs it (the
+            // TMEM accesses are warp-collective). The decision needs only the maxima; the rescale itself
+            // waits for the previous tile's PV further down.
+            float alpha = 1.f;
+            bool rescale = false;
             if (it == 0) {
                 m_used = tile_max;  // finite: column `row` of the diagonal tile is always visible
             } else {
-                // Gated rescale: O and l are only brought to a new reference maximum when the row
-                // maximum grew by more than 2^kRescaleThreshold, and only if some row of the warp
-                // needs it (the TMEM accesses are warp-collective).
                 const float m_new = fmaxf(m_used, tile_max);
                 const bool grow = (m_new - m_used) * p.scale_log2 > kRescaleThreshold;
-                // PV of the previous tile must have finished before its P columns are overwritten
-                // (and before O may be rescaled); it was issued long ago, so this rarely waits.
+                rescale = __any_sync(0xffffffffu, grow);
+                if (rescale) {
+                    const float m_target = grow ? m_new : m_used;
+                    alpha = tc::fast_exp2((m_used - m_target) * p.scale_log2);
+                    m_used = m_target;
+                }
+            }
+            const float neg_bias = -m_used * p.scale_log2;
+            const float2 bias2 = make_float2(neg_bias, neg_bias);
+            float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            // One chunk = 32 keys: x = s*scale - bias on packed pairs, 2^x either on the exponential
+            // unit or (kEmulate) on the FMA pipes, BF16 pack, store to this head's P columns.
+            auto chunk = [&](int c, auto emulate_tag, uint32_t (&packed)[16]) {
+                constexpr bool kEmulate = decltype(emulate_tag)::value;
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+#if PREFILL_PACKED_MATH
+                    float2 x = __ffma2_rn(make_float2(s[c * 32 + j], s[c * 32 + j + 1]), scale2, bias2);
+#else
+                    float2 x = make_float2(fmaf(s[c * 32 + j], p.scale_log2, neg_bias), fmaf(s[c * 32 + j + 1], p.scale_log2, neg_bias));
+#endif
+                    float2 e;
+                    if (kEmulate || (j >> 1) % 8 < kEmulatedPairsPer8) {
+                        x.x = fmaxf(x.x, -125.f);
+                        x.y = fmaxf(x.y, -125.f);
+                        e = exp2_pair_fma(x);
+                    } else {
+                        e.x = tc::fast_exp2(x.x);
+                        e.y = tc::fast_exp2(x.y);
+                    }
+#if PREFILL_PACKED_MATH
+                    sum2[(j >> 1) & 1] = __fadd2_rn(sum2[(j >> 1) & 1], e);
+#else
+                    sum2[(j >> 1) & 1].x += e.x;
+                    sum2[(j >> 1) & 1].y += e.y;
+#endif
+                    packed[j >> 1] = tc::pack_bf16x2(e.x, e.y);
+                }
+            };
+            // While the other head holds the exponential unit this warpgroup would only wait, so it
+            // spends that time on the FMA pipes: the first kShadowChunks chunks of the tile get their
+            // 2^x from the polynomial, which shortens this head's own turn by the same share.
+            uint32_t shadow[kShadowChunks > 0 ? kShadowChunks : 1][16];
+#pragma unroll
+            for (int c = 0; c < kShadowChunks; ++c) chunk(c, std::true_type{}, shadow[c]);
+            if (it > 0) {
+                // PV of the previous tile must have finished before its P columns are overwritten and
+                // before O may be rescaled; it was issued long ago, so this rarely waits.
                 if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1);
                 tc::tc_fence_after_sync();
-                if (__any_sync(0xffffffffu, grow)) {
-                    const float m_target = grow ? m_new : m_used;
-                    const float alpha = tc::fast_exp2((m_used - m_target) * p.scale_log2);
+                if (rescale) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t acc[32];
@@ -346,8 +409,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     }
                     tc::tmem_wait_st();
                     l *= alpha;
-                    m_used = m_target;
                 }
+            }
+#pragma unroll
+            for (int c = 0; c < kShadowChunks; ++c) tc::tmem_st16(p_tmem + c * 16, shadow[c]);
+            if (kSplitP && kShadowChunks >= 2) {
+                tc::tmem_wait_st();
+                tc::tc_fence_before_sync();
+                warp_arrive(&bars->p_half[h][0], lane);
             }
 #if PREFILL_PINGPONG
             // The exponential unit is the scarcest resource, so the two heads take turns at it: while
@@ -364,42 +433,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
 #endif
             }
 #endif
-            const float neg_bias = -m_used * p.scale_log2;
-            const float2 bias2 = make_float2(neg_bias, neg_bias);
-            float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-            // Four chunks of 32 keys. Each chunk: x = s*scale - bias on packed pairs, 2^x partly on the
-            // exponential unit and partly on the FMA pipes, BF16 pack, store over the S columns.
-            // Two mbarriers tell the MMA warp when each 64-key half of P is complete.
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = kShadowChunks; c < 4; ++c) {
                 uint32_t packed[16];
-#pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-#if PREFILL_PACKED_MATH
-                    float2 x = __ffma2_rn(make_float2(s[c * 32 + j], s[c * 32 + j + 1]), scale2, bias2);
-#else
-                    float2 x = make_float2(fmaf(s[c * 32 + j], p.scale_log2, neg_bias), fmaf(s[c * 32 + j + 1], p.scale_log2, neg_bias));
-#endif
-                    float2 e;
-                    if ((j >> 1) % 8 < kEmulatedPairsPer8) {
-                        x.x = fmaxf(x.x, -125.f);
-                        x.y = fmaxf(x.y, -125.f);
-                        e = exp2_pair_fma(x);
-                    } else {
-                        e.x = tc::fast_exp2(x.x);
-                        e.y = tc::fast_exp2(x.y);
-                    }
-#if PREFILL_PACKED_MATH
-                    sum2[(j >> 1) & 1] = __fadd2_rn(sum2[(j >> 1) & 1], e);
-#else
-                    sum2[(j >> 1) & 1].x += e.x;
-                    sum2[(j >> 1) & 1].y += e.y;
-#endif
-                    packed[j >> 1] = tc::pack_bf16x2(e.x, e.y);
-                }
+                chunk(c, std::false_type{}, packed);
 #if PREFILL_PINGPONG
-                // Hand the exponential unit over a little before this head's last exponentials drain:
-                // the other warpgroup needs about a hundred cycles to wake up.
+                // Hand the exponential unit over when this head's last exponentials are issued: the
+                // other warpgroup needs about a hundred cycles to wake up.
 #if PREFILL_TURN_NAMED
                 if (c == PREFILL_TURN_CHUNK && (h == 0 || it + 1 < n_tiles))
                     asm volatile("bar.arrive %0, 256;" ::"r"(3 + (1 - h)) : "memory");
@@ -407,18 +447,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 if (c == PREFILL_TURN_CHUNK) tc::mbar_arrive(&bars->turn[1 - h]);
 #endif
 #endif
-                if (kSplitP && c == 2) {
+                if (kSplitP && kShadowChunks < 2 && c == 2) {
                     // Chunks 0 and 1 were stored a whole chunk of arithmetic ago, so this wait is short.
                     tc::tmem_wait_st();
                     tc::tc_fence_before_sync();
-                    tc::mbar_arrive(&bars->p_half[h][0]);
+                    warp_arrive(&bars->p_half[h][0], lane);
                 }
                 tc::tmem_st16(p_tmem + c * 16, packed);
             }
             tc::tmem_wait_st();
             tc::tc_fence_before_sync();
-            if (!kSplitP) tc::mbar_arrive(&bars->p_half[h][0]);
-            tc::mbar_arrive(&bars->p_half[h][1]);
+            if (!kSplitP) warp_arrive(&bars->p_half[h][0], lane);
+            warp_arrive(&bars->p_half[h][1], lane);
             l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
         }
 
