@@ -29,6 +29,9 @@
 #ifndef PREFILL_SPLIT_P
 #define PREFILL_SPLIT_P 1
 #endif
+#ifndef PREFILL_EARLY_P
+#define PREFILL_EARLY_P 1
+#endif
 #ifndef PREFILL_WARP_ARRIVE
 #define PREFILL_WARP_ARRIVE 0
 #endif

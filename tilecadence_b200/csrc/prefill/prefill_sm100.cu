@@ -49,6 +49,7 @@ constexpr int kThreads = 3 * kSoftmaxThreads;   // two softmax warpgroups + one 
 constexpr int kSoftmaxRegisters = 216, kDataRegisters = 72;  // 256*216 + 128*72 = 64512 <= 65536
 constexpr bool kSplitP = PREFILL_SPLIT_P != 0;  // signal the MMA issuer after each 64-key half of P
 constexpr int kEmulatedPairsPer8 = PREFILL_EXP_FMA_PAIRS_PER_8;
+constexpr bool kEarlyP = PREFILL_EARLY_P != 0;  // rewrite the first half of P as soon as the first half of PV is done
 constexpr int kShadowChunks = PREFILL_SHADOW_CHUNKS;  // leading 32-key chunks exponentiated on the FMA pipes before the turn  // of every 8 key pairs, how many use the FMA-pipe 2^x
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr uint32_t kTmemColumns = 512;
@@ -72,11 +73,12 @@ constexpr int shared_bytes(bool handoff) { return 1024 + kBarrierOffset + kBarri
 struct Barriers {
     uint64_t q_full;
     uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-    uint64_t s_full[2], s_free[2], p_half[2][2], o_done[2], turn[2];
+    uint64_t s_full[2], s_free[2], p_half[2][2], p_lo_free[2], o_done[2], turn[2];
     uint32_t tmem_base;
     int32_t abort;
 };
 static_assert(sizeof(Barriers) <= kBarrierBytes, "barrier block");
+static_assert(PREFILL_SHADOW_CHUNKS <= 2, "pre-turn chunks must stay inside the first half of P");
 
 struct PrefillParams {
     float* lse;
@@ -163,6 +165,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             tc::mbar_init(&bars->p_half[h][0], kArrivals);
             tc::mbar_init(&bars->p_half[h][1], kArrivals);
             tc::mbar_init(&bars->o_done[h], 1);
+            tc::mbar_init(&bars->p_lo_free[h], 1);
             tc::mbar_init(&bars->turn[h], kSoftmaxThreads);
         }
         bars->abort = 0;
@@ -255,6 +258,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 if (!tc::mbar_wait(&bars->p_half[h][0], uint32_t(it) & 1)) return false;
                 tc::tc_fence_after_sync();
                 issue_pv_half(it, 0);
+                if (kEarlyP) tc::umma_commit(&bars->p_lo_free[h]);  // P columns of the first 64 keys may be rewritten
                 if (!tc::mbar_wait(&bars->p_half[h][1], uint32_t(it) & 1)) return false;
                 tc::tc_fence_after_sync();
                 issue_pv_half(it, 1);
@@ -392,10 +396,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             uint32_t shadow[kShadowChunks > 0 ? kShadowChunks : 1][16];
 #pragma unroll
             for (int c = 0; c < kShadowChunks; ++c) chunk(c, std::true_type{}, shadow[c]);
+            // PV of the previous tile reads P: its first half (keys 0-63, P chunks 0 and 1) must be done
+            // before chunk 0 is rewritten, all of it before chunk 2 is rewritten or O is rescaled. Waiting
+            // only for the first half here takes the second half's execution off this head's
+            // exp -> PV -> exp chain; the full wait follows before chunk 2, by when it has long finished.
+            bool pv_done = it == 0;
             if (it > 0) {
-                // PV of the previous tile must have finished before its P columns are overwritten and
-                // before O may be rescaled; it was issued long ago, so this rarely waits.
-                if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1);
+                if (!kEarlyP || rescale) {
+                    if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1);
+                    pv_done = true;
+                } else {
+                    if (ok) ok = tc::mbar_wait(&bars->p_lo_free[h], uint32_t(it - 1) & 1);
+                }
                 tc::tc_fence_after_sync();
                 if (rescale) {
 #pragma unroll
@@ -452,6 +464,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     tc::tmem_wait_st();
                     tc::tc_fence_before_sync();
                     warp_arrive(&bars->p_half[h][0], lane);
+                }
+                if (c == 2 && !pv_done) {
+                    if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1);
+                    tc::tc_fence_after_sync();
+                    pv_done = true;
                 }
                 tc::tmem_st16(p_tmem + c * 16, packed);
             }
