@@ -163,6 +163,20 @@ int tc_decode_indexed_forward_out(int device, void* stream, const void* q, void*
                                   const int32_t* block_table, int64_t block_table_stride, int64_t pages_per_seq,
                                   const int32_t* cache_batch_idx);
 
+/* tc_decode_forward_out for callers whose q and knew are NOT yet rotated: the step before attention in the
+ * reference's pipeline ("the host passes pre-rotated Q/K", ab_fused_splitkv.cuh:189) folded into the decode
+ * launch. The kernel applies rotate-half rotary position embedding to every query head and to the new K
+ * row for position old_lengths[b], attends with the rotated q, and appends the rotated K row (V is copied
+ * as is). rope_cos / rope_sin are FP32 [rope_positions, 64] (the 64 distinct frequencies; row = position,
+ * clamped to the table), 16-byte aligned. For i < 64: x'[i] = x[i]*cos[i] - x[i+64]*sin[i],
+ * x'[i+64] = x[i+64]*cos[i] + x[i]*sin[i], every product and sum rounded to FP32 separately and the result
+ * rounded to BF16 (round to nearest even), so a host restatement reproduces the appended row bit for bit. */
+int tc_decode_rope_forward_out(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                               const void* vnew, const int32_t* old_lengths, void* out, float* lse, float* workspace_o,
+                               int64_t workspace_o_elems, float* workspace_lse, int64_t workspace_lse_elems,
+                               int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping,
+                               int append, const float* rope_cos, const float* rope_sin, int64_t rope_positions);
+
 /* Fused variant of tc_decode_partial_out + all-gather + tc_combine_partials for the ranks of one
  * node (one process per GPU, every GPU a peer of every other over NVLink); no counterpart in the
  * reference. One launch per rank: the CTA that finishes a (batch, KV head) unit stores this rank's

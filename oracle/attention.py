@@ -104,6 +104,34 @@ def decode_step(q, kcache, vcache, knew, vnew, old_lengths, append=True, scale=D
     return out, lse, kcache, vcache
 
 
+def rope_tables(positions, theta=1.0e6, dim=64):
+    """cos / sin tables fp32 [positions, dim] of rotary position embedding with base ``theta`` (Qwen3's
+    1e6 by default): angle[p, i] = p * theta ** (-i / dim), computed in float64 and rounded once."""
+    inv_freq = theta ** (-torch.arange(dim, dtype=torch.float64) / dim)
+    angle = torch.arange(positions, dtype=torch.float64)[:, None] * inv_freq[None]
+    return angle.cos().float(), angle.sin().float()
+
+
+def rope_rotate(x, cos, sin):
+    """Rotate-half RoPE of x [..., 128] (any float dtype) with cos/sin [..., 64] broadcastable to it:
+    x'[i] = x[i]*cos[i] - x[i+64]*sin[i], x'[i+64] = x[i+64]*cos[i] + x[i]*sin[i], each product and sum
+    a separate fp32 rounding, result rounded to x's dtype. The published rotate-half form (the one
+    Qwen-style models use); the reference itself receives q and K already rotated
+    (``tilecadence/cuda/decode/ab_fused_splitkv.cuh:189``)."""
+    lo, hi = x[..., :64].float(), x[..., 64:].float()
+    out_lo = lo * cos - hi * sin
+    out_hi = hi * cos + lo * sin
+    return torch.cat([out_lo, out_hi], dim=-1).to(x.dtype)
+
+
+def decode_step_rope(q, kcache, vcache, knew, vnew, old_lengths, cos, sin, append=True, scale=DEFAULT_SCALE):
+    """:func:`decode_step` on un-rotated q / knew: both are rotated for position ``old_lengths[b]``
+    (clamped to the table), rounded to their dtype, and the step runs on the rotated tensors."""
+    position = old_lengths.long().clamp(0, cos.size(0) - 1)
+    c, s = cos[position][:, None, None, :], sin[position][:, None, None, :]  # [B,1,1,64]
+    return decode_step(rope_rotate(q, c, s), kcache, vcache, rope_rotate(knew, c, s), vnew, old_lengths, append, scale)
+
+
 def decode_step_indexed(q, kcache, vcache, knew, vnew, old_lengths, block_table=None, cache_batch_idx=None,
                         append=True, scale=DEFAULT_SCALE):
     """Decode step over indexed caches, by gathering each sequence's rows into a contiguous cache,

@@ -240,6 +240,36 @@ def test_indexed_argument_checks(ops, gpu_device):
     torch.cuda.synchronize()
 
 
+@pytest.mark.parametrize("batch,capacity,lengths,num_splits", [
+    (1, 256, [130], 0),
+    (4, 1024, [1023, 0, 511, 64], 0),
+    (2, 8192, [8191, 4000], 3),
+])
+def test_rotary_embedding_inside_the_launch(ops, gpu_device, batch, capacity, lengths, num_splits):
+    """Un-rotated q / knew + RoPE tables give exactly what the plain entry point gives on inputs rotated
+    (and re-rounded to BF16) on the host: same O and LSE bits, and the appended K row is the rotated row."""
+    q, kcache, vcache, knew, vnew = make_case(500 + capacity, batch, capacity, fill=lengths)
+    old = torch.tensor(lengths, dtype=torch.int32)
+    cos, sin = oracle.rope_tables(capacity)
+    want_o, want_lse, want_k, want_v = oracle.decode_step_rope(q, kcache, vcache, knew, vnew, old, cos, sin)
+    device = gpu_device
+    dq, dk, dv, dkn, dvn, dold = (t.to(device) for t in (q, kcache, vcache, knew, vnew, old))
+    out = torch.full_like(dq, float("nan"))
+    lse = torch.full((batch, 32, 1), float("nan"), device=device, dtype=torch.float32)
+    spec = ops.workspace_spec(dq, dk, dold, num_splits, 1, True)
+    ws = [torch.full((n,), float("nan"), device=device, dtype=torch.float32) for n in spec[1:3]]
+    ops.rope_forward_out(dq, dk, dv, dkn, dvn, dold, out, lse, *ws, num_splits, 1, True, cos.to(device), sin.to(device))
+    torch.cuda.synchronize()
+    assert ops.library.device_status(device.index) == 0
+    oracle.check_outputs(out.cpu(), lse.cpu(), want_o, want_lse)
+    assert torch.equal(bits(dk.cpu()), bits(want_k)) and torch.equal(bits(dv.cpu()), bits(want_v))
+    position = old.long()
+    pc, ps = cos[position][:, None, None, :], sin[position][:, None, None, :]
+    flat_o, flat_lse, _, _, _ = run_step(ops, device, oracle.rope_rotate(q, pc, ps), kcache, vcache,
+                                         oracle.rope_rotate(knew, pc, ps), vnew, old, num_splits=num_splits)
+    assert torch.equal(bits(out.cpu()), bits(flat_o)) and torch.equal(lse.cpu().view(torch.int32), flat_lse.view(torch.int32))
+
+
 def test_in_launch_exchange_with_one_rank(ops, gpu_device):
     """The fused exchange route with a world of one: three consecutive steps (both slot parities and a
     reused slot) must equal the plain entry point bit for bit."""

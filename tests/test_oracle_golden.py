@@ -117,3 +117,35 @@ def test_indexed_caches_equal_the_gathered_contiguous_step():
     assert (k_after != kcache).any(dim=(2, 3)).nonzero().tolist() == [[1, 63], [4, 10]]
     with pytest.raises(ValueError):
         oracle.decode_step_indexed(q, kcache, vcache, knew, vnew, old)
+
+
+def test_rotary_embedding_restatement():
+    """rope_rotate is the published rotate-half form: identity at position 0, the textbook
+    x*cos + rotate_half(x)*sin, a pure rotation of each (i, i+64) pair, and scores that depend only on
+    the distance between the two positions."""
+    cos, sin = oracle.rope_tables(512)
+    assert cos.shape == (512, 64) and torch.all(cos[0] == 1) and torch.all(sin[0] == 0)
+    assert abs(cos[1, 0].item() - 0.5403023) < 1e-6 and abs(sin[1, 0].item() - 0.8414710) < 1e-6  # angle 1 rad
+    x, y = oracle.seeded_normal(12, (3, 1, 8, 128), (3, 1, 8, 128), dtype=torch.float32)
+    position = torch.tensor([0, 17, 511])
+    c, s = cos[position][:, None, None, :], sin[position][:, None, None, :]
+    rotated = oracle.rope_rotate(x, c, s)
+    assert torch.equal(rotated[0], x[0])
+    rotate_half = torch.cat([-x[..., 64:], x[..., :64]], dim=-1)
+    textbook = x * torch.cat([c, c], dim=-1) + rotate_half * torch.cat([s, s], dim=-1)
+    assert torch.allclose(rotated, textbook, rtol=0, atol=1e-6)
+    pair_norm = lambda t: t[..., :64] ** 2 + t[..., 64:] ** 2
+    assert torch.allclose(pair_norm(rotated), pair_norm(x), rtol=1e-5, atol=1e-6)
+    # <R_m x, R_n y> depends on m - n only
+    a = (oracle.rope_rotate(x[:1], cos[40], sin[40]) * oracle.rope_rotate(y[:1], cos[33], sin[33])).sum(-1)
+    b = (oracle.rope_rotate(x[:1], cos[107], sin[107]) * oracle.rope_rotate(y[:1], cos[100], sin[100])).sum(-1)
+    assert torch.allclose(a, b, rtol=1e-4, atol=1e-3)
+    # the fused step is the plain step on rotated, re-rounded inputs
+    kcache, vcache, q, knew, vnew = oracle.seeded_normal(3, (2, 96, 8, 128), (2, 96, 8, 128), (2, 1, 32, 128),
+                                                         (2, 1, 8, 128), (2, 1, 8, 128))
+    old = torch.tensor([40, 95], dtype=torch.int32)
+    got = oracle.decode_step_rope(q, kcache, vcache, knew, vnew, old, cos, sin)
+    pc, ps = cos[old.long()][:, None, None, :], sin[old.long()][:, None, None, :]
+    want = oracle.decode_step(oracle.rope_rotate(q, pc, ps), kcache, vcache, oracle.rope_rotate(knew, pc, ps), vnew, old)
+    assert all(torch.equal(g, w) for g, w in zip(got, want))
+    assert torch.equal(got[2][0, 40], oracle.rope_rotate(knew, pc, ps)[0, 0]) and got[2].dtype == torch.bfloat16

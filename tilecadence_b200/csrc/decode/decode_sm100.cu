@@ -96,7 +96,23 @@ struct DecodeParams {
     const int32_t* cache_batch_idx;
     int64_t table_stride;
     int page_size, cache_slots;
+    // Rotary position embedding applied in the kernel to q and to the appended K row (both arrive
+    // un-rotated): fp32 tables [rope_positions, 64], row = the token's position old_lengths[b].
+    const float* rope_cos;
+    const float* rope_sin;
+    int rope_positions;
 };
+
+// Rotate-half RoPE of one (x[i], x[i + 64]) pair, i < 64, with every product and sum rounded to fp32
+// on its own (no fused multiply-add), so that a host restatement gets the same bits:
+//   lo' = x_lo * cos - x_hi * sin,   hi' = x_hi * cos + x_lo * sin.
+__device__ __forceinline__ void rope_pair(float x_lo, float x_hi, float c, float sn, float& lo, float& hi) {
+    lo = __fsub_rn(__fmul_rn(x_lo, c), __fmul_rn(x_hi, sn));
+    hi = __fadd_rn(__fmul_rn(x_hi, c), __fmul_rn(x_lo, sn));
+}
+__device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+
 
 // Cache slot (page, or batch entry of the cache tensor) and row inside it for logical row `row`.
 __device__ __forceinline__ void locate_row(const DecodeParams& p, int b, int slot_of_b, int row, int& slot, int& local) {
@@ -275,6 +291,27 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
             qa[ks][0] = row_ok ? __ldg(qptr + ks * 8 + quad) : 0u;
             qa[ks][1] = row_ok ? __ldg(qptr + ks * 8 + 4 + quad) : 0u;
         }
+        if (p.rope_cos && row_ok) {
+            // This thread holds columns 16*ks + 2*quad + {0,1} and + 8 + {0,1}; the partner of column
+            // i < 64 is i + 64, i.e. the same slot of fragment ks + 4: the rotation is thread-local.
+            int64_t position = old_len < p.rope_positions ? old_len : p.rope_positions - 1;
+            const float2* cos2 = reinterpret_cast<const float2*>(p.rope_cos + position * 64);
+            const float2* sin2 = reinterpret_cast<const float2*>(p.rope_sin + position * 64);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int pair = ks * 8 + half * 4 + quad;  // columns 2*pair, 2*pair + 1
+                    const float2 c = __ldg(cos2 + pair), sn = __ldg(sin2 + pair);
+                    const uint32_t lo = qa[ks][half], hi = qa[ks + 4][half];
+                    float lo0, hi0, lo1, hi1;
+                    rope_pair(bf16_lo(lo), bf16_lo(hi), c.x, sn.x, lo0, hi0);
+                    rope_pair(bf16_hi(lo), bf16_hi(hi), c.y, sn.y, lo1, hi1);
+                    qa[ks][half] = tc::pack_bf16x2(lo0, lo1);
+                    qa[ks + 4][half] = tc::pack_bf16x2(hi0, hi1);
+                }
+            }
+        }
     }
     float o[16][4];
 #pragma unroll
@@ -301,8 +338,37 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
             const uint32_t r = uint32_t(append_row - tile_row0);
             const int chunk = lane & 15;
             const bool is_v = lane >= 16;
-            const uint4 value = __ldg(reinterpret_cast<const uint4*>(
+            uint4 value = __ldg(reinterpret_cast<const uint4*>(
                 (is_v ? p.vnew : p.knew) + (int64_t(b) * p.kv_heads + kvh) * kDim) + chunk);
+            if (p.rope_cos) {
+                // Lanes 0-7 hold K columns [8*lane, 8*lane + 8), lanes 8-15 their partners 64 further on.
+                uint4 other;
+                other.x = __shfl_xor_sync(0xffffffffu, value.x, 8);
+                other.y = __shfl_xor_sync(0xffffffffu, value.y, 8);
+                other.z = __shfl_xor_sync(0xffffffffu, value.z, 8);
+                other.w = __shfl_xor_sync(0xffffffffu, value.w, 8);
+                if (!is_v) {
+                    const bool upper = chunk >= 8;
+                    int64_t position = old_len < p.rope_positions ? old_len : p.rope_positions - 1;
+                    const float4* cos4 = reinterpret_cast<const float4*>(p.rope_cos + position * 64) + (chunk & 7) * 2;
+                    const float4* sin4 = reinterpret_cast<const float4*>(p.rope_sin + position * 64) + (chunk & 7) * 2;
+                    const float4 c0 = __ldg(cos4), c1 = __ldg(cos4 + 1), s0 = __ldg(sin4), s1 = __ldg(sin4 + 1);
+                    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                    const uint32_t mine[4] = {value.x, value.y, value.z, value.w};
+                    const uint32_t theirs[4] = {other.x, other.y, other.z, other.w};
+                    uint32_t rotated[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t lo = upper ? theirs[j] : mine[j], hi = upper ? mine[j] : theirs[j];
+                        float lo0, hi0, lo1, hi1;
+                        rope_pair(bf16_lo(lo), bf16_lo(hi), c[2 * j], sn[2 * j], lo0, hi0);
+                        rope_pair(bf16_hi(lo), bf16_hi(hi), c[2 * j + 1], sn[2 * j + 1], lo1, hi1);
+                        rotated[j] = upper ? tc::pack_bf16x2(hi0, hi1) : tc::pack_bf16x2(lo0, lo1);
+                    }
+                    value = make_uint4(rotated[0], rotated[1], rotated[2], rotated[3]);
+                }
+            }
             *reinterpret_cast<uint4*>((is_v ? vbase : kbase) + swizzled(r, chunk)) = value;
             __nv_bfloat16* cache = is_v ? p.vcache : p.kcache;
             int slot, local;
@@ -669,6 +735,12 @@ struct PeerArgs {
     int world, rank;
 };
 
+struct RopeTables {
+    const float* cos;  // fp32 [positions, 64]
+    const float* sin;
+    int64_t positions;
+};
+
 struct IndexedCache {
     const int32_t* block_table;     // [B, pages_per_seq] (row stride table_stride) or nullptr
     int64_t table_stride, pages_per_seq;
@@ -718,7 +790,7 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
                   float* workspace_o, int64_t workspace_o_elems, float* workspace_lse, int64_t workspace_lse_elems,
                   int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping, int append,
                   int partial, int64_t shard_start, const PeerArgs* peer = nullptr,
-                  const IndexedCache* indexed = nullptr) {
+                  const IndexedCache* indexed = nullptr, const RopeTables* rope = nullptr) {
     tc::DeviceInfo info;
     int splits = 1;
     int status = check_geometry(device, batch, capacity, kv_heads, num_splits, mapping, append, &info, &splits);
@@ -804,6 +876,15 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
     p.partial_o = partial_o;
     p.page_size = int(slot_rows);
     p.cache_slots = int(cache_slots);
+    if (rope) {
+        TC_REQUIRE(rope->cos && rope->sin && rope->positions >= 1 && rope->positions <= (int64_t(1) << 30),
+                   "RoPE needs cos/sin tables FP32[positions,64] with positions >= 1");
+        TC_REQUIRE(reinterpret_cast<uintptr_t>(rope->cos) % 16 == 0 && reinterpret_cast<uintptr_t>(rope->sin) % 16 == 0,
+                   "16-byte aligned RoPE tables required");
+        p.rope_cos = rope->cos;
+        p.rope_sin = rope->sin;
+        p.rope_positions = int(rope->positions);
+    }
     if (indexed) {
         p.block_table = indexed->block_table;
         p.table_stride = indexed->table_stride;
@@ -1037,6 +1118,17 @@ int tc_decode_indexed_forward_out(int device, void* stream, const void* q, void*
     return decode_common(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, nullptr, workspace_o,
                          workspace_o_elems, workspace_lse, workspace_lse_elems, batch, capacity, kv_heads, num_splits,
                          mapping, append, 0, 0, nullptr, &indexed);
+}
+
+int tc_decode_rope_forward_out(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                               const void* vnew, const int32_t* old_lengths, void* out, float* lse, float* workspace_o,
+                               int64_t workspace_o_elems, float* workspace_lse, int64_t workspace_lse_elems,
+                               int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping,
+                               int append, const float* rope_cos, const float* rope_sin, int64_t rope_positions) {
+    const RopeTables rope{rope_cos, rope_sin, rope_positions};
+    return decode_common(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, nullptr, workspace_o,
+                         workspace_o_elems, workspace_lse, workspace_lse_elems, batch, capacity, kv_heads, num_splits,
+                         mapping, append, 0, 0, nullptr, nullptr, &rope);
 }
 
 int tc_peer_block_bytes(int64_t batch, int64_t kv_heads, int64_t world, int64_t* bytes) {

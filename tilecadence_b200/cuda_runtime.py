@@ -179,6 +179,10 @@ class Library:
         "tc_decode_partial_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, ctypes.c_int64)),
+        "tc_decode_rope_forward_out": (ctypes.c_int, (
+            ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
+            ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+            ctypes.c_int64)),
         "tc_decode_indexed_forward_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 6, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64,
@@ -469,6 +473,26 @@ class DecodeOps:
             _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse), workspace_lse.numel(),
             q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping), int(bool(append)),
             int(kv_shard_start))
+
+    def rope_forward_out(self, q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse,
+                         num_splits, mapping, append, rope_cos, rope_sin):
+        """``forward_out`` for un-rotated ``q`` / ``knew``: rotary position embedding (rotate-half, tables
+        FP32 [positions, 64], row = ``old_lengths[b]``) is applied inside the decode launch and the rotated K
+        row is what gets appended."""
+        import torch
+
+        self._check_call(q, kcache, vcache, knew, vnew, old_lengths, workspace_o, workspace_lse)
+        self._check_out(q, out, lse)
+        for table in (rope_cos, rope_sin):
+            _require(table.device == q.device and table.dtype == torch.float32 and table.dim() == 2
+                     and table.size(1) == 64 and table.is_contiguous() and table.shape == rope_cos.shape,
+                     "RoPE tables must be contiguous FP32[positions,64]")
+        self.library.call(
+            "tc_decode_rope_forward_out", q.device.index, _stream(q), _pointer(q), _pointer(kcache), _pointer(vcache),
+            _pointer(knew), _pointer(vnew), _pointer(old_lengths), _pointer(out), _pointer(lse),
+            _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse), workspace_lse.numel(),
+            q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping), int(bool(append)),
+            _pointer(rope_cos), _pointer(rope_sin), rope_cos.size(0))
 
     def indexed_forward_out(self, q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse,
                             num_splits, mapping, append, block_table=None, cache_batch_idx=None):
