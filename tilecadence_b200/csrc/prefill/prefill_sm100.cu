@@ -7,27 +7,27 @@
 //
 // One CTA owns a 128-row query tile of the two query heads that share a KV head pair slot, so one
 // K/V tile in shared memory feeds both heads. The two dense contractions run on the 5th-generation
-// tensor cores: S_h = Q_h K^T as a shared x shared tcgen05.mma into TMEM, O_h += P_h V as a
-// TMEM x shared tcgen05.mma with P written back over its own S columns as BF16. TMEM holds
-// S0 | S1 | O0 | O1 (4 x 128 fp32 columns = all 512 columns). Roles:
+// tensor cores: S = Q_h K^T as a shared x shared tcgen05.mma into one 128-column score buffer in TMEM
+// that the two heads use in strict alternation, O_h += P_h V as a TMEM x shared tcgen05.mma with P_h
+// (BF16) in columns of its own. TMEM: S | P0 P1 | O0 | O1 = 128 + 2*64 + 2*128 = all 512 columns. Roles:
 //   warps 0-3  softmax for head 0 (one query row per thread, TMEM lane = row)
 //   warps 4-7  softmax for head 1
 //   warp  8    TMA producer: Q once, then a 2-stage K ring and a 2-stage V ring (128-byte swizzle)
 //   warps 9,10 tcgen05.mma issuers, one elected thread per head (warp 9 also owns TMEM)
 //   warp  11   idle: it completes the third warpgroup so that it can release registers
 //              (setmaxnreg) to the softmax warpgroups
-// Per head the issue order is PV(first 64 keys) | PV(last 64 keys) | next QK; each head has its
-// own issuer, so the tensor pipe works on one head while the other head's softmax runs. The
-// softmax is bound by the exponential unit (16 results per clock per SM against 8192 MMA flops),
-// so part of the 2^x evaluations run as a cubic polynomial on the packed-FP32 FMA pipes. Key tiles go from the diagonal down to 0, the ring index is
-// chosen so that the final tile always uses stage 0: that stage is the "terminal K" donor whose
-// bytes receive the two 512-byte LSE arrays in the epilogue.
+// Per head the issue order is QK(it+1) | PV(it) first 64 keys | PV(it) last 64 keys; each head has
+// its own issuer, so the tensor pipe works on one head while the other head's softmax runs. The
+// softmax is bound by the exponential unit (16 results per clock per SM against 8192 MMA flops), so
+// the two warpgroups take turns at it (named barriers). A head may rewrite the first half of its P as
+// soon as the first half of the previous PV has retired. Key tiles go from the diagonal down to 0; the
+// ring index is chosen so that the final tile always uses stage 0: that stage is the "terminal K" donor
+// whose bytes receive the two 512-byte LSE arrays in the epilogue.
 #include "config.cuh"
 #include "tc_host.cuh"
 #include "tc_ptx.cuh"
 
 #include <cmath>
-#include <type_traits>
 
 namespace {
 
@@ -47,10 +47,6 @@ constexpr int kStagingBytes = 1024;           // dedicated LSE staging when the 
 constexpr int kSoftmaxThreads = 128;
 constexpr int kThreads = 3 * kSoftmaxThreads;   // two softmax warpgroups + one data/MMA warpgroup
 constexpr int kSoftmaxRegisters = 216, kDataRegisters = 72;  // 256*216 + 128*72 = 64512 <= 65536
-constexpr bool kSplitP = PREFILL_SPLIT_P != 0;  // signal the MMA issuer after each 64-key half of P
-constexpr int kEmulatedPairsPer8 = PREFILL_EXP_FMA_PAIRS_PER_8;
-constexpr bool kEarlyP = PREFILL_EARLY_P != 0;  // rewrite the first half of P as soon as the first half of PV is done
-constexpr int kShadowChunks = PREFILL_SHADOW_CHUNKS;  // leading 32-key chunks exponentiated on the FMA pipes before the turn  // of every 8 key pairs, how many use the FMA-pipe 2^x
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kSColumn = 0, kPColumn = 128, kOColumn = 256;  // S (shared) | P0 P1 | O0 O1
@@ -73,12 +69,11 @@ constexpr int shared_bytes(bool handoff) { return 1024 + kBarrierOffset + kBarri
 struct Barriers {
     uint64_t q_full;
     uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-    uint64_t s_full[2], s_free[2], p_half[2][2], p_lo_free[2], o_done[2], turn[2];
+    uint64_t s_full[2], s_free[2], p_half[2][2], p_lo_free[2], o_done[2];
     uint32_t tmem_base;
     int32_t abort;
 };
 static_assert(sizeof(Barriers) <= kBarrierBytes, "barrier block");
-static_assert(PREFILL_SHADOW_CHUNKS <= 2, "pre-turn chunks must stay inside the first half of P");
 
 struct PrefillParams {
     float* lse;
@@ -86,20 +81,6 @@ struct PrefillParams {
     int batch, tokens, q_heads, kv_heads, m_blocks;
     float scale, scale_log2;
 };
-
-// Arrival of a softmax warp on a barrier the MMA issuer waits on. With PREFILL_WARP_ARRIVE one lane
-// arrives for the warp after a warp barrier (every lane has fenced its own tensor-memory accesses
-// first), so the barrier sees 4 arrivals instead of 128 serialised ones.
-constexpr int kArrivals = PREFILL_WARP_ARRIVE ? kSoftmaxThreads / 32 : kSoftmaxThreads;
-__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
-#if PREFILL_WARP_ARRIVE
-    __syncwarp();
-    if (lane == 0) tc::mbar_arrive(bar);
-#else
-    (void)lane;
-    tc::mbar_arrive(bar);
-#endif
-}
 
 __device__ __forceinline__ void wg_barrier(int head) {
     asm volatile("bar.sync %0, %1;" ::"r"(head + 1), "n"(kSoftmaxThreads) : "memory");
@@ -109,24 +90,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
-}
-
-// 2^x for a pair of values on the FMA pipes instead of the exponential unit: split x into a
-// rounded integer n (magic-number add) and r = x - n in [-0.5, 0.5], evaluate a cubic fit of 2^r
-// (relative error 7.5e-5, far below the BF16 rounding P receives), and add n to the exponent
-// field. x must be >= -125 so the exponent cannot wrap.
-__device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
-    const float2 magic = make_float2(12582912.f, 12582912.f);  // 1.5 * 2^23
-    const float2 t = __fadd2_rn(x, magic);
-    const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
-    const float2 r = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
-    float2 poly = __ffma2_rn(r, make_float2(0.055171460f, 0.055171460f), make_float2(0.24261086f, 0.24261086f));
-    poly = __ffma2_rn(poly, r, make_float2(0.69326097f, 0.69326097f));
-    poly = __ffma2_rn(poly, r, make_float2(0.99992812f, 0.99992812f));
-    float2 result;
-    result.x = __uint_as_float(__float_as_uint(poly.x) + (__float_as_uint(t.x) << 23));
-    result.y = __uint_as_float(__float_as_uint(poly.y) + (__float_as_uint(t.y) << 23));
-    return result;
 }
 
 template <bool kHandoff>
@@ -161,12 +124,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         }
         for (int h = 0; h < 2; ++h) {
             tc::mbar_init(&bars->s_full[h], 1);
-            tc::mbar_init(&bars->s_free[h], kArrivals);
-            tc::mbar_init(&bars->p_half[h][0], kArrivals);
-            tc::mbar_init(&bars->p_half[h][1], kArrivals);
+            tc::mbar_init(&bars->s_free[h], kSoftmaxThreads);
+            tc::mbar_init(&bars->p_half[h][0], kSoftmaxThreads);
+            tc::mbar_init(&bars->p_half[h][1], kSoftmaxThreads);
             tc::mbar_init(&bars->o_done[h], 1);
             tc::mbar_init(&bars->p_lo_free[h], 1);
-            tc::mbar_init(&bars->turn[h], kSoftmaxThreads);
         }
         bars->abort = 0;
         tc::mbar_fence_init();
@@ -184,9 +146,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     // two softmax warpgroups, which keep a whole 128-column score row per thread. Each role's code
     // sits under its own setmaxnreg so that the register allocator sees the right budget.
     if (warp >= 2 * (kSoftmaxThreads / 32)) {
-#if PREFILL_SETMAXNREG
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kDataRegisters));
-#endif
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -258,7 +218,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 if (!tc::mbar_wait(&bars->p_half[h][0], uint32_t(it) & 1)) return false;
                 tc::tc_fence_after_sync();
                 issue_pv_half(it, 0);
-                if (kEarlyP) tc::umma_commit(&bars->p_lo_free[h]);  // P columns of the first 64 keys may be rewritten
+                tc::umma_commit(&bars->p_lo_free[h]);  // P columns of the first 64 keys may be rewritten
                 if (!tc::mbar_wait(&bars->p_half[h][1], uint32_t(it) & 1)) return false;
                 tc::tc_fence_after_sync();
                 issue_pv_half(it, 1);
@@ -290,9 +250,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         }
     }
     } else {
-#if PREFILL_SETMAXNREG
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegisters));
-#endif
         // ------------------------------------------------------------------ softmax warpgroups
         const int h = warp >> 2;                        // head slot
         const int row = threadIdx.x & (kSoftmaxThreads - 1);
@@ -313,14 +271,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             for (int c = 0; c < 4; ++c) tc::tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
             tc::tmem_wait_ld();
             tc::tc_fence_before_sync();
-            warp_arrive(&bars->s_free[h], lane);  // the score buffer may be overwritten by the other head
+            tc::mbar_arrive(&bars->s_free[h]);  // the score buffer may be overwritten by the other head
             if (it == 0) {
                 // Diagonal tile: key column j is visible to query row i only if j <= i.
 #pragma unroll
                 for (int j = 0; j < 128; ++j) s[j] = j > row ? -INFINITY : s[j];
             }
             float mx[4];
-#if PREFILL_MAX3
 #pragma unroll
             for (int q = 0; q < 4; ++q) mx[q] = max3(s[q * 32], s[q * 32 + 1], s[q * 32 + 2]);
 #pragma unroll
@@ -330,15 +287,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             }
 #pragma unroll
             for (int q = 0; q < 4; ++q) mx[q] = fmaxf(mx[q], s[q * 32 + 31]);
-#else
-#pragma unroll
-            for (int q = 0; q < 4; ++q) mx[q] = s[q * 32];
-#pragma unroll
-            for (int j = 1; j < 32; ++j) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) mx[q] = fmaxf(mx[q], s[q * 32 + j]);
-            }
-#endif
             const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
             // Gated rescale: O and l are only brought to a new reference maximum when the row maximum
             // grew by more than 2^kRescaleThreshold, and only if some row of the warp needs it (the
@@ -361,48 +309,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             const float neg_bias = -m_used * p.scale_log2;
             const float2 bias2 = make_float2(neg_bias, neg_bias);
             float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-            // One chunk = 32 keys: x = s*scale - bias on packed pairs, 2^x either on the exponential
-            // unit or (kEmulate) on the FMA pipes, BF16 pack, store to this head's P columns.
-            auto chunk = [&](int c, auto emulate_tag, uint32_t (&packed)[16]) {
-                constexpr bool kEmulate = decltype(emulate_tag)::value;
+            // One chunk = 32 keys: x = s*scale - bias on packed pairs (fma.rn.f32x2), 2^x on the
+            // exponential unit, packed row sums, BF16 pack for this head's P columns.
+            auto chunk = [&](int c, uint32_t (&packed)[16]) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 2) {
-#if PREFILL_PACKED_MATH
-                    float2 x = __ffma2_rn(make_float2(s[c * 32 + j], s[c * 32 + j + 1]), scale2, bias2);
-#else
-                    float2 x = make_float2(fmaf(s[c * 32 + j], p.scale_log2, neg_bias), fmaf(s[c * 32 + j + 1], p.scale_log2, neg_bias));
-#endif
-                    float2 e;
-                    if (kEmulate || (j >> 1) % 8 < kEmulatedPairsPer8) {
-                        x.x = fmaxf(x.x, -125.f);
-                        x.y = fmaxf(x.y, -125.f);
-                        e = exp2_pair_fma(x);
-                    } else {
-                        e.x = tc::fast_exp2(x.x);
-                        e.y = tc::fast_exp2(x.y);
-                    }
-#if PREFILL_PACKED_MATH
+                    const float2 x = __ffma2_rn(make_float2(s[c * 32 + j], s[c * 32 + j + 1]), scale2, bias2);
+                    const float2 e = make_float2(tc::fast_exp2(x.x), tc::fast_exp2(x.y));
                     sum2[(j >> 1) & 1] = __fadd2_rn(sum2[(j >> 1) & 1], e);
-#else
-                    sum2[(j >> 1) & 1].x += e.x;
-                    sum2[(j >> 1) & 1].y += e.y;
-#endif
                     packed[j >> 1] = tc::pack_bf16x2(e.x, e.y);
                 }
             };
-            // While the other head holds the exponential unit this warpgroup would only wait, so it
-            // spends that time on the FMA pipes: the first kShadowChunks chunks of the tile get their
-            // 2^x from the polynomial, which shortens this head's own turn by the same share.
-            uint32_t shadow[kShadowChunks > 0 ? kShadowChunks : 1][16];
-#pragma unroll
-            for (int c = 0; c < kShadowChunks; ++c) chunk(c, std::true_type{}, shadow[c]);
             // PV of the previous tile reads P: its first half (keys 0-63, P chunks 0 and 1) must be done
             // before chunk 0 is rewritten, all of it before chunk 2 is rewritten or O is rescaled. Waiting
             // only for the first half here takes the second half's execution off this head's
             // exp -> PV -> exp chain; the full wait follows before chunk 2, by when it has long finished.
             bool pv_done = it == 0;
             if (it > 0) {
-                if (!kEarlyP || rescale) {
+                if (rescale) {
                     if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1);
                     pv_done = true;
                 } else {
@@ -423,47 +347,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     l *= alpha;
                 }
             }
-#pragma unroll
-            for (int c = 0; c < kShadowChunks; ++c) tc::tmem_st16(p_tmem + c * 16, shadow[c]);
-            if (kSplitP && kShadowChunks >= 2) {
-                tc::tmem_wait_st();
-                tc::tc_fence_before_sync();
-                warp_arrive(&bars->p_half[h][0], lane);
-            }
-#if PREFILL_PINGPONG
             // The exponential unit is the scarcest resource, so the two heads take turns at it: while
             // one warpgroup exponentiates, the other head's P is being consumed by the tensor pipe
             // and its next S tile is produced. Head 0 goes first on every tile.
             if (h == 1 || it > 0) {
-#if PREFILL_TURN_NAMED
                 // Hardware named barrier: the other warpgroup's 128 threads arrive without blocking when
                 // their exponentials are issued, this warpgroup's 128 threads wait. It wakes faster than
                 // an mbarrier wait; both sides execute it on every path so the counts always match.
                 asm volatile("bar.sync %0, 256;" ::"r"(3 + h) : "memory");
-#else
-                if (ok) ok = tc::mbar_wait(&bars->turn[h], uint32_t(h == 1 ? it : it - 1) & 1);
-#endif
             }
-#endif
 #pragma unroll
-            for (int c = kShadowChunks; c < 4; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 uint32_t packed[16];
-                chunk(c, std::false_type{}, packed);
-#if PREFILL_PINGPONG
+                chunk(c, packed);
                 // Hand the exponential unit over when this head's last exponentials are issued: the
                 // other warpgroup needs about a hundred cycles to wake up.
-#if PREFILL_TURN_NAMED
-                if (c == PREFILL_TURN_CHUNK && (h == 0 || it + 1 < n_tiles))
+                if (c == 3 && (h == 0 || it + 1 < n_tiles))
                     asm volatile("bar.arrive %0, 256;" ::"r"(3 + (1 - h)) : "memory");
-#else
-                if (c == PREFILL_TURN_CHUNK) tc::mbar_arrive(&bars->turn[1 - h]);
-#endif
-#endif
-                if (kSplitP && kShadowChunks < 2 && c == 2) {
+                if (c == 2) {
                     // Chunks 0 and 1 were stored a whole chunk of arithmetic ago, so this wait is short.
                     tc::tmem_wait_st();
                     tc::tc_fence_before_sync();
-                    warp_arrive(&bars->p_half[h][0], lane);
+                    tc::mbar_arrive(&bars->p_half[h][0]);
                 }
                 if (c == 2 && !pv_done) {
                     if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1);
@@ -474,8 +379,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             }
             tc::tmem_wait_st();
             tc::tc_fence_before_sync();
-            if (!kSplitP) warp_arrive(&bars->p_half[h][0], lane);
-            warp_arrive(&bars->p_half[h][1], lane);
+            tc::mbar_arrive(&bars->p_half[h][1]);
             l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
         }
 
