@@ -114,7 +114,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     const int m0 = m_block * kBlockM;
     const int n_tiles = m_block + 1;  // key tiles m_block, m_block-1, ..., 0
 
-    if (threadIdx.x == 0) {
+    // The TMA producer owns the operand barriers: it initialises them itself and sends for Q and for
+    // the first ring stages at once, so the first loads are in flight while the other warps set up
+    // their barriers and tensor memory. Everything else waits for the CTA barrier below.
+    const uint64_t keep = tc::policy_evict_last(), stream_once = tc::policy_evict_first();
+    auto load_kv = [&](int it) {
+        const int stage = (n_tiles - 1 - it) % kStages;
+        const int n0 = (m_block - it) * kBlockN;
+        uint8_t* kdst = smem + kKOffset + stage * kTileBytes;
+        tc::mbar_arrive_expect_tx(&bars->k_full[stage], kTileBytes);
+        tc::tma_load_4d(kdst, &kmap, &bars->k_full[stage], 0, kvh, n0, b, keep);
+        tc::tma_load_4d(kdst + kHalfBytes, &kmap, &bars->k_full[stage], 64, kvh, n0, b, keep);
+        return stage;
+    };
+    auto load_v = [&](int it, int stage) {
+        const int n0 = (m_block - it) * kBlockN;
+        uint8_t* vdst = smem + kVOffset + stage * kTileBytes;
+        tc::mbar_arrive_expect_tx(&bars->v_full[stage], kTileBytes);
+        tc::tma_load_4d(vdst, &vmap, &bars->v_full[stage], 0, kvh, n0, b, keep);
+        tc::tma_load_4d(vdst + kHalfBytes, &vmap, &bars->v_full[stage], 64, kvh, n0, b, keep);
+    };
+    if (threadIdx.x == kProducerWarp * 32) {
         tc::mbar_init(&bars->q_full, 1);
         for (int s = 0; s < kStages; ++s) {
             tc::mbar_init(&bars->k_full[s], 1);
@@ -122,6 +142,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             tc::mbar_init(&bars->v_full[s], 1);
             tc::mbar_init(&bars->v_empty[s], 2);
         }
+        tc::mbar_fence_init();
+        tc::tma_prefetch_desc(&qmap);
+        tc::tma_prefetch_desc(&kmap);
+        tc::tma_prefetch_desc(&vmap);
+        tc::mbar_arrive_expect_tx(&bars->q_full, 2 * kTileBytes);
+        for (int h = 0; h < 2; ++h) {
+            uint8_t* dst = smem + kQOffset + h * kTileBytes;
+            tc::tma_load_4d(dst, &qmap, &bars->q_full, 0, head0 + h, m0, b, stream_once);
+            tc::tma_load_4d(dst + kHalfBytes, &qmap, &bars->q_full, 64, head0 + h, m0, b, stream_once);
+        }
+        for (int it = 0; it < kStages && it < n_tiles; ++it) load_v(it, load_kv(it));  // fresh stages: nothing to wait for
+    }
+    if (threadIdx.x == 0) {
         for (int h = 0; h < 2; ++h) {
             tc::mbar_init(&bars->s_full[h], 1);
             tc::mbar_init(&bars->s_free[h], kSoftmaxThreads);
@@ -150,30 +183,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            tc::tma_prefetch_desc(&qmap);
-            tc::tma_prefetch_desc(&kmap);
-            tc::tma_prefetch_desc(&vmap);
-            const uint64_t keep = tc::policy_evict_last(), stream = tc::policy_evict_first();
-            tc::mbar_arrive_expect_tx(&bars->q_full, 2 * kTileBytes);
-            for (int h = 0; h < 2; ++h) {
-                uint8_t* dst = smem + kQOffset + h * kTileBytes;
-                tc::tma_load_4d(dst, &qmap, &bars->q_full, 0, head0 + h, m0, b, stream);
-                tc::tma_load_4d(dst + kHalfBytes, &qmap, &bars->q_full, 64, head0 + h, m0, b, stream);
-            }
-            for (int it = 0; it < n_tiles; ++it) {
+            for (int it = kStages; it < n_tiles; ++it) {
                 const int stage = (n_tiles - 1 - it) % kStages;
                 const uint32_t parity = (uint32_t(it / kStages) & 1) ^ 1;
-                const int n0 = (m_block - it) * kBlockN;
                 if (!tc::mbar_wait(&bars->k_empty[stage], parity)) { atomicCAS(p.status, 0, 11); break; }
-                uint8_t* kdst = smem + kKOffset + stage * kTileBytes;
-                tc::mbar_arrive_expect_tx(&bars->k_full[stage], kTileBytes);
-                tc::tma_load_4d(kdst, &kmap, &bars->k_full[stage], 0, kvh, n0, b, keep);
-                tc::tma_load_4d(kdst + kHalfBytes, &kmap, &bars->k_full[stage], 64, kvh, n0, b, keep);
+                load_kv(it);
                 if (!tc::mbar_wait(&bars->v_empty[stage], parity)) { atomicCAS(p.status, 0, 12); break; }
-                uint8_t* vdst = smem + kVOffset + stage * kTileBytes;
-                tc::mbar_arrive_expect_tx(&bars->v_full[stage], kTileBytes);
-                tc::tma_load_4d(vdst, &vmap, &bars->v_full[stage], 0, kvh, n0, b, keep);
-                tc::tma_load_4d(vdst + kHalfBytes, &vmap, &bars->v_full[stage], 64, kvh, n0, b, keep);
+                load_v(it, stage);
             }
         }
     } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
