@@ -41,7 +41,7 @@ sys.path.insert(0, str(ROOT))
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the three benchmarked launches, from
 # the ncu captures summarised under profiles/ (prefill_kernel_config2.md, decode_splitkv_kernel_config4_config5.md).
-NCU_TRAFFIC_BYTES = {"prefill_c2": 121.3e6, "decode_c4": 33.61e6, "decode_c5": 541.5e6}
+NCU_TRAFFIC_BYTES = {"prefill_c2": 119.5e6, "decode_c4": 33.62e6, "decode_c5": 541.2e6}
 HQ, HKV, DIM = 32, 8, 128
 SCALE = DIM ** -0.5
 PREFILL = dict(batch=1, tokens=8192, seed=1)
