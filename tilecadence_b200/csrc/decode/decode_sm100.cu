@@ -14,6 +14,12 @@
 // are staged at the planner's offsets inside the terminal V region, published with one barrier and
 // exported with one 16-byte vector per thread. The last CTA to finish a (batch, KV head) merges
 // the split partials, so no second launch is needed.
+//
+// Options on the same kernel: caches addressed through a block table (pages) or a per-sequence
+// batch index (ab_fused_splitkv.cuh:92-103); rotary position embedding of q and of the appended K
+// row applied in registers; a KV-sequence shard of a longer cache (global lengths, shard start)
+// that writes a partial result; and, for shards spread over the GPUs of one node, the cross-GPU
+// merge of those partials inside the launch through peer stores (template parameter kPeer).
 #include "config.cuh"
 #include "tc_host.cuh"
 #include "tc_ptx.cuh"
