@@ -298,6 +298,44 @@ def test_in_launch_exchange_with_one_rank(ops, gpu_device):
         driver.close()
 
 
+def test_missing_rank_ends_the_exchange_with_a_status(ops, gpu_device):
+    """Failure detection without a fault: rank 0 of a world of two runs alone (rank 1's exchange block is a
+    second block on this GPU that nobody fills). Its bounded wait expires, the kernel returns, the status
+    word reports it, and the next ordinary call on the same context is correct."""
+    import ctypes
+
+    library, device = ops.library, gpu_device
+    batch, capacity = 1, 256
+    q, kcache, vcache, knew, vnew = make_case(31, batch, capacity)
+    old = torch.tensor([100], dtype=torch.int32)
+    size = ctypes.c_int64(0)
+    library.call("tc_peer_block_bytes", batch, 8, 2, ctypes.byref(size))
+    blocks = []
+    try:
+        for _ in range(2):
+            block, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+            library.call("tc_peer_block_create", device.index, size.value, ctypes.byref(block), handle)
+            blocks.append(block.value)
+        table = (ctypes.c_void_p * 2)(*blocks)
+        dq, dkn, dvn, dold = q.to(device), knew.to(device), vnew.to(device), old.to(device)
+        dk, dv = kcache[:, :128].contiguous().to(device), vcache[:, :128].contiguous().to(device)
+        out = torch.empty_like(dq)
+        lse = torch.empty((batch, 32, 1), device=device, dtype=torch.float32)
+        spec = ops.workspace_spec(dq, dk, dold, 0, 1, True)
+        ws = [torch.empty(n, device=device, dtype=torch.float32) for n in spec[1:3]]
+        ops.exchange_out(dq, dk, dv, dkn, dvn, dold, out, lse, *ws, 0, 1, True, 0, 0, table)
+        torch.cuda.synchronize()
+        assert library.device_status(device.index) == 5   # "a rank never delivered"
+        assert library.device_status(device.index) == 0   # reading clears it
+    finally:
+        torch.cuda.synchronize()
+        for block in blocks:
+            library.call("tc_peer_block_destroy", device.index, block)
+    want_o, want_lse, _, _ = oracle.decode_step(q, kcache, vcache, knew, vnew, old)
+    got_o, got_lse, _, _, _ = run_step(ops, device, q, kcache, vcache, knew, vnew, old)
+    oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+
+
 def test_argument_checks(ops, gpu_device):
     q, kcache, vcache, knew, vnew = (t.to(gpu_device) for t in make_case(1, 1, 128))
     old = torch.zeros(1, dtype=torch.int32, device=gpu_device)

@@ -88,3 +88,75 @@ def test_shard_arithmetic():
         sharding.kv_head_slice(0, 3)
     with pytest.raises(ValueError):
         sharding.kv_sequence_shard(0, 3, 32768)
+
+
+class FakePeerLibrary:
+    """Stands in for the C-ABI library's exchange-block calls (no GPU): hands out fake addresses, and on
+    the rank named ``fail_on`` refuses to map other ranks' blocks, like a box without peer access."""
+
+    def __init__(self, rank, fail_on):
+        self.rank, self.fail_on, self.calls = rank, fail_on, []
+
+    def call(self, name, *arguments):
+        import ctypes
+
+        self.calls.append(name)
+        if name == "tc_peer_block_bytes":
+            arguments[3]._obj.value = 4096
+        elif name == "tc_peer_block_create":
+            arguments[2]._obj.value = 0x1000 * (self.rank + 1)
+            ctypes.memmove(arguments[3], bytes([self.rank + 1]) * 64, 64)
+        elif name == "tc_peer_block_open":
+            if self.rank == self.fail_on:
+                raise RuntimeError("tc_peer_block_open: peer access is not available (status 2)")
+            arguments[2]._obj.value = 0x100000 + arguments[1][0]  # tagged with the owner's handle byte
+
+
+class FakeDevice:
+    index = 0
+
+
+def peer_worker(rank, world, port, fail_on, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        library = FakePeerLibrary(rank, fail_on)
+        original = torch.cuda.synchronize
+        torch.cuda.synchronize = lambda device=None: None  # close() drains the device first; there is none here
+        try:
+            try:
+                blocks = sharding.PeerBlocks(library, rank, world, 4, 8, FakeDevice())
+            except RuntimeError as error:
+                results[rank] = ("refused", str(error), list(library.calls))
+                return
+            table = [blocks.table[r] for r in range(world)]
+            blocks.close()
+            results[rank] = ("mapped", table, list(library.calls))
+        finally:
+            torch.cuda.synchronize = original
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fail_on", [None, 1])
+def test_peer_blocks_are_mapped_by_all_ranks_or_by_none(fail_on):
+    """Handles travel through one all-gather; if any rank cannot map a block, every rank gives the route
+    up with the same error class, unmaps what it had mapped and frees its own block."""
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(peer_worker, args=(world, free_port(), fail_on, results), nprocs=world, join=True)
+    assert set(results.keys()) == {0, 1}
+    if fail_on is None:
+        for rank in range(world):
+            state, table, calls = results[rank]
+            assert state == "mapped"
+            assert table[rank] == 0x1000 * (rank + 1) and table[1 - rank] == 0x100000 + (2 - rank)
+            assert calls == ["tc_peer_block_bytes", "tc_peer_block_create", "tc_peer_block_open",
+                             "tc_peer_block_close", "tc_peer_block_destroy"]
+    else:
+        for rank in range(world):
+            state, message, calls = results[rank]
+            assert state == "refused" and message.startswith("peer exchange unavailable")
+            assert calls[-1] == "tc_peer_block_destroy"
+        assert "tc_peer_block_close" in results[0][2] and "tc_peer_block_close" not in results[1][2]
