@@ -229,8 +229,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                                 idesc_pv, !(it == 0 && ks == 0));
                 }
             };
+            // The caller has already seen v_full of this tile: every barrier check costs this lone
+            // thread 100-170 cycles on a scheduler it shares with two busy softmax warps, so only the
+            // checks that can actually block stay between the score MMA and PV.
             auto issue_pv = [&](int it) {
-                if (!tc::mbar_wait(&bars->v_full[stage_of(it)], parity_of(it))) return false;
                 if (!tc::mbar_wait(&bars->p_half[h][0], uint32_t(it) & 1)) return false;
                 tc::tc_fence_after_sync();
                 issue_pv_half(it, 0);
@@ -249,6 +251,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             bool ok = tc::mbar_wait(&bars->q_full, 0);
             for (int it = 0; ok && it < n_tiles; ++it) {
                 if (!(ok = tc::mbar_wait(&bars->k_full[stage_of(it)], parity_of(it)))) break;
+                if (it > 0 && !(ok = tc::mbar_wait(&bars->v_full[stage_of(it - 1)], parity_of(it - 1)))) break;  // for PV(it-1) below
                 if (h == 0) {
                     if (it > 0 && !(ok = tc::mbar_wait(&bars->s_free[1], uint32_t(it - 1) & 1))) break;
                 } else {
@@ -258,6 +261,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 issue_qk(it);
                 if (it > 0 && !(ok = issue_pv(it - 1))) break;
             }
+            if (ok) ok = tc::mbar_wait(&bars->v_full[stage_of(n_tiles - 1)], parity_of(n_tiles - 1));
             if (ok) ok = issue_pv(n_tiles - 1);
             if (!ok) {
                 atomicCAS(p.status, 0, 13);
