@@ -13,11 +13,11 @@
 //   warps 0-3  softmax for head 0 (one query row per thread, TMEM lane = row)
 //   warps 4-7  softmax for head 1
 //   warp  8    TMA producer: Q once, then a 2-stage K ring and a 2-stage V ring (128-byte swizzle)
-//   warps 9,10 tcgen05.mma issuers, one elected thread per head (warp 9 also owns TMEM)
-//   warp  11   idle: it completes the third warpgroup so that it can release registers
-//              (setmaxnreg) to the softmax warpgroups
-// Per head the issue order is QK(it+1) | PV(it) first 64 keys | PV(it) last 64 keys; each head has
-// its own issuer, so the tensor pipe works on one head while the other head's softmax runs. The
+//   warp  9    issues every score MMA (one elected thread; the warp also owns TMEM)
+//   warps 10,11 issue PV for head 0 / head 1 (one elected thread each)
+// The third warpgroup gives most of its registers to the softmax warpgroups (setmaxnreg). Score
+// MMAs and PV MMAs have separate issuers because issue blocks at the tensor pipe's rate: a thread that
+// is busy issuing one kind must not be the one that has to notice the other kind becoming ready. The
 // softmax is bound by the exponential unit (16 results per clock per SM against 8192 MMA flops), so
 // the two warpgroups take turns at it (named barriers). A head may rewrite the first half of its P as
 // soon as the first half of the previous PV has retired. Key tiles go from the diagonal down to 0; the
@@ -192,77 +192,78 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 load_v(it, stage);
             }
         }
-    } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
-        // ------------------------------------------------------------------ MMA issuers (one per head)
+    } else {
+        // ------------------------------------------------------------------ MMA issuers
+        // Warp 9 issues every score MMA (the shared score buffer is used 0,1,0,1,... so their order is
+        // fixed anyway); warps 10 and 11 issue PV for head 0 and head 1. Each role is one elected thread.
+        // Issue blocks at the tensor pipe's rate and every barrier check costs such a lone thread
+        // 100-170 cycles, so a thread that is busy issuing one kind of MMA must not be the one that has
+        // to notice that the other kind has become ready.
         if (lane == 0) {
-            const int h = warp - kMmaWarp;
             constexpr uint32_t idesc_qk = tc::umma_idesc(128, 128, 1, 0, 0);
             constexpr uint32_t idesc_pv = tc::umma_idesc(128, 128, 1, 0, 1);
-            const uint32_t q_addr = tc::smem_u32(smem + kQOffset) + h * kTileBytes;
-            const uint32_t k_addr = tc::smem_u32(smem + kKOffset);
-            const uint32_t v_addr = tc::smem_u32(smem + kVOffset);
-            const uint32_t s_col = tmem + kSColumn, p_col = tmem + kPColumn + uint32_t(h) * 64;
-            const uint32_t o_col = tmem + kOColumn + uint32_t(h) * 128;
             auto stage_of = [&](int it) { return (n_tiles - 1 - it) % kStages; };
             auto parity_of = [&](int it) { return uint32_t(it / kStages) & 1; };
-            // S = Q_h K^T into the shared score buffer: both operands K-major, 8 steps of 16 along D
-            // (4 per 64-element half).
-            auto issue_qk = [&](int it) {
-                const uint32_t kb = k_addr + stage_of(it) * kTileBytes;
+            bool ok = true;
+            if (warp == kMmaWarp) {
+                // S = Q_h K^T into the shared score buffer: both operands K-major, 8 steps of 16 along D
+                // (4 per 64-element half). A score MMA may overwrite the buffer once the other head's
+                // softmax warpgroup has pulled its tile into registers; because P has its own columns it
+                // does not wait for any PV.
+                const uint32_t q_addr = tc::smem_u32(smem + kQOffset);
+                const uint32_t k_addr = tc::smem_u32(smem + kKOffset);
+                const uint32_t s_col = tmem + kSColumn;
+                ok = tc::mbar_wait(&bars->q_full, 0);
+                for (int it = 0; ok && it < n_tiles; ++it) {
+                    if (!(ok = tc::mbar_wait(&bars->k_full[stage_of(it)], parity_of(it)))) break;
+                    const uint32_t kb = k_addr + stage_of(it) * kTileBytes;
+                    for (int h = 0; h < 2 && ok; ++h) {
+                        if (h == 0) {
+                            if (it > 0) ok = tc::mbar_wait(&bars->s_free[1], uint32_t(it - 1) & 1);
+                        } else {
+                            ok = tc::mbar_wait(&bars->s_free[0], uint32_t(it) & 1);
+                        }
+                        if (!ok) break;
+                        tc::tc_fence_after_sync();
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = uint32_t(ks >> 2) * kHalfBytes + uint32_t(ks & 3) * 32;
-                    tc::umma_ss(s_col, tc::umma_desc_sw128(q_addr + off, 16, 1024),
-                                tc::umma_desc_sw128(kb + off, 16, 1024), idesc_qk, ks > 0);
+                        for (int ks = 0; ks < 8; ++ks) {
+                            const uint32_t off = uint32_t(ks >> 2) * kHalfBytes + uint32_t(ks & 3) * 32;
+                            tc::umma_ss(s_col, tc::umma_desc_sw128(q_addr + h * kTileBytes + off, 16, 1024),
+                                        tc::umma_desc_sw128(kb + off, 16, 1024), idesc_qk, ks > 0);
+                        }
+                        tc::umma_commit(&bars->s_full[h]);
+                        tc::umma_commit(&bars->k_empty[stage_of(it)]);  // two arrivals per stage: one per head
+                    }
                 }
-                tc::umma_commit(&bars->s_full[h]);
-                tc::umma_commit(&bars->k_empty[stage_of(it)]);  // second arrival comes from the other head
-            };
-            // O_h += P_h V for one half (64 keys) of the tile: P from TMEM (8 columns per 16 keys), V
-            // MN-major (row = key, 128 bytes per 64 d; the d halves 16 KiB apart, 8-key groups 1 KiB).
-            auto issue_pv_half = [&](int it, int half) {
-                const uint32_t vb = v_addr + stage_of(it) * kTileBytes;
+            } else {
+                // O_h += P_h V, one 64-key half at a time: P from TMEM (8 columns per 16 keys), V MN-major
+                // (row = key, 128 bytes per 64 d; the d halves 16 KiB apart, 8-key groups 1 KiB).
+                const int h = warp - (kMmaWarp + 1);
+                const uint32_t v_addr = tc::smem_u32(smem + kVOffset);
+                const uint32_t p_col = tmem + kPColumn + uint32_t(h) * 64;
+                const uint32_t o_col = tmem + kOColumn + uint32_t(h) * 128;
+                auto issue_pv_half = [&](int it, int half) {
+                    const uint32_t vb = v_addr + stage_of(it) * kTileBytes;
 #pragma unroll
-                for (int k4 = 0; k4 < 4; ++k4) {
-                    const int ks = half * 4 + k4;
-                    tc::umma_ts(o_col, p_col + uint32_t(ks) * 8, tc::umma_desc_sw128(vb + ks * 2048, kHalfBytes, 1024),
-                                idesc_pv, !(it == 0 && ks == 0));
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const int ks = half * 4 + k4;
+                        tc::umma_ts(o_col, p_col + uint32_t(ks) * 8, tc::umma_desc_sw128(vb + ks * 2048, kHalfBytes, 1024),
+                                    idesc_pv, !(it == 0 && ks == 0));
+                    }
+                };
+                for (int it = 0; ok && it < n_tiles; ++it) {
+                    if (!(ok = tc::mbar_wait(&bars->v_full[stage_of(it)], parity_of(it)))) break;
+                    if (!(ok = tc::mbar_wait(&bars->p_half[h][0], uint32_t(it) & 1))) break;
+                    tc::tc_fence_after_sync();
+                    issue_pv_half(it, 0);
+                    tc::umma_commit(&bars->p_lo_free[h]);  // P columns of the first 64 keys may be rewritten
+                    if (!(ok = tc::mbar_wait(&bars->p_half[h][1], uint32_t(it) & 1))) break;
+                    tc::tc_fence_after_sync();
+                    issue_pv_half(it, 1);
+                    tc::umma_commit(&bars->o_done[h]);
+                    tc::umma_commit(&bars->v_empty[stage_of(it)]);
                 }
-            };
-            // The caller has already seen v_full of this tile: every barrier check costs this lone
-            // thread 100-170 cycles on a scheduler it shares with two busy softmax warps, so only the
-            // checks that can actually block stay between the score MMA and PV.
-            auto issue_pv = [&](int it) {
-                if (!tc::mbar_wait(&bars->p_half[h][0], uint32_t(it) & 1)) return false;
-                tc::tc_fence_after_sync();
-                issue_pv_half(it, 0);
-                tc::umma_commit(&bars->p_lo_free[h]);  // P columns of the first 64 keys may be rewritten
-                if (!tc::mbar_wait(&bars->p_half[h][1], uint32_t(it) & 1)) return false;
-                tc::tc_fence_after_sync();
-                issue_pv_half(it, 1);
-                tc::umma_commit(&bars->o_done[h]);
-                tc::umma_commit(&bars->v_empty[stage_of(it)]);
-                return true;
-            };
-            // The score buffer is used by the heads in strict alternation (0,1,0,1,...): a score MMA
-            // may overwrite it once the other head's softmax warpgroup has pulled its tile into
-            // registers. Because P has its own columns, the score MMA of tile it+1 does not wait for
-            // PV of tile it, so each head's next S is ready long before its warpgroup comes back.
-            bool ok = tc::mbar_wait(&bars->q_full, 0);
-            for (int it = 0; ok && it < n_tiles; ++it) {
-                if (!(ok = tc::mbar_wait(&bars->k_full[stage_of(it)], parity_of(it)))) break;
-                if (it > 0 && !(ok = tc::mbar_wait(&bars->v_full[stage_of(it - 1)], parity_of(it - 1)))) break;  // for PV(it-1) below
-                if (h == 0) {
-                    if (it > 0 && !(ok = tc::mbar_wait(&bars->s_free[1], uint32_t(it - 1) & 1))) break;
-                } else {
-                    if (!(ok = tc::mbar_wait(&bars->s_free[0], uint32_t(it) & 1))) break;
-                }
-                tc::tc_fence_after_sync();
-                issue_qk(it);
-                if (it > 0 && !(ok = issue_pv(it - 1))) break;
             }
-            if (ok) ok = tc::mbar_wait(&bars->v_full[stage_of(n_tiles - 1)], parity_of(n_tiles - 1));
-            if (ok) ok = issue_pv(n_tiles - 1);
             if (!ok) {
                 atomicCAS(p.status, 0, 13);
                 bars->abort = 1;
