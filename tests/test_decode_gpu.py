@@ -134,6 +134,42 @@ def test_config4_full_size(ops, gpu_device):
     assert not kcache[:, length + 2:].any() and not vcache[:, length + 2:].any()
 
 
+def test_config5_full_size(ops, gpu_device):
+    """BASELINE config 5 on one GPU: batch 4, 32768 rows attended (old_len 32767, the new row lands in the
+    last cache row), seed 4. Checked against the oracle, and against eight KV-sequence shards of the same
+    caches merged by the combine kernel (the multi-GPU decomposition on one device)."""
+    batch, capacity, shards = 4, 32768, 8
+    generator = torch.Generator().manual_seed(4)
+    kcache = torch.randn((batch, capacity, 8, 128), generator=generator).to(torch.bfloat16)
+    vcache = torch.randn((batch, capacity, 8, 128), generator=generator).to(torch.bfloat16)
+    q, knew, vnew = (torch.randn(shape, generator=generator).to(torch.bfloat16)
+                     for shape in ((batch, 1, 32, 128), (batch, 1, 8, 128), (batch, 1, 8, 128)))
+    old = torch.full((batch,), capacity - 1, dtype=torch.int32)
+    want_o, want_lse, want_k, want_v = oracle.decode_step(q, kcache, vcache, knew, vnew, old)
+    got_o, got_lse, got_k, got_v, _ = run_step(ops, gpu_device, q, kcache, vcache, knew, vnew, old)
+    oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+    assert torch.equal(bits(got_k), bits(want_k)) and torch.equal(bits(got_v), bits(want_v))
+    del got_k, got_v, want_k, want_v
+    device = gpu_device
+    dq, dkn, dvn, dold = q.to(device), knew.to(device), vnew.to(device), old.to(device)
+    part_o = torch.empty((shards, batch * 32, 128), device=device, dtype=torch.float32)
+    part_lse = torch.empty((shards, batch * 32), device=device, dtype=torch.float32)
+    length = capacity // shards
+    for s in range(shards):
+        dk = kcache[:, s * length:(s + 1) * length].contiguous().to(device)
+        dv = vcache[:, s * length:(s + 1) * length].contiguous().to(device)
+        spec = ops.workspace_spec(dq, dk, dold, 0, 1, True)
+        ws = [torch.empty(n, device=device, dtype=torch.float32) for n in spec[1:3]]
+        ops.partial_out(dq, dk, dv, dkn, dvn, dold, part_o[s], part_lse[s], *ws, 0, 1, True, s * length)
+    out = torch.empty((batch, 1, 32, 128), device=device, dtype=torch.bfloat16)
+    lse = torch.empty((batch, 32, 1), device=device, dtype=torch.float32)
+    ops.combine_partials(part_o, part_lse, out, lse)
+    torch.cuda.synchronize()
+    assert ops.library.device_status(device.index) == 0
+    oracle.check_outputs(out.cpu(), lse.cpu(), want_o, want_lse)
+    assert (out.cpu().float() - got_o.float()).abs().max().item() <= 2e-2
+
+
 def test_sharded_partials_and_combine(ops, gpu_device):
     """KV-sequence shards produce partials whose LSE-weighted merge equals the unsharded step."""
     batch, capacity, shards = 4, 2048, 4

@@ -113,6 +113,26 @@ def test_long_sequence_rows_against_oracle(ops, gpu_device):
             oracle.check_outputs(got_o[0, rows, g * 4:(g + 1) * 4], got_lse[0, g * 4:(g + 1) * 4, rows], want_o, want_lse)
 
 
+def test_batch_four_is_four_independent_sequences(ops, gpu_device):
+    """Config-3 shape B4 x 8192: every sequence of the batch gives the bits of the same sequence run alone,
+    and a sample of rows of the last sequence matches the oracle."""
+    tokens = 8192
+    q, k, v = oracle.seeded_normal(2, (4, tokens, 32, 128), (4, tokens, 8, 128), (4, tokens, 8, 128))
+    got_o, got_lse = run_prefill(ops, gpu_device, q, k, v)
+    for b in (0, 3):
+        alone_o, alone_lse = run_prefill(ops, gpu_device, q[b:b + 1], k[b:b + 1], v[b:b + 1])
+        assert torch.equal(bits(alone_o[0]), bits(got_o[b]))
+        assert torch.equal(alone_lse[0].view(torch.int32), got_lse[b].view(torch.int32))
+    r0, g = 5000, 6
+    rows = slice(r0, r0 + 64)
+    qh = q[3, rows, g * 4:(g + 1) * 4].float().permute(1, 0, 2)
+    scores = (qh @ k[3, :r0 + 64, g].float().T) * 128 ** -0.5
+    scores.masked_fill_(torch.arange(r0 + 64)[None, :] > torch.arange(r0, r0 + 64)[:, None], float("-inf"))
+    want_o = (scores.softmax(-1) @ v[3, :r0 + 64, g].float()).permute(1, 0, 2)
+    oracle.check_outputs(got_o[3, rows, g * 4:(g + 1) * 4], got_lse[3, g * 4:(g + 1) * 4, rows], want_o,
+                         scores.logsumexp(-1))
+
+
 def test_argument_checks(ops, gpu_device):
     q, k, v = (t.to(gpu_device) for t in oracle.seeded_normal(1, (1, 128, 32, 128), (1, 128, 8, 128), (1, 128, 8, 128)))
     out, lse = torch.empty_like(q), torch.empty((1, 32, 128), device=gpu_device)
