@@ -17,8 +17,11 @@ reference's saved Qwen3 projections). A step is one forward over that batch.
                  neighbouring steps overlap on three streams.
 * ``roofline``   the prefill kernel against the measured dense BF16 peak.
 * ``decode``     split-KV decode with fused append: config 4 (batch 1, 8192 of 32768 rows valid) and
-                 config 5 (batch 4, 32768 rows attended; KV sequence sharded over the ranks when N > 1,
-                 one all-gather plus the LSE combine per step), as HBM GB/s with their own roofline.
+                 config 5 (batch 4, 32768 rows attended; KV sequence sharded over the ranks when N > 1 and
+                 merged inside the decode launch over NVLink, with the all-gather + combine route beside
+                 it as ``c5_nccl``), as HBM GB/s with their own roofline.
+* ``project``    the step before decode (fused QKV projection + head RMS norm + RoPE, 4 tokens, Qwen3-4B
+                 shapes) as HBM GB/s of streamed weights.
 * ``prefill_sharded`` (N > 1) config 2 itself split by KV-head group over the ranks (strong scaling).
 * ``cpu_baseline`` the CPU oracle (the reference's only CPU attention, ``bench_exchange.py:54-60``)
                  timed on this host on a bounded sample.
@@ -417,6 +420,50 @@ def run_ours(args, rank, world, local_rank):
         decode["c5"] = decode_case(DECODE_C5, sets=2, graph_steps=4, sharded=None)
         decode["c5"]["workload"] = "config5 B4 32768 rows attended (new row lands at index 32767), one GPU"
 
+    # ------------------------------------------------------------------ the step before decode (replicas at N > 1)
+    def project_case(tokens, hidden=2560, sets=8, graph_steps=16):
+        nonlocal launches
+        ops = cuda_runtime.ops_for(library, "project")
+        rows = (HQ + 2 * HKV) * DIM
+        generator = torch.Generator(device=device).manual_seed(7 + rank)
+        weights = [(torch.randn((rows, hidden), generator=generator, device=device) / hidden ** 0.5).to(torch.bfloat16)
+                   for _ in range(sets)]  # rotating weight sets, together larger than L2
+        x = torch.randn((tokens, hidden), generator=generator, device=device).to(torch.bfloat16)
+        norm = [torch.ones(DIM, device=device, dtype=torch.bfloat16) for _ in range(2)]
+        angles = torch.rand((32768, DIM // 2), generator=generator, device=device)
+        cos, sin = angles.cos(), angles.sin()
+        positions = torch.full((tokens,), 8192, dtype=torch.int32, device=device)
+        outs = [torch.empty((tokens, 1, heads, DIM), device=device, dtype=torch.bfloat16) for heads in (HQ, HKV, HKV)]
+        counter = [0]
+
+        def step():
+            ops.forward_out(x, weights[counter[0] % sets], positions, *outs, q_norm_weight=norm[0],
+                            k_norm_weight=norm[1], rope_cos=cos, rope_sin=sin)
+            counter[0] += 1
+
+        step()
+        torch.cuda.synchronize(device)
+        stream = torch.cuda.Stream(device)
+        with torch.cuda.stream(stream):
+            step()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(graph_steps):
+                    step()
+        replays = 10
+        ms = timed(graph.replay, replays, 3) / (replays * graph_steps)
+        launches += replays * graph_steps
+        moved = rows * hidden * 2 + tokens * hidden * 2 + tokens * (HQ + 2 * HKV) * DIM * 2
+        gbs = moved / (ms * 1e-3) / 1e9
+        return {"workload": f"fused QKV projection + head RMS norm + RoPE, {tokens} token(s), hidden {hidden}, "
+                            f"{HQ}+{HKV}+{HKV} heads (Qwen3-4B shapes), weights streamed from HBM",
+                "us_per_step_graph": ms * 1e3, "bytes_per_step": moved,
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
+                             "frac": gbs / peaks["hbm"], "traffic": None, "peak_source": peaks["source"]}}
+
+    project = project_case(tokens=4)
+
     status = library.device_status(device.index)
     if status != 0:
         raise RuntimeError(f"a kernel reported an expired wait (status {status}); results are invalid")
@@ -440,7 +487,7 @@ def run_ours(args, rank, world, local_rank):
                          "traffic": NCU_TRAFFIC_BYTES["prefill_c2"], "peak_source": peaks["source"] + " burst"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                     "ms_per_step": e2e_ms / args.steps},
-            "clocks": clocks, "gpu_launches": launches, "decode": decode,
+            "clocks": clocks, "gpu_launches": launches, "decode": decode, "project": project,
         }
         if prefill_sharded:
             line["prefill_sharded"] = prefill_sharded

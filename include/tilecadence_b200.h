@@ -211,6 +211,28 @@ int tc_peer_block_destroy(int device, void* block);
 int tc_decode_resources(int device, int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits,
                         int64_t mapping, int append, int64_t* values, int64_t capacity_values, int64_t* count);
 
+/* ---------------------------------------------------------------------------------- the step before decode
+ * Fused QKV projection + per-head RMS norm + RoPE for one new token per sequence, writing q, knew and vnew in
+ * the layout tc_decode_forward_out takes. No counterpart in the reference, whose decode kernel is handed
+ * pre-rotated Q/K and one new row (ab_fused_splitkv.cuh:189).
+ *   x BF16 [tokens, hidden] (1 <= tokens <= 8, hidden a multiple of 64); w_qkv BF16 [(q_heads + 2*kv_heads)*128,
+ *   hidden] row-major, rows ordered q heads, k heads, v heads; y = x w_qkv^T accumulated in FP32.
+ *   q_norm_weight / k_norm_weight BF16 [128] or NULL: y * rsqrt(mean(y^2) + rms_eps) rounded to BF16, times the
+ *   weight, rounded to BF16 (Qwen3's per-head norm). Without a weight y is rounded to BF16.
+ *   rope_cos / rope_sin FP32 [rope_positions, 64] or both NULL, positions int32 [tokens] on the device
+ *   (old_lengths): rotate-half RoPE of the q and k heads as in tc_decode_rope_forward_out. v heads get neither
+ *   norm nor RoPE.
+ *   q_out BF16 [tokens,1,q_heads,128], knew_out / vnew_out BF16 [tokens,1,kv_heads,128].
+ * Weight-streaming, HBM-bound: one cluster of up to 4 CTAs per head splits the hidden dimension and reduces
+ * through distributed shared memory. The kernel is launched with programmatic dependent launch and starts
+ * reading w_qkv before the preceding kernel of the stream has finished: the weights must not be an output of
+ * that kernel (x, positions, tables and norm weights may be). */
+int tc_qkv_rope_forward_out(int device, void* stream, const void* x, const void* w_qkv, const void* q_norm_weight,
+                            const void* k_norm_weight, const float* rope_cos, const float* rope_sin,
+                            int64_t rope_positions, const int32_t* positions, void* q_out, void* knew_out,
+                            void* vnew_out, int64_t tokens, int64_t hidden, int64_t q_heads, int64_t kv_heads,
+                            double rms_eps);
+
 /* ---------------------------------------------------------------------------------- two-tile exchange
  * Complete attention for 64 queries x 64 keys per (batch, head), D = 128, FP16 or BF16, generated as
  * straight-line code from a residency-exchange plan. Replaces `forward_out(q,k,v,out!,lse!,nonce,causal,

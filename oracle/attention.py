@@ -124,6 +124,35 @@ def rope_rotate(x, cos, sin):
     return torch.cat([out_lo, out_hi], dim=-1).to(x.dtype)
 
 
+def project_qkv_rope(x, w_qkv, positions, q_heads, kv_heads, q_norm_weight=None, k_norm_weight=None, cos=None,
+                     sin=None, rms_eps=1e-6):
+    """The step before decode attention for one new token per sequence: y = x W^T in fp32, per-head RMS
+    norm of the q and k heads (x * rsqrt(mean(x^2) + eps) rounded to the input dtype, times the weight,
+    rounded again: the form Qwen3 uses), rotate-half RoPE of q and k for ``positions``, v untouched.
+
+    x [tokens, hidden], w_qkv [(q_heads + 2 kv_heads) * 128, hidden], rows ordered q, k, v heads.
+    Returns q [tokens,1,q_heads,128], knew and vnew [tokens,1,kv_heads,128] in x's dtype. The reference
+    has no such step (its decode op receives these tensors); this restates the published model math.
+    """
+    tokens = x.size(0)
+    y = (x.float() @ w_qkv.float().T).view(tokens, q_heads + 2 * kv_heads, 128)
+
+    def normed(part, weight):
+        if weight is None:
+            return part.to(x.dtype)
+        scaled = part * torch.rsqrt(part.pow(2).mean(-1, keepdim=True) + rms_eps)
+        return (scaled.to(x.dtype).float() * weight.float()).to(x.dtype)
+
+    q = normed(y[:, :q_heads], q_norm_weight)
+    k = normed(y[:, q_heads:q_heads + kv_heads], k_norm_weight)
+    v = y[:, q_heads + kv_heads:].to(x.dtype)
+    if cos is not None:
+        position = positions.long().clamp(0, cos.size(0) - 1)
+        c, s = cos[position][:, None, :], sin[position][:, None, :]
+        q, k = rope_rotate(q, c, s), rope_rotate(k, c, s)
+    return q[:, None], k[:, None], v[:, None]
+
+
 def decode_step_rope(q, kcache, vcache, knew, vnew, old_lengths, cos, sin, append=True, scale=DEFAULT_SCALE):
     """:func:`decode_step` on un-rotated q / knew: both are rotated for position ``old_lengths[b]``
     (clamped to the table), rounded to their dtype, and the step runs on the rotated tensors."""

@@ -149,3 +149,22 @@ def test_rotary_embedding_restatement():
     want = oracle.decode_step(oracle.rope_rotate(q, pc, ps), kcache, vcache, oracle.rope_rotate(knew, pc, ps), vnew, old)
     assert all(torch.equal(g, w) for g, w in zip(got, want))
     assert torch.equal(got[2][0, 40], oracle.rope_rotate(knew, pc, ps)[0, 0]) and got[2].dtype == torch.bfloat16
+
+
+def test_projection_step_restatement():
+    """project_qkv_rope = matmul, then exactly the norm and RoPE functions above, head by head."""
+    x, w, qn, kn = oracle.seeded_normal(8, (3, 256), (48 * 128, 256), (128,), (128,), dtype=torch.float32)
+    x, w = x.to(torch.bfloat16), (w / 16).to(torch.bfloat16)
+    qn, kn = (1 + 0.1 * qn).to(torch.bfloat16), (1 + 0.1 * kn).to(torch.bfloat16)
+    cos, sin = oracle.rope_tables(64)
+    positions = torch.tensor([0, 5, 63], dtype=torch.int32)
+    q, k, v = oracle.project_qkv_rope(x, w, positions, 32, 8, qn, kn, cos, sin)
+    assert q.shape == (3, 1, 32, 128) and k.shape == (3, 1, 8, 128) and v.shape == (3, 1, 8, 128)
+    y = (x.float() @ w.float().T).view(3, 48, 128)
+    assert torch.equal(v[:, 0], y[:, 40:].to(torch.bfloat16))
+    head = y[1, 33]  # a k head of token 1
+    normed = ((head * torch.rsqrt(head.pow(2).mean() + 1e-6)).to(torch.bfloat16).float() * kn.float()).to(torch.bfloat16)
+    assert torch.equal(k[1, 0, 1], oracle.rope_rotate(normed, cos[5], sin[5]))
+    plain = oracle.project_qkv_rope(x, w, None, 32, 8)
+    assert torch.equal(plain[0][:, 0], y[:, :32].to(torch.bfloat16))
+    assert torch.equal(q[0], oracle.project_qkv_rope(x, w, positions, 32, 8, qn, kn)[0][0])  # position 0: no rotation

@@ -1,0 +1,106 @@
+"""The fused QKV projection + RMS norm + RoPE step (``tc_qkv_rope_forward_out``) against its CPU oracle.
+
+The accumulation order of a 2560-term dot product differs between the tensor-core kernel and the host, so
+the fp32 sums agree to rounding noise only and results are compared after the BF16 roundings with a
+two-ulp bound (2^-7 relative to max(1, |expected|)); without norm and RoPE almost every element must be
+bit-identical. The step's outputs then feed the decode operator, which must agree with the operator fed
+by the oracle's outputs within the decode tolerances.
+"""
+import pytest
+import torch
+
+from oracle import attention as oracle
+from tilecadence_b200 import cuda_runtime
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def project(library):
+    return cuda_runtime.ops_for(library, "project")
+
+
+def make_inputs(seed, tokens, hidden, q_heads=32, kv_heads=8):
+    rows = (q_heads + 2 * kv_heads) * 128
+    x, w, qn, kn = oracle.seeded_normal(seed, (tokens, hidden), (rows, hidden), (128,), (128,), dtype=torch.float32)
+    w = (w / hidden ** 0.5).to(torch.bfloat16)
+    return x.to(torch.bfloat16), w, (1 + 0.1 * qn).to(torch.bfloat16), (1 + 0.1 * kn).to(torch.bfloat16)
+
+
+def run(project, device, x, w, positions, qn=None, kn=None, cos=None, sin=None):
+    tokens = x.size(0)
+    move = lambda t: None if t is None else t.to(device)
+    outs = [torch.full((tokens, 1, heads, 128), float("nan"), device=device, dtype=torch.bfloat16)
+            for heads in (project.q_heads, project.kv_heads, project.kv_heads)]
+    project.forward_out(move(x), move(w), move(positions), *outs, q_norm_weight=move(qn), k_norm_weight=move(kn),
+                        rope_cos=move(cos), rope_sin=move(sin))
+    torch.cuda.synchronize()
+    assert project.library.device_status(device.index) == 0
+    return [t.cpu() for t in outs]
+
+
+def close(got, want, exact_share):
+    got, want = got.float(), want.float()
+    assert torch.isfinite(got).all()
+    assert ((got - want).abs() <= 2 ** -7 * want.abs().clamp_min(1.0)).all()
+    assert (got == want).float().mean().item() >= exact_share
+
+
+@pytest.mark.parametrize("tokens,hidden", [(1, 2560), (4, 2560), (8, 4096), (3, 64), (5, 192)])
+def test_plain_projection(project, gpu_device, tokens, hidden):
+    x, w, _, _ = make_inputs(10 + tokens, tokens, hidden)
+    want = oracle.project_qkv_rope(x, w, None, 32, 8)
+    got = run(project, gpu_device, x, w, None)
+    for g, t in zip(got, want):
+        close(g, t, 0.97)
+
+
+@pytest.mark.parametrize("tokens", [1, 4])
+def test_norm_and_rope_like_qwen3(project, gpu_device, tokens):
+    x, w, qn, kn = make_inputs(20 + tokens, tokens, 2560)
+    cos, sin = oracle.rope_tables(4096)
+    positions = torch.tensor([4095, 0, 17, 1234][:tokens], dtype=torch.int32)
+    want = oracle.project_qkv_rope(x, w, positions, 32, 8, qn, kn, cos, sin)
+    got = run(project, gpu_device, x, w, positions, qn, kn, cos, sin)
+    for g, t in zip(got, want):
+        close(g, t, 0.85)
+
+
+def test_feeds_the_decode_operator(project, library, gpu_device):
+    """The projected q / knew / vnew go straight into the decode operator (same layout, no copy or cast):
+    its result matches the oracle's decode of the same tensors, and the row appended to the K cache is the
+    projected, normed and rotated K row."""
+    tokens, capacity = 4, 512
+    x, w, qn, kn = make_inputs(31, tokens, 2560)
+    cos, sin = oracle.rope_tables(capacity)
+    old = torch.tensor([100, 0, 511, 257], dtype=torch.int32)
+    kcache, vcache = oracle.seeded_normal(32, (tokens, capacity, 8, 128), (tokens, capacity, 8, 128))
+    q, knew, vnew = run(project, gpu_device, x, w, old, qn, kn, cos, sin)
+    want_q, want_k, want_v = oracle.project_qkv_rope(x, w, old, 32, 8, qn, kn, cos, sin)
+    for got, want in ((q, want_q), (knew, want_k), (vnew, want_v)):
+        close(got, want, 0.85)
+    want_o, want_lse, _, _ = oracle.decode_step(q, kcache, vcache, knew, vnew, old)
+    decode = cuda_runtime.ops_for(library, "decode")
+    device = gpu_device
+    dq, dk, dv, dkn, dvn, dold = (t.to(device) for t in (q, kcache, vcache, knew, vnew, old))
+    out, lse = torch.empty_like(dq), torch.empty((tokens, 32, 1), device=device, dtype=torch.float32)
+    spec = decode.workspace_spec(dq, dk, dold, 0, 1, True)
+    ws = [torch.empty(n, device=device, dtype=torch.float32) for n in spec[1:3]]
+    decode.forward_out(dq, dk, dv, dkn, dvn, dold, out, lse, *ws, 0, 1, True)
+    torch.cuda.synchronize()
+    oracle.check_outputs(out.cpu(), lse.cpu(), want_o, want_lse)
+    for b in range(tokens):
+        assert torch.equal(dk[b, old[b]].cpu().view(torch.int16), knew[b, 0].view(torch.int16))
+
+
+def test_argument_checks(project, gpu_device):
+    x, w, _, _ = make_inputs(1, 2, 128)
+    outs = [torch.empty((2, 1, h, 128), device=gpu_device, dtype=torch.bfloat16) for h in (32, 8, 8)]
+    cos, sin = oracle.rope_tables(8)
+    with pytest.raises(RuntimeError, match="tokens<=8"):
+        project.forward_out(torch.zeros((9, 128), device=gpu_device, dtype=torch.bfloat16), w.to(gpu_device), None, *outs)
+    with pytest.raises(RuntimeError, match="both RoPE"):
+        project.forward_out(x.to(gpu_device), w.to(gpu_device), None, *outs, rope_cos=cos.to(gpu_device))
+    with pytest.raises(RuntimeError, match="multiple of 64"):
+        bad = torch.zeros((2, 96), device=gpu_device, dtype=torch.bfloat16)
+        project.forward_out(bad, torch.zeros((6144, 96), device=gpu_device, dtype=torch.bfloat16), None, *outs)

@@ -179,6 +179,9 @@ class Library:
         "tc_decode_partial_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, ctypes.c_int64)),
+        "tc_qkv_rope_forward_out": (ctypes.c_int, (
+            ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 6, ctypes.c_int64, *[ctypes.c_void_p] * 4,
+            *[ctypes.c_int64] * 4, ctypes.c_double)),
         "tc_decode_rope_forward_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
@@ -630,6 +633,50 @@ class ExchangeOps:
         return list(values)
 
 
+class ProjectOps:
+    """The step before decode attention: fused QKV projection, per-head RMS norm and RoPE for one new
+    token per sequence (``tc_qkv_rope_forward_out``). The reference has no such operator; its decode op
+    takes the results as inputs."""
+
+    phase = "project"
+
+    def __init__(self, library, q_heads=32, kv_heads=8):
+        self.library, self.q_heads, self.kv_heads = library, q_heads, kv_heads
+
+    def forward_out(self, x, w_qkv, positions, q_out, knew_out, vnew_out, q_norm_weight=None, k_norm_weight=None,
+                    rope_cos=None, rope_sin=None, rms_eps=1e-6):
+        import torch
+
+        tokens, hidden = x.shape
+        rows = (self.q_heads + 2 * self.kv_heads) * 128
+        _require(x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and 1 <= tokens <= 8,
+                 "x must be contiguous CUDA BF16[tokens<=8,hidden]")
+        _require(w_qkv.device == x.device and w_qkv.dtype == x.dtype and w_qkv.is_contiguous()
+                 and tuple(w_qkv.shape) == (rows, hidden), "w_qkv must be contiguous BF16[(Hq+2Hkv)*128,hidden]")
+        for tensor, heads in ((q_out, self.q_heads), (knew_out, self.kv_heads), (vnew_out, self.kv_heads)):
+            _require(tensor.device == x.device and tensor.dtype == x.dtype and tensor.is_contiguous()
+                     and tuple(tensor.shape) == (tokens, 1, heads, 128), "outputs must be BF16[tokens,1,heads,128]")
+        for weight in (q_norm_weight, k_norm_weight):
+            _require(weight is None or (weight.device == x.device and weight.dtype == x.dtype
+                                        and tuple(weight.shape) == (128,) and weight.is_contiguous()),
+                     "norm weights must be BF16[128]")
+        _require((rope_cos is None) == (rope_sin is None), "pass both RoPE tables or neither")
+        if rope_cos is not None:
+            for table in (rope_cos, rope_sin):
+                _require(table.device == x.device and table.dtype == torch.float32 and table.dim() == 2
+                         and table.size(1) == 64 and table.is_contiguous() and table.shape == rope_cos.shape,
+                         "RoPE tables must be contiguous FP32[positions,64]")
+            _require(positions is not None and positions.device == x.device and positions.dtype == torch.int32
+                     and tuple(positions.shape) == (tokens,) and positions.is_contiguous(),
+                     "positions must be contiguous int32[tokens]")
+        optional = lambda tensor: _pointer(tensor) if tensor is not None else None
+        self.library.call(
+            "tc_qkv_rope_forward_out", x.device.index, _stream(x), _pointer(x), _pointer(w_qkv),
+            optional(q_norm_weight), optional(k_norm_weight), optional(rope_cos), optional(rope_sin),
+            rope_cos.size(0) if rope_cos is not None else 0, optional(positions), _pointer(q_out), _pointer(knew_out),
+            _pointer(vnew_out), tokens, hidden, self.q_heads, self.kv_heads, float(rms_eps))
+
+
 def ops_for(library, phase=None, q_heads=32):
     if phase is None:
         phase = ("prefill" if library.has("tc_prefill_") else "decode" if library.has("tc_decode_")
@@ -640,6 +687,8 @@ def ops_for(library, phase=None, q_heads=32):
         return PrefillOps(library, q_heads)
     if phase == "decode":
         return DecodeOps(library, q_heads)
+    if phase == "project":
+        return ProjectOps(library, q_heads, q_heads // 4)
     raise RuntimeError(f"{library.path} exports neither the prefill nor the decode operator")
 
 
