@@ -43,8 +43,8 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the three benchmarked launches, from
-# the ncu captures summarised under profiles/ (prefill_kernel_config2.md, decode_splitkv_kernel_config4_config5.md).
-NCU_TRAFFIC_BYTES = {"prefill_c2": 119.5e6, "decode_c4": 33.62e6, "decode_c5": 541.2e6}
+# the ncu captures summarised under profiles/.
+NCU_TRAFFIC_BYTES = {"prefill_c2": 119.5e6, "decode_c4": 33.62e6, "decode_c5": 541.2e6, "project": 31.5e6}
 HQ, HKV, DIM = 32, 8, 128
 SCALE = DIM ** -0.5
 PREFILL = dict(batch=1, tokens=8192, seed=1)
@@ -460,7 +460,8 @@ def run_ours(args, rank, world, local_rank):
                             f"{HQ}+{HKV}+{HKV} heads (Qwen3-4B shapes), weights streamed from HBM",
                 "us_per_step_graph": ms * 1e3, "bytes_per_step": moved,
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
-                             "frac": gbs / peaks["hbm"], "traffic": None, "peak_source": peaks["source"]}}
+                             "frac": gbs / peaks["hbm"], "traffic": NCU_TRAFFIC_BYTES["project"] if (tokens, hidden) == (4, 2560) else None,
+                             "peak_source": peaks["source"]}}
 
     project = project_case(tokens=4)
 
