@@ -188,7 +188,7 @@ int tc_decode_rope_forward_out(int device, void* stream, const void* q, void* kc
  * (fp32 [B,Hq]). peer_blocks[r] is rank r's exchange block as mapped into this process
  * (peer_blocks[rank] is this rank's own block). All ranks must make the same sequence of calls with
  * the same batch, kv_heads and world on the same blocks. splits * Hkv * B CTAs must be resident at
- * once (rejected otherwise). No TMA multicast and no collective library call is involved.
+ * once (rejected otherwise). Plain stores only; no collective library call is involved.
  *
  * Exchange blocks: tc_peer_block_bytes gives the size for (batch, kv_heads, world);
  * tc_peer_block_create allocates and zeroes one on `device` and returns a 64-byte interprocess handle;
