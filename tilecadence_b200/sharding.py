@@ -13,8 +13,9 @@ configurations call for, one process per GPU with ``torch.distributed`` for the 
   - ``exchange="nccl"``: one all-gather of the packed partials (``B*Hq*129`` floats per rank), then
     the LSE-weighted combine kernel. Three launches per step; the collective's latency dominates.
   - ``exchange="peer"``: one launch. The decode kernel itself stores the rank's partial into every
-    rank's exchange block over NVLink (plain peer stores only), signals with
-    system-scope flags and merges in the same CTA. See ``tc_decode_exchange_out`` in the header.
+    rank's exchange block over NVLink (plain peer stores only; every 4-byte value travels with the
+    call's epoch in the same 8-byte word, so no fence or separate flag is needed), polls its own block
+    and merges in the same CTA. See ``tc_decode_exchange_out`` in the header.
 """
 from __future__ import annotations
 
