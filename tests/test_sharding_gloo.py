@@ -160,3 +160,38 @@ def test_peer_blocks_are_mapped_by_all_ranks_or_by_none(fail_on):
             assert state == "refused" and message.startswith("peer exchange unavailable")
             assert calls[-1] == "tc_peer_block_destroy"
         assert "tc_peer_block_close" in results[0][2] and "tc_peer_block_close" not in results[1][2]
+
+
+def absent_rank_worker(rank, world, port, results):
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    batch, capacity = 1, 64
+    kcache, vcache, q, knew, vnew = oracle.seeded_normal(2, (batch, capacity, 8, 128), (batch, capacity, 8, 128),
+                                                         (batch, 1, 32, 128), (batch, 1, 8, 128), (batch, 1, 8, 128))
+    start, length = sharding.kv_sequence_shard(rank, world, capacity)
+    driver = sharding.ShardedDecode(OracleOps(), rank, world, batch, capacity, torch.device("cpu"))
+    out = torch.empty((batch, 1, 32, 128), dtype=torch.bfloat16)
+    lse = torch.empty((batch, 32, 1), dtype=torch.float32)
+    old = torch.tensor([40], dtype=torch.int32)
+    if rank == 1:
+        results[rank] = "left"
+        return  # leaves between steps without joining the collective (its process then exits)
+    try:
+        driver.step(q, kcache[:, start:start + length].clone(), vcache[:, start:start + length].clone(), knew, vnew,
+                    old, out, lse)
+        results[rank] = "no error"
+    except Exception as error:  # the collective ends with an error instead of hanging
+        results[rank] = f"raised {type(error).__name__}"
+
+
+def test_a_rank_that_never_joins_ends_the_step_with_an_error():
+    """Failure on the host side, no GPU involved: one rank leaves before the exchange; the other rank's
+    collective returns an error within the process-group timeout and the step raises."""
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(absent_rank_worker, args=(world, free_port(), results), nprocs=world, join=True)
+    assert results[1] == "left"
+    assert results[0].startswith("raised"), results[0]
