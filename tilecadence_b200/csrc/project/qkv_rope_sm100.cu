@@ -11,7 +11,7 @@
 // (31.5 MB for hidden 2560, 32 + 8 + 8 heads), the arithmetic is negligible, so the bound is HBM
 // bandwidth. One cluster of `splits` CTAs owns one head's 128 output rows; CTA r of the cluster
 // streams the r-th slice of the hidden dimension as 128-row x 64-column weight tiles (16 KiB, TMA,
-// 128-byte swizzle, mbarrier ring), multiplies with warp-level BF16 MMAs against the token slab held in
+// 128-byte swizzle, 5-stage mbarrier ring), multiplies with warp-level BF16 MMAs against the token slab held in
 // shared memory, and ships its 128 x 8 partial sums into CTA 0's shared memory (distributed shared
 // memory stores + one cluster barrier). CTA 0 finishes the head: sum, RMS norm, RoPE, BF16 stores.
 #include "tc_host.cuh"
@@ -24,7 +24,8 @@ namespace {
 constexpr int kRows = 128;                       // outputs of one head
 constexpr int kTileK = 64;                       // hidden elements per weight tile: 128-byte rows
 constexpr int kTileBytes = kRows * kTileK * 2;   // 16 KiB
-constexpr int kStages = 8;
+constexpr int kStages = 5;                       // 80 KiB ring: two CTAs fit one SM at hidden 2560, so the next
+                                                 // launch's CTAs can start their weight ring during this one's tail
 constexpr int kWarps = 8;                        // 16 output rows per consumer warp
 constexpr int kConsumerThreads = kWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;  // + one TMA producer warp
@@ -58,7 +59,7 @@ __host__ __device__ constexpr int shared_bytes(int k_local) { return 1024 + barr
 
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
