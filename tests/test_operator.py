@@ -9,17 +9,35 @@ from tilecadence_b200.operator import OFFSETS, emit
 from tilecadence_b200.placement import HANDOFFS, replay
 
 
-@pytest.mark.parametrize("phase", ("prefill", "decode"))
-def test_solved_offsets_reach_the_cuda_template(tmp_path: Path, phase: str):
-    placement = emit(phase, tmp_path / phase)
-    config = (tmp_path / phase / "config.cuh").read_text()
-    offsets = {name: value["offset_bytes"] for name, value in placement["regions"].items()}
-    for name, macro in OFFSETS[phase].items():
-        assert f"#define {macro} {offsets[name]}\n" in config
-    first, second = offsets
-    offsets[second] = offsets[first]
+def defines_of(text):
+    """{macro: value} for every ``#define NAME <integer>`` line of a header."""
+    found = {}
+    for line in text.splitlines():
+        words = line.split()
+        if len(words) == 3 and words[0] == "#define" and words[2].lstrip("-").isdigit():
+            found[words[1]] = int(words[2])
+    return found
+
+
+@pytest.mark.parametrize("phase", sorted(OFFSETS))
+def test_emitted_config_carries_the_solved_offsets(tmp_path, phase):
+    """What the reference's ``tests/test_operator.py:9-19`` pins: every region's solved offset is the value
+    of its macro in the emitted ``config.cuh``, and a placement that puts two regions on the same bytes is
+    rejected by ``replay`` with an "overlap" error."""
+    directory = tmp_path / "emitted" / phase
+    solved = emit(phase, directory)
+    macros = defines_of((directory / "config.cuh").read_text())
+    placed = {}
+    for region, macro in OFFSETS[phase].items():
+        placed[region] = solved["regions"][region]["offset_bytes"]
+        assert macros[macro] == placed[region]
+    assert set(placed) == set(solved["regions"])
+    replay(HANDOFFS[phase], placed)  # the solved placement itself is accepted
+    regions = list(placed)
+    collided = dict(placed)
+    collided[regions[1]] = collided[regions[0]]
     with pytest.raises(ValueError, match="overlap"):
-        replay(HANDOFFS[phase], offsets)
+        replay(HANDOFFS[phase], collided)
 
 
 def test_emit_is_self_contained_and_never_overwrites(tmp_path: Path):

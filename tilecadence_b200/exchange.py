@@ -106,150 +106,193 @@ def build_problem(arm):
                                provenance={PROVENANCE_KEY: contract}, plan=plan_for(arm))
 
 
+class _Audit:
+    """Read-only view of a solved plan with the checks ``verify`` is built from. Every failed check
+    raises ``ValueError`` (through :func:`model.require`) prefixed with the arm's name."""
+
+    def __init__(self, arm, contract, result):
+        self.arm = arm
+        self.slab = model.SLAB_BYTES
+        self.arena_bytes = contract["arena_slabs"] * model.SLAB_BYTES
+        self.events = {event["id"]: event for event in result["events"]}
+        self.copies = {copy["id"]: copy for copy in result["copies"]}
+
+    def check(self, holds, what):
+        model.require(holds, f"{self.arm}: {what}")
+
+    def byte_span(self, copy):
+        """[first byte, one past the last byte] of a shared-memory copy, after checking it is slab-shaped."""
+        first, length = copy["offset_bytes"], copy["occupied_bytes"]
+        well_formed = (copy["tier"] == "smem" and model.integer(first) and model.integer(length, 1)
+                       and first % self.slab == 0 and length % self.slab == 0 and first + length <= self.arena_bytes)
+        self.check(well_formed, f"invalid arena span for {copy['id']}")
+        return [first, first + length]
+
+    def reads(self, consumer, port, producer_output):
+        known = consumer in self.events and producer_output in self.copies
+        self.check(known and self.events[consumer]["inputs"][port] == producer_output,
+                   f"{consumer} must consume {producer_output} at port {port}")
+
+    def in_source_order(self, *names):
+        pairs = zip(names, names[1:])
+        self.check(all(self.events[first]["end"] <= self.events[second]["start"] for first, second in pairs),
+                   "required source order " + " < ".join(names) + " is violated")
+
+    def checkpoint_path(self, tile, stats_port):
+        """P of ``tile`` goes registers -> shared -> registers between its two PV stripes."""
+        probabilities = f"stats_{tile}#0:out{stats_port}"
+        store, load = f"store_P{tile}#0", f"load_P{tile}#0"
+        self.reads(store, 0, probabilities)
+        self.reads(load, 0, f"{store}:out0")
+        self.reads(f"pv_{tile}_0#0", 0, probabilities)
+        self.reads(f"pv_{tile}_1#0", 0, f"{load}:out0")
+        self.in_source_order(f"pv_{tile}_0#0", load)
+
+
+def _disjoint(first, second):
+    return first[1] <= second[0] or second[1] <= first[0]
+
+
 def verify(contract, result):
-    """Independently validate actual selected bindings, intervals, and byte ranges."""
+    """Re-derive every promise of the arm's contract from a solved plan's events and copies.
+
+    Returns the residency certificate (donor and restore spans, each recipient's span and source steps,
+    the reservation windows); raises ``ValueError`` if the plan breaks the contract. Nothing here trusts
+    the planner: only the selected bindings, intervals and byte offsets recorded in ``result`` are read.
+    """
     arm = _arm(contract)
     model.require(result.get("status") in ("OPTIMAL", "FEASIBLE"), "Residency verification needs a solved plan")
-    events = {row["id"]: row for row in result["events"]}
-    copies = {row["id"]: row for row in result["copies"]}
-    slab, arena = model.SLAB_BYTES, contract["arena_slabs"] * model.SLAB_BYTES
+    audit = _Audit(arm, contract, result)
+    events, copies, check = audit.events, audit.copies, audit.check
+    moved_in = RECIPIENTS[arm]
 
-    def need(condition, message):
-        model.require(condition, f"{arm}: {message}")
+    # -- what every arm shares: the action set, the two Q reads, the original Q copy
+    score_actions = {event["id"] for event in events.values() if event["kind"] == "qk"}
+    check(score_actions == {"qk_0#0", "qk_1#0"}, "exactly one required QK per tile")
+    allowed_repeats = {"load_Q#1"} if arm == "retain" else {"load_Q#1", "copy_Q#1"}
+    check(all(identity.endswith("#0") or identity in allowed_repeats for identity in events),
+          "unexpected repeated action outside the common graph")
+    q_in_shared = {copy["id"] for copy in copies.values() if copy["role"] == "q" and copy["tier"] == "smem"}
+    check(q_in_shared == ({INITIAL_Q} if arm == "retain" else {INITIAL_Q, RESTORED_Q}), "unexpected shared Q copies")
+    audit.reads("load_Q#0", 0, INITIAL_Q)
+    audit.reads("qk_0#0", 0, "load_Q#0:out0")
+    original = copies[INITIAL_Q]
+    donor_span = audit.byte_span(original)
+    check(original["occupied_bytes"] == 16384, "full Q donor must occupy 16 KiB")
+    stored = {event["id"] + ":out0" for event in events.values() if event["kind"] == "store_r2s"}
+    check(stored == {name for name in moved_in if name.startswith("store_")}, "unexpected checkpoint path")
 
-    def span(copy):
-        lo, size = copy["offset_bytes"], copy["occupied_bytes"]
-        need(copy["tier"] == "smem" and model.integer(lo) and model.integer(size, 1) and lo % slab == 0
-             and size % slab == 0 and lo + size <= arena, f"invalid arena span for {copy['id']}")
-        return [lo, lo + size]
-
-    def bound(event, port, source):
-        need(event in events and source in copies and events[event]["inputs"][port] == source,
-             f"{event} must consume {source} at port {port}")
-
-    def ordered(*names):
-        need(all(events[a]["end"] <= events[b]["start"] for a, b in zip(names, names[1:])),
-             "required source order " + " < ".join(names) + " is violated")
-
-    need({e["id"] for e in events.values() if e["kind"] == "qk"} == {"qk_0#0", "qk_1#0"}, "exactly one required QK per tile")
-    repeats = {"load_Q#1"} | ({"copy_Q#1"} if arm != "retain" else set())
-    need(all(i.endswith("#0") or i in repeats for i in events), "unexpected repeated action outside the common graph")
-    shared_q = {c["id"] for c in copies.values() if c["tier"] == "smem" and c["role"] == "q"}
-    need(shared_q == ({INITIAL_Q} if arm == "retain" else {INITIAL_Q, RESTORED_Q}), "unexpected shared Q copies")
-    bound("load_Q#0", 0, INITIAL_Q)
-    bound("qk_0#0", 0, "load_Q#0:out0")
-    donor = copies[INITIAL_Q]
-    donor_span = span(donor)
-    need(donor["occupied_bytes"] == 16384, "full Q donor must occupy 16 KiB")
     certificate = {
         "contract": contract,
         "donor_span_bytes": donor_span,
-        "original_q_shared_source_steps": [donor["start"], donor["end"]],
+        "original_q_shared_source_steps": [original["start"], original["end"]],
         "recipients": [],
         "scope": "Address reservation and source-order dependencies; readiness on the GPU is what the emitted waits enforce",
     }
-    checkpoints = {e["id"] + ":out0" for e in events.values() if e["kind"] == "store_r2s"}
-    need(checkpoints == {p for p in RECIPIENTS[arm] if p.startswith("store_")}, "unexpected checkpoint path")
     if arm == "retain":
-        source = events["qk_1#0"]["inputs"][0]
-        if source != "load_Q#0:out0":
-            bound("qk_1#0", 0, "load_Q#1:out0")
-            bound("load_Q#1", 0, INITIAL_Q)
-        certificate["qk1_q_register_source"] = source
+        q_registers = events["qk_1#0"]["inputs"][0]
+        if q_registers != "load_Q#0:out0":  # Q was read from the one shared copy a second time
+            audit.reads("qk_1#0", 0, "load_Q#1:out0")
+            audit.reads("load_Q#1", 0, INITIAL_Q)
+        certificate["qk1_q_register_source"] = q_registers
         return certificate
 
-    bound("load_Q#1", 0, RESTORED_Q)
-    bound("qk_1#0", 0, "load_Q#1:out0")
-    restored = copies[RESTORED_Q]
-    restore_span = span(restored)
-    need(restored["occupied_bytes"] == donor["occupied_bytes"]
-         and (restore_span[1] <= donor_span[0] or donor_span[1] <= restore_span[0]),
-         "restore Q must use a disjoint address range")
-    need(events["qk_0#0"]["end"] <= restored["start"], "restore must follow the original QK")
-    need(copies["load_Q#0:out0"]["end"] == events["qk_0#0"]["end"], "original Q RF held beyond first QK")
-    certificate["restore_span_bytes"] = restore_span
-    certificate["restore_issue_source_step"] = restored["start"]
+    # -- Q is copied again, elsewhere, for the second score product
+    audit.reads("load_Q#1", 0, RESTORED_Q)
+    audit.reads("qk_1#0", 0, "load_Q#1:out0")
+    second_q = copies[RESTORED_Q]
+    second_span = audit.byte_span(second_q)
+    check(second_q["occupied_bytes"] == original["occupied_bytes"] and _disjoint(second_span, donor_span),
+          "restore Q must use a disjoint address range")
+    check(events["qk_0#0"]["end"] <= second_q["start"], "restore must follow the original QK")
+    check(copies["load_Q#0:out0"]["end"] == events["qk_0#0"]["end"], "original Q RF held beyond first QK")
+    certificate.update(restore_span_bytes=second_span, restore_issue_source_step=second_q["start"])
 
-    def checkpoint(tile, port):
-        produced = f"stats_{tile}#0:out{port}"
-        bound(f"store_P{tile}#0", 0, produced)
-        bound(f"load_P{tile}#0", 0, f"store_P{tile}#0:out0")
-        bound(f"pv_{tile}_0#0", 0, produced)
-        bound(f"pv_{tile}_1#0", 0, f"load_P{tile}#0:out0")
-        ordered(f"pv_{tile}_0#0", f"load_P{tile}#0")
-
-    checkpoint(0, 2)
-    ordered("pv_0_0#0", "qk_1#0", "load_P0#0")
+    # -- the checkpointed probabilities (and, for `multi`, the V stripe) and their ordering
+    audit.checkpoint_path(0, 2)
+    audit.in_source_order("pv_0_0#0", "qk_1#0", "load_P0#0")
     if arm == "multi":
-        bound("load_V0_1#0", 0, V)
-        bound("pv_0_1#0", 1, "load_V0_1#0:out0")
-        ordered("copy_Q#1", "load_V0_1#0")
-    elif arm == "relocated_two_p":
-        checkpoint(1, 3)
-        ordered("store_P1#0", "load_P0#0")
-
-    tenants = [copies[identity] for identity in RECIPIENTS[arm]]
-    for copy in tenants:
-        lo, hi = span(copy)
-        need(donor_span[0] <= lo < hi <= donor_span[1] and hi - lo == slab,
-             f"recipient {copy['id']} must occupy one slab in the vacated donor")
-        need(donor["end"] <= copy["start"] and copy["available"] < copy["end"],
-             f"recipient {copy['id']} has invalid donor reuse or no later consumer")
-        certificate["recipients"].append({"copy": copy["id"], "span_bytes": [lo, hi],
-                                          "source_steps": [copy["start"], copy["end"]],
-                                          "producer_end": copy["available"]})
-    early = tenants[:1] if arm == "relocated_two_p" else tenants
-    pre_start, pre_end = max(c["available"] for c in early), restored["start"]
-    need(pre_start < pre_end <= min(c["end"] for c in early), "no pre-restore recipient window")
-    certificate["pre_restore_reservation_source_steps"] = [pre_start, pre_end]
-    for copy in copies.values():
-        if copy["tier"] != "smem" or copy["id"] in (INITIAL_Q, RESTORED_Q, *RECIPIENTS[arm]):
-            continue
-        lo, hi = span(copy)
-        need(copy["end"] <= pre_start or pre_end <= copy["start"] or hi <= donor_span[0] or donor_span[1] <= lo,
-             f"undeclared occupant {copy['id']} in the pre-restore window")
-    joint_start, joint_end = max(c["available"] for c in tenants), min(c["end"] for c in tenants)
-    need(joint_start < joint_end, "no common recipient reservation window")
-    if len(tenants) == 2:
-        a, b = (span(c) for c in tenants)
-        need(a[1] <= b[0] or b[1] <= a[0], "simultaneous recipients overlap in address")
+        audit.reads("load_V0_1#0", 0, V)
+        audit.reads("pv_0_1#0", 1, "load_V0_1#0:out0")
+        audit.in_source_order("copy_Q#1", "load_V0_1#0")
     if arm == "relocated_two_p":
-        need(restored["available"] <= joint_start, "P1 is not available before Q is restored elsewhere")
-    certificate["joint_reservation_source_steps"] = [joint_start, joint_end]
+        audit.checkpoint_path(1, 3)
+        audit.in_source_order("store_P1#0", "load_P0#0")
+
+    # -- the recipients live in the vacated range, after the donor, with a consumer still to come
+    tenants = [copies[name] for name in moved_in]
+    for tenant in tenants:
+        tenant_span = audit.byte_span(tenant)
+        inside = donor_span[0] <= tenant_span[0] and tenant_span[1] <= donor_span[1]
+        check(inside and tenant_span[1] - tenant_span[0] == audit.slab,
+              f"recipient {tenant['id']} must occupy one slab in the vacated donor")
+        check(original["end"] <= tenant["start"] and tenant["available"] < tenant["end"],
+              f"recipient {tenant['id']} has invalid donor reuse or no later consumer")
+        certificate["recipients"].append({"copy": tenant["id"], "span_bytes": tenant_span,
+                                          "source_steps": [tenant["start"], tenant["end"]],
+                                          "producer_end": tenant["available"]})
+
+    # -- between "recipient produced" and "Q copied again" nobody else may sit in the donor's range
+    before_restore = tenants[:1] if arm == "relocated_two_p" else tenants
+    window = [max(tenant["available"] for tenant in before_restore), second_q["start"]]
+    check(window[0] < window[1] <= min(tenant["end"] for tenant in before_restore), "no pre-restore recipient window")
+    certificate["pre_restore_reservation_source_steps"] = window
+    declared = {INITIAL_Q, RESTORED_Q, *moved_in}
+    for other in copies.values():
+        if other["tier"] == "smem" and other["id"] not in declared:
+            outside_window = other["end"] <= window[0] or window[1] <= other["start"]
+            check(outside_window or _disjoint(audit.byte_span(other), donor_span),
+                  f"undeclared occupant {other['id']} in the pre-restore window")
+
+    # -- all recipients are resident together for a while, in different slabs
+    together = [max(tenant["available"] for tenant in tenants), min(tenant["end"] for tenant in tenants)]
+    check(together[0] < together[1], "no common recipient reservation window")
+    if len(tenants) == 2:
+        check(_disjoint(audit.byte_span(tenants[0]), audit.byte_span(tenants[1])),
+              "simultaneous recipients overlap in address")
+    if arm == "relocated_two_p":
+        check(second_q["available"] <= together[0], "P1 is not available before Q is restored elsewhere")
+    certificate["joint_reservation_source_steps"] = together
     return certificate
 
 
-def main():
-    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("--out", type=Path, required=True)
-    parser.add_argument("--arm", action="append", choices=ARMS)
-    parser.add_argument("--seconds", type=float, default=15)
-    parser.add_argument("--no-emit", action="store_true")
-    args = parser.parse_args()
-    model.require(0 < args.seconds <= 120, "Per-arm search budget must be between zero and 120 seconds")
-    arms = args.arm or ARMS
-    model.require(len(set(arms)) == len(arms), "Each arm may only be generated once")
-    args.out.mkdir(parents=True, exist_ok=False)
-    failures = []
-    for arm in arms:
-        role = args.out / arm
-        role.mkdir()
-        problem = build_problem(arm)
-        try:
-            result = model.solve(problem, max_time_seconds=args.seconds, artifact_dir=role / "solver")
-            certificate = verify(problem.provenance[PROVENANCE_KEY], result)
-            (role / "residency_certificate.json").write_text(json.dumps(certificate, indent=2) + "\n")
-            if not args.no_emit:
-                from .emit_exchange import emit
+def _run_arm(arm, directory, seconds, emit_sources):
+    """Plan, verify and (optionally) emit one arm into ``directory``; returns a one-line report."""
+    problem = build_problem(arm)
+    result = model.solve(problem, max_time_seconds=seconds, artifact_dir=directory / "solver")
+    certificate = verify(problem.provenance[PROVENANCE_KEY], result)
+    (directory / "residency_certificate.json").write_text(json.dumps(certificate, indent=2) + "\n")
+    if emit_sources:
+        from .emit_exchange import emit
 
-                emit(problem, result, role / "emitted")
-            print(f"{arm}: {result['status']}; {result['finish_step']} source steps", flush=True)
+        emit(problem, result, directory / "emitted")
+    return f"{result['status']}; {result['finish_step']} source steps"
+
+
+def main(argv=None):
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--out", required=True, type=Path, help="directory to create; one sub-directory per arm")
+    parser.add_argument("--arm", action="append", choices=ARMS, help="repeatable; default: all four arms")
+    parser.add_argument("--seconds", type=float, default=15, help="search budget per arm (scales a node budget)")
+    parser.add_argument("--no-emit", action="store_true", help="plan and verify only")
+    arguments = parser.parse_args(argv)
+    model.require(0 < arguments.seconds <= 120, "Per-arm search budget must be between zero and 120 seconds")
+    chosen = list(arguments.arm or ARMS)
+    model.require(len(chosen) == len(set(chosen)), "Each arm may only be generated once")
+    arguments.out.mkdir(parents=True, exist_ok=False)
+    failed = []
+    for arm in chosen:
+        directory = arguments.out / arm
+        directory.mkdir()
+        try:
+            report = _run_arm(arm, directory, arguments.seconds, not arguments.no_emit)
         except (ValueError, RuntimeError) as error:
-            (role / "failure.txt").write_text(str(error) + "\n")
-            failures.append(arm)
-            print(f"{arm}: {error}", flush=True)
-    if failures:
-        raise SystemExit("Unsuccessful arms: " + ", ".join(failures))
+            (directory / "failure.txt").write_text(f"{error}\n")
+            failed.append(arm)
+            report = str(error)
+        print(f"{arm}: {report}", flush=True)
+    if failed:
+        raise SystemExit("Unsuccessful arms: " + ", ".join(failed))
 
 
 if __name__ == "__main__":

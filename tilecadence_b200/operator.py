@@ -1,59 +1,84 @@
-"""Emit the prefill or decode schedule with solved shared-memory offsets.
+"""Turn a solved handoff into a buildable source directory for the prefill or the decode kernel.
 
-Same behaviour as ``tilecadence/operator.py`` (``OFFSETS`` :13-18, ``emit`` :21-38, CLI :41-46):
-solve the phase's handoff, rewrite exactly one ``#define <MACRO> <n>`` per region in the phase's
-``config.cuh``, copy the remaining template files next to it and write ``placement.json``. The
-output directory must not exist. The emitted directory is self-contained (kernel, PTX helpers,
-host plumbing and the C-ABI header) and is what :func:`tilecadence_b200.cuda_runtime.build_cuda`
-compiles.
+Public surface and behaviour follow ``tilecadence/operator.py`` (``OFFSETS`` :13-18, ``emit`` :21-38,
+command line :41-46): the phase's handoff is solved, each region's byte offset replaces the value of
+one macro in that phase's ``config.cuh``, every other source file is copied unchanged, and the solver's
+answer is stored as ``placement.json``. An existing output directory is an error. What is written here
+is self-contained (kernel, PTX helpers, host plumbing, C-ABI header): it is exactly what
+:func:`tilecadence_b200.cuda_runtime.build_cuda` compiles.
 """
 from __future__ import annotations
 
 import argparse
 import json
 from pathlib import Path
-import re
-import shutil
 
+from . import placement as _placement
 from .cuda_runtime import staged_sources
-from .placement import HANDOFFS, solve
 
-
+#: region name -> macro that carries its offset, per phase (the reference's names, so that emitted
+#: configurations stay readable side by side).
 OFFSETS = {
-    "prefill": {"head0_lse": "PREFILL_LSE_HEAD0_OFFSET_BYTES",
-                "head1_lse": "PREFILL_LSE_HEAD1_OFFSET_BYTES"},
-    "decode": {"output_tile": "AB_DECODE_O_OFFSET_BYTES",
-               "row_lse": "AB_DECODE_LSE_OFFSET_BYTES"},
+    "prefill": {
+        "head0_lse": "PREFILL_LSE_HEAD0_OFFSET_BYTES",
+        "head1_lse": "PREFILL_LSE_HEAD1_OFFSET_BYTES",
+    },
+    "decode": {
+        "output_tile": "AB_DECODE_O_OFFSET_BYTES",
+        "row_lse": "AB_DECODE_LSE_OFFSET_BYTES",
+    },
 }
+
+CONFIG_NAME = "config.cuh"
+
+
+def _with_macro_values(text: str, values: dict[str, int]) -> str:
+    """``text`` with the integer after ``#define NAME`` replaced for every NAME in ``values``.
+
+    Each name must be defined exactly once, on a line of its own, with an unsigned decimal value.
+    """
+    seen = dict.fromkeys(values, 0)
+    lines = text.split("\n")
+    for index, line in enumerate(lines):
+        words = line.split()
+        if len(words) == 3 and words[0] == "#define" and words[1] in values and words[2].isdigit() \
+                and line == " ".join(words):
+            lines[index] = f"#define {words[1]} {values[words[1]]}"
+            seen[words[1]] += 1
+    for name, count in seen.items():
+        if count != 1:
+            raise ValueError(f"Expected exactly one template definition of {name}")
+    return "\n".join(lines)
 
 
 def emit(phase: str, out: Path) -> dict:
-    if phase not in OFFSETS:
+    """Solve ``phase``'s handoff and write the source directory ``out``; returns the placement."""
+    macros = OFFSETS.get(phase)
+    if macros is None:
         raise ValueError(f"Unknown operator: {phase}")
-    placement = solve(HANDOFFS[phase])
-    template = staged_sources(phase)
-    config = template["config.cuh"].read_text(encoding="utf-8")
-    for region, macro in OFFSETS[phase].items():
-        offset = placement["regions"][region]["offset_bytes"]
-        config, count = re.subn(rf"^#define {macro} \d+$", f"#define {macro} {offset}", config, flags=re.M)
-        if count != 1:
-            raise ValueError(f"Expected exactly one template definition of {macro}")
-    out = Path(out)
-    out.mkdir(parents=True, exist_ok=False)
-    for name, path in template.items():
-        if name != "config.cuh":
-            shutil.copyfile(path, out / name)
-    (out / "config.cuh").write_text(config, encoding="utf-8", newline="\n")
-    (out / "placement.json").write_text(json.dumps(placement, indent=2) + "\n", encoding="utf-8")
-    return placement
+    solved = _placement.solve(_placement.HANDOFFS[phase])
+    sources = staged_sources(phase)
+    values = {macro: int(solved["regions"][region]["offset_bytes"]) for region, macro in macros.items()}
+    config = _with_macro_values(sources[CONFIG_NAME].read_text(encoding="utf-8"), values)
+
+    target = Path(out)
+    target.mkdir(parents=True, exist_ok=False)
+    for name, source in sources.items():
+        destination = target / name
+        if name == CONFIG_NAME:
+            destination.write_text(config, encoding="utf-8", newline="\n")
+        else:
+            destination.write_bytes(source.read_bytes())
+    (target / "placement.json").write_text(json.dumps(solved, indent=2) + "\n", encoding="utf-8")
+    return solved
 
 
-def main():
-    parser = argparse.ArgumentParser(description=__doc__)
-    parser.add_argument("--phase", choices=OFFSETS, required=True)
-    parser.add_argument("--out", type=Path, required=True)
-    args = parser.parse_args()
-    emit(args.phase, args.out)
+def main(argv=None):
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--phase", required=True, choices=sorted(OFFSETS))
+    parser.add_argument("--out", required=True, type=Path)
+    arguments = parser.parse_args(argv)
+    emit(arguments.phase, arguments.out)
 
 
 if __name__ == "__main__":

@@ -1,38 +1,50 @@
-"""Solve shared-memory handoff offsets for the B200 attention kernels.
+"""Where inside a released shared-memory range the epilogue's staging regions go.
 
-Same declarative surface as ``tilecadence/placement.py`` (``Region`` :13-19, ``Handoff`` :22-28,
-``HANDOFFS`` :31-44, ``replay`` :47-62, ``solve`` :65-103, CLI :106-115): a donor byte range that a
-kernel releases at a known step of a short timeline, and recipient regions (size, alignment,
-half-open live interval) that must be packed into it without overlapping in time x address. The
-result dictionary has the reference's schema and the reference's objective: minimum recipient
-address high-water, then minimum offset of the first region.
+The declarative surface is that of ``tilecadence/placement.py`` (``Region`` :13-19, ``Handoff``
+:22-28, ``HANDOFFS`` :31-44, ``replay`` :47-62, ``solve`` :65-103, command line :106-115): a *donor*
+byte range that a kernel stops reading at a known step of a three-step timeline, and *recipient*
+regions (bytes, alignment, half-open live interval in steps) that have to be packed into the donor so
+that no two regions that are alive together share a byte. ``solve`` returns the reference's result
+dictionary (same keys, same ``schema`` string, same objective text) and ``replay`` raises the same
+``ValueError`` messages, so emitted ``placement.json`` files are interchangeable.
 
-What changed for sm_100a is the donor geometry (the kernels' shared-memory maps) and the solver:
-the reference states the problem to OR-tools CP-SAT; here the optimum is found by exact
-enumeration. Any packing can be slid down to a "first-fit" packing without raising either
-objective term, and every first-fit packing is produced by placing the regions in some order at
-the lowest aligned conflict-free address, so trying every order is exhaustive.
+Two things differ. The donors describe the sm_100a kernels' shared-memory maps, not the reference's.
+And the optimum is found by exhaustive search instead of OR-tools CP-SAT: any feasible packing can be
+slid towards the donor's start until every region rests against the donor's start or against a region
+that is alive with it, without raising the high-water mark or the first region's offset; such
+"resting" packings are exactly what placing the regions one after another at the lowest aligned free
+address produces, for some order. Trying every order therefore visits an optimal packing.
 """
 from __future__ import annotations
 
 import argparse
-from dataclasses import asdict, dataclass
-from itertools import permutations
+import itertools
 import json
+from dataclasses import asdict, dataclass
 from pathlib import Path
+
+SCHEMA = "qwen3-residency-placement-v79"
+OBJECTIVE = "Minimum recipient address high-water, then first recipient offset"
 
 
 @dataclass(frozen=True)
 class Region:
+    """A recipient: ``size_bytes`` at a multiple of ``alignment_bytes``, alive during steps [start, end)."""
+
     name: str
     size_bytes: int
     alignment_bytes: int
     start: int
     end: int
 
+    def alive_with(self, other: "Region") -> bool:
+        return self.start < other.end and other.start < self.end
+
 
 @dataclass(frozen=True)
 class Handoff:
+    """A donor range [donor_offset_bytes, +donor_bytes) free from step ``donor_release`` on, and what moves in."""
+
     donor_name: str
     donor_offset_bytes: int
     donor_bytes: int
@@ -40,115 +52,120 @@ class Handoff:
     regions: tuple[Region, ...]
     timeline: tuple[str, ...]
 
+    @property
+    def donor_end(self) -> int:
+        return self.donor_offset_bytes + self.donor_bytes
 
-# Donors on B200:
-#   prefill  K stage 0 of the 2-stage K ring (32 KiB at byte 65536 of the CTA arena, after the two
-#            32 KiB Q tiles); the ring index is chosen so the last QK^T always reads stage 0.
-#   decode   the V half (16 KiB at byte 0) of stage 0 of the K/V ring; the last tile always uses it.
-# Recipients keep the reference's sizes, alignments and live intervals.
+
+_STEPS_K = ("last_K_read", "K_readers_released_and_epilogue_scatter", "CTA_publish_and_export")
+_STEPS_V = ("last_V_read", "V_readers_released_and_epilogue_scatter", "CTA_publish_and_export")
+
+#: The two handoffs of the B200 kernels. Recipient sizes, alignments and live intervals are the
+#: reference's; the donors are this build's:
+#:   prefill -- stage 0 of the two-stage K ring: 32 KiB at byte 65536 of the CTA's arena, behind the two
+#:              32 KiB Q tiles. The ring index is chosen so that the last score MMA always reads stage 0.
+#:   decode  -- the V half of stage 0 of the K/V ring: 16 KiB at byte 0. The last tile always lands there.
 HANDOFFS = {
     "prefill": Handoff(
-        "terminal_K", 64 * 1024, 32 * 1024, 1,
-        (Region("head0_lse", 512, 128, 1, 3),
-         Region("head1_lse", 512, 128, 1, 3)),
-        ("last_K_read", "K_readers_released_and_epilogue_scatter", "CTA_publish_and_export"),
-    ),
+        donor_name="terminal_K", donor_offset_bytes=65536, donor_bytes=32768, donor_release=1,
+        regions=(Region("head0_lse", 512, 128, start=1, end=3), Region("head1_lse", 512, 128, start=1, end=3)),
+        timeline=_STEPS_K),
     "decode": Handoff(
-        "terminal_V", 0, 16 * 1024, 1,
-        (Region("output_tile", 2048, 16, 1, 3),
-         Region("row_lse", 16, 16, 1, 3)),
-        ("last_V_read", "V_readers_released_and_epilogue_scatter", "CTA_publish_and_export"),
-    ),
+        donor_name="terminal_V", donor_offset_bytes=0, donor_bytes=16384, donor_release=1,
+        regions=(Region("output_tile", 2048, 16, start=1, end=3), Region("row_lse", 16, 16, start=1, end=3)),
+        timeline=_STEPS_V),
 }
 
 
+def _bytes_collide(first_offset: int, first: Region, second_offset: int, second: Region) -> bool:
+    return first_offset < second_offset + second.size_bytes and second_offset < first_offset + first.size_bytes
+
+
 def replay(handoff: Handoff, offsets: dict[str, int]) -> None:
-    """Independently check half-open times and byte ranges."""
-    donor_lo = handoff.donor_offset_bytes
-    donor_hi = donor_lo + handoff.donor_bytes
-    steps = len(handoff.timeline)
-    placed = []
+    """Check a placement from first principles; raises ``ValueError`` on the first violated rule."""
+    last_step = len(handoff.timeline)
+    checked: list[Region] = []
     for region in handoff.regions:
-        lo = offsets[region.name]
-        hi = lo + region.size_bytes
-        time_ok = handoff.donor_release <= region.start < region.end <= steps
-        bytes_ok = donor_lo <= lo < hi <= donor_hi and lo % region.alignment_bytes == 0
-        if not (time_ok and bytes_ok):
+        offset = offsets[region.name]
+        in_time = handoff.donor_release <= region.start < region.end <= last_step
+        in_donor = (handoff.donor_offset_bytes <= offset and region.size_bytes > 0
+                    and offset + region.size_bytes <= handoff.donor_end)
+        aligned = offset % region.alignment_bytes == 0
+        if not (in_time and in_donor and aligned):
             raise ValueError(f"Invalid time/address placement for {region.name}")
-        for other, other_lo in placed:
-            live_together = max(region.start, other.start) < min(region.end, other.end)
-            if live_together and max(lo, other_lo) < min(hi, other_lo + other.size_bytes):
-                raise ValueError(f"Live byte ranges overlap for {region.name} and {other.name}")
-        placed.append((region, lo))
+        for earlier in checked:
+            if region.alive_with(earlier) and _bytes_collide(offset, region, offsets[earlier.name], earlier):
+                raise ValueError(f"Live byte ranges overlap for {region.name} and {earlier.name}")
+        checked.append(region)
 
 
-def _align_up(value: int, step: int) -> int:
-    return -(-value // step) * step
+def _lowest_free_offset(handoff: Handoff, region: Region, taken: dict[str, int], by_name: dict[str, Region]) -> int:
+    """Lowest aligned offset in the donor at which ``region`` collides with nothing already placed."""
+    step = region.alignment_bytes
+    offset = (handoff.donor_offset_bytes + step - 1) // step * step
+    while True:
+        blockers = [taken[name] + by_name[name].size_bytes for name in taken
+                    if region.alive_with(by_name[name]) and _bytes_collide(offset, region, taken[name], by_name[name])]
+        if not blockers:
+            return offset
+        offset = (max(blockers) + step - 1) // step * step
 
 
-def _first_fit(handoff: Handoff, order) -> dict[str, int] | None:
-    donor_lo = handoff.donor_offset_bytes
-    donor_hi = donor_lo + handoff.donor_bytes
-    placed: list[tuple[Region, int]] = []
+def _pack_in_order(handoff: Handoff, order, by_name: dict[str, Region]):
+    taken: dict[str, int] = {}
     for region in order:
-        offset = _align_up(donor_lo, region.alignment_bytes)
-        moved = True
-        while moved:
-            moved = False
-            for other, other_lo in placed:
-                if max(region.start, other.start) >= min(region.end, other.end):
-                    continue
-                other_hi = other_lo + other.size_bytes
-                if max(offset, other_lo) < min(offset + region.size_bytes, other_hi):
-                    offset = _align_up(other_hi, region.alignment_bytes)
-                    moved = True
-        if offset + region.size_bytes > donor_hi:
+        offset = _lowest_free_offset(handoff, region, taken, by_name)
+        if offset + region.size_bytes > handoff.donor_end:
             return None
-        placed.append((region, offset))
-    return {region.name: offset for region, offset in placed}
+        taken[region.name] = offset
+    return taken
 
 
 def solve(handoff: Handoff) -> dict:
-    for region in handoff.regions:
+    """Optimal placement: least recipient high-water mark, ties broken by the first region's offset."""
+    regions = handoff.regions
+    for region in regions:
         if region.size_bytes <= 0 or region.alignment_bytes <= 0:
             raise ValueError(f"Invalid size or alignment for {region.name}")
-    first = handoff.regions[0].name
-    best = None
-    for order in permutations(handoff.regions):
-        placement = _first_fit(handoff, order)
-        if placement is None:
-            continue
-        high_water = max(placement[r.name] + r.size_bytes for r in handoff.regions)
-        key = (high_water, placement[first], tuple(placement[r.name] for r in handoff.regions))
-        if best is None or key < best[0]:
-            best = (key, placement)
-    if best is None:
+    by_name = {region.name: region for region in regions}
+
+    def rank(candidate: dict[str, int]):
+        high_water = max(candidate[r.name] + r.size_bytes for r in regions)
+        return high_water, candidate[regions[0].name], [candidate[r.name] for r in regions]
+
+    packings = (_pack_in_order(handoff, order, by_name) for order in itertools.permutations(regions))
+    feasible = [packing for packing in packings if packing is not None]
+    if not feasible:
         raise ValueError("No optimal physical handoff placement")
-    (high_water, _, _), placement = best
-    replay(handoff, placement)
+    chosen = min(feasible, key=rank)
+    replay(handoff, chosen)
+    placed_regions = {}
+    for region in regions:
+        record = asdict(region)
+        record["offset_bytes"] = chosen[region.name]
+        placed_regions[region.name] = record
     return {
-        "schema": "qwen3-residency-placement-v79",
+        "schema": SCHEMA,
         "status": "OPTIMAL",
         "donor": {"name": handoff.donor_name, "offset_bytes": handoff.donor_offset_bytes,
                   "size_bytes": handoff.donor_bytes, "release": handoff.donor_release},
-        "regions": {r.name: {**asdict(r), "offset_bytes": placement[r.name]}
-                    for r in handoff.regions},
+        "regions": placed_regions,
         "timeline": handoff.timeline,
-        "recipient_high_water_bytes": high_water,
-        "objective": "Minimum recipient address high-water, then first recipient offset",
+        "recipient_high_water_bytes": rank(chosen)[0],
+        "objective": OBJECTIVE,
     }
 
 
-def main():
-    parser = argparse.ArgumentParser(description=__doc__)
-    parser.add_argument("--out", type=Path, required=True)
-    parser.add_argument("--phase", choices=HANDOFFS)
-    args = parser.parse_args()
-    args.out.mkdir(parents=True, exist_ok=False)
-    for phase in (args.phase,) if args.phase else HANDOFFS:
-        with (args.out / f"{phase}.json").open("x", encoding="utf-8") as stream:
-            json.dump(solve(HANDOFFS[phase]), stream, indent=2)
-            stream.write("\n")
+def main(argv=None):
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--out", required=True, type=Path, help="directory to create; receives <phase>.json")
+    parser.add_argument("--phase", choices=sorted(HANDOFFS), help="only this handoff (default: all)")
+    arguments = parser.parse_args(argv)
+    arguments.out.mkdir(parents=True, exist_ok=False)
+    for phase in ([arguments.phase] if arguments.phase else list(HANDOFFS)):
+        text = json.dumps(solve(HANDOFFS[phase]), indent=2) + "\n"
+        with (arguments.out / f"{phase}.json").open("x", encoding="utf-8") as stream:
+            stream.write(text)
 
 
 if __name__ == "__main__":
