@@ -45,35 +45,39 @@ _loaded: dict[str, "Library"] = {}
 
 
 def file_sha256(path):
-    with Path(path).open("rb") as stream:
-        digest = sha256()
-        for chunk in iter(lambda: stream.read(1024 * 1024), b""):
-            digest.update(chunk)
-        return digest.hexdigest()
+    """Hex SHA-256 of a file's bytes."""
+    import hashlib
+
+    with open(path, "rb") as stream:
+        return hashlib.file_digest(stream, "sha256").hexdigest()
 
 
 def find_nvcc():
-    home = os.environ.get("CUDA_HOME") or os.environ.get("CUDA_PATH") or "/usr/local/cuda"
-    candidate = Path(home) / "bin" / "nvcc"
-    if candidate.is_file():
-        return candidate
-    found = shutil.which("nvcc")
-    return Path(found) if found else None
+    """Path of nvcc: ``$CUDA_HOME/bin`` (or ``$CUDA_PATH``, or /usr/local/cuda) first, then ``$PATH``."""
+    roots = [os.environ.get(name) for name in ("CUDA_HOME", "CUDA_PATH")] + ["/usr/local/cuda"]
+    for root in roots:
+        if root and (Path(root) / "bin" / "nvcc").is_file():
+            return Path(root) / "bin" / "nvcc"
+    on_path = shutil.which("nvcc")
+    return Path(on_path) if on_path else None
 
 
 def cuda_device(device="cuda:0"):
-    """Validate the selected device: CUDA, visible, and compute capability 10.x."""
+    """``(torch.device with an explicit index, compute capability)`` of a usable sm_100 device; anything
+    else (no CUDA build of torch, no visible GPU, another architecture) is a ``RuntimeError``: there is
+    no other code path to fall back to."""
     import torch
 
-    selected = torch.device(device)
-    if selected.type != "cuda" or not torch.version.cuda or not torch.cuda.is_available():
+    wanted = torch.device(device)
+    usable = wanted.type == "cuda" and bool(torch.version.cuda) and torch.cuda.is_available()
+    if not usable:
         raise RuntimeError("An NVIDIA CUDA device and CUDA-enabled PyTorch are required")
-    index = torch.cuda.current_device() if selected.index is None else selected.index
-    selected = torch.device("cuda", index)
-    capability = torch.cuda.get_device_capability(selected)
-    if capability[0] != 10:
-        raise RuntimeError(f"The kernels are written for sm_100a only; device reports sm_{capability[0]}{capability[1]}")
-    return selected, capability
+    if wanted.index is None:
+        wanted = torch.device("cuda", torch.cuda.current_device())
+    major, minor = torch.cuda.get_device_capability(wanted)
+    if major != 10:
+        raise RuntimeError(f"The kernels are written for sm_100a only; device reports sm_{major}{minor}")
+    return wanted, (major, minor)
 
 
 def staged_sources(phase):

@@ -26,6 +26,9 @@ RESOURCE_KEYS = ("block_m", "block_n", "head_dim", "value_stripe_dim", "threads"
                  "ptx_version", "theoretical_active_ctas_per_sm", "required_nonce_elements", "diagnostic_guard")
 
 
+INDENT = "    "  # generated statements sit one level inside the kernel body
+
+
 def _mapping(value):
     if isinstance(value, (str, Path)):
         return json.loads(Path(value).read_text())
@@ -116,39 +119,39 @@ def source_for(problem, result, *, output_cache="default"):
             mask |= ((1 << ((hi - lo) // SLAB)) - 1) << (lo // SLAB)
         return mask
 
-    def emit(text):
-        lines.append("    " + text)
+    def write(statement):
+        lines.append(INDENT + statement)
 
     for event in events:
         kind = event["kind"]
-        inputs = [copies[x] for x in event["inputs"]]
-        outputs = [copies[x] for x in event["outputs"]]
-        ins = [names[c["id"]] for c in inputs]
-        outs = [names[c["id"]] for c in outputs]
+        consumed = [copies[identity] for identity in event["inputs"]]
+        produced = [copies[identity] for identity in event["outputs"]]
+        ins = [names[copy["id"]] for copy in consumed]
+        outs = [names[copy["id"]] for copy in produced]
         event_lines[event["id"]] = {"comment_line": len(lines) + 1}
-        emit("// EVENT " + event["id"])
+        write("// EVENT " + event["id"])
         entry = {"kind": kind, "workspace_copies": event.get("workspace_copies", []), "read_mask_before": read_mask(),
                  "ready_cutoff_before": ready_cutoff, "last_commit_hmma_before": hmma_gap,
                  "last_commit_ex2_before": ex2_gap, "wait_before_load": False, "acquire_before_load": False}
-        writes = [c for c in outputs if c["tier"] == "smem"] if kind in ("copy_g2s", "store_r2s") else []
+        writes = [c for c in produced if c["tier"] == "smem"] if kind in ("copy_g2s", "store_r2s") else []
         if kind == "normalize_store":
             writes = [copies[x] for x in event["workspace_copies"]]
         hazards = [[c["id"], old] for c in writes for old, (lo, hi) in unreleased if span(c)[0] < hi and lo < span(c)[1]]
         if hazards:
-            emit("release_shared_reads();  // this shared write overlaps slabs with distributed reads outstanding")
+            write("release_shared_reads();  // this shared write overlaps slabs with distributed reads outstanding")
             unreleased.clear()
         entry.update(release_before_write=bool(hazards), shared_read_write_hazards=hazards)
         if kind == "copy_g2s":
-            dst = outputs[0]
+            dst = produced[0]
             role, tile, stripe = dst["role"], dst["tile"], dst["stripe"]
             if issued >= 16:
                 raise ValueError("More copies than the kernel has barriers for")
             if role == "q":
-                emit(f"issue_g2s<Element,64,128,{issued}>(ctx,&qmap,0,0,{smem[dst['id']]});")
+                write(f"issue_g2s<Element,64,128,{issued}>(ctx,&qmap,0,0,{smem[dst['id']]});")
             elif role == "k":
-                emit(f"issue_g2s<Element,32,128,{issued}>(ctx,&kmap,{tile * 32},0,{smem[dst['id']]});")
+                write(f"issue_g2s<Element,32,128,{issued}>(ctx,&kmap,{tile * 32},0,{smem[dst['id']]});")
             elif role == "v" and stripe is not None:
-                emit(f"issue_g2s<Element,32,64,{issued}>(ctx,&vmap,{tile * 32},{stripe * 64},{smem[dst['id']]});")
+                write(f"issue_g2s<Element,32,64,{issued}>(ctx,&vmap,{tile * 32},{stripe * 64},{smem[dst['id']]});")
             else:
                 raise ValueError("Only Q, K and V stripes have global copies")
             entry.update(primitive="tma_tile_copy_arm_mbarrier", barrier_index=issued)
@@ -157,65 +160,65 @@ def source_for(problem, result, *, output_cache="default"):
             if issued - waited > model.MAX_OUTSTANDING_COPIES:
                 raise ValueError("More than eight copies in flight")
         elif kind == "load_s2r":
-            src, dst = inputs[0], outputs[0]
+            src, dst = consumed[0], produced[0]
             role = dst["role"]
             producer = by_event[src["producer"]]
             wait = False
             if role == "p":
                 if producer["kind"] != "store_r2s":
                     raise ValueError("A checkpoint load needs its checkpoint store")
-                emit(f"auto {outs[0]}=load_checkpoint<Element>({smem[src['id']]},ctx);")
+                write(f"auto {outs[0]}=load_checkpoint<Element>({smem[src['id']]},ctx);")
                 entry.update(primitive="load_checkpoint")
             else:
                 if producer["kind"] != "copy_g2s":
                     raise ValueError("An operand load needs its input copy")
                 wait = producer["end"] > ready_cutoff
                 if wait:
-                    emit(f"acquire_copies<{waited},{issued}>(ctx);  // copy newer than the ready cutoff")
+                    write(f"acquire_copies<{waited},{issued}>(ctx);  // copy newer than the ready cutoff")
                     unreleased.clear()
                     waited, ready_cutoff = issued, event["end"]
                 loader = {"q": "load_q_ready", "k": "load_k_ready", "v": "load_v_ready"}[role]
-                emit(f"auto {outs[0]}={loader}<Element>(ctx,{smem[src['id']]});")
+                write(f"auto {outs[0]}={loader}<Element>(ctx,{smem[src['id']]});")
                 entry.update(primitive="ldmatrix_after_acquire" if wait else "ldmatrix_ready")
             if src["id"] not in [identity for identity, _ in unreleased]:
                 unreleased.append((src["id"], span(src)))
             entry.update(wait_before_load=wait, acquire_before_load=wait)
         elif kind == "store_r2s":
-            emit(f"store_checkpoint({ins[0]},{smem[outputs[0]['id']]},ctx);")
+            write(f"store_checkpoint({ins[0]},{smem[produced[0]['id']]},ctx);")
             unreleased.clear()  # store_checkpoint ends with a CTA barrier
             entry.update(primitive="store_checkpoint_with_cta_barrier")
         elif kind == "qk":
-            emit(f"auto {outs[0]}=qk<Element>({ins[0]},{ins[1]});")
+            write(f"auto {outs[0]}=qk<Element>({ins[0]},{ins[1]});")
         elif kind in ("stats_first", "stats_next"):
-            for c, name in zip(outputs, outs):
-                emit(f"Probabilities<Element> {name};" if c["role"] == "p" else f"RowPair {name};")
+            for c, name in zip(produced, outs):
+                write(f"Probabilities<Element> {name};" if c["role"] == "p" else f"RowPair {name};")
             tile = event["tile"]
             if kind == "stats_first":
-                emit(f"stats_first<Causal,{tile},Element>(ctx,{ins[0]},{outs[0]},{outs[1]},{outs[2]});")
+                write(f"stats_first<Causal,{tile},Element>(ctx,{ins[0]},{outs[0]},{outs[1]},{outs[2]});")
             else:
-                emit(f"stats_next<Causal,{tile},Element>(ctx,{ins[0]},{ins[1]},{ins[2]},{outs[0]},{outs[1]},{outs[2]},{outs[3]});")
+                write(f"stats_next<Causal,{tile},Element>(ctx,{ins[0]},{ins[1]},{ins[2]},{outs[0]},{outs[1]},{outs[2]},{outs[3]});")
         elif kind in ("pv_first", "pv_next"):
             stripe = event["stripe"]
             if kind == "pv_first":
                 if stripe in opened:
                     raise ValueError("An output stripe may only be opened once")
-                emit(f"Accumulator o{stripe};")
-                emit(f"clear(o{stripe});  // the stripe's register lifetime begins here")
+                write(f"Accumulator o{stripe};")
+                write(f"clear(o{stripe});  // the stripe's register lifetime begins here")
                 opened.add(stripe)
             elif stripe not in opened:
                 raise ValueError("PV update before the stripe was opened")
-            emit(f"pv<Element>({ins[0]},{ins[1]},o{stripe});")
+            write(f"pv<Element>({ins[0]},{ins[1]},o{stripe});")
         elif kind == "rescale_o":
-            emit(f"rescale(o{event['stripe']},{ins[0]});")
+            write(f"rescale(o{event['stripe']},{ins[0]});")
         elif kind == "normalize_store":
             stripe = event["stripe"]
             scratch = copies[event["workspace_copies"][0]]
-            emit(f"normalize_store_coalesced128<Element,{stripe}>(ctx,o{stripe},{ins[0]},o_base,row_stride,arena+{scratch['offset_bytes']});")
+            write(f"normalize_store_coalesced128<Element,{stripe}>(ctx,o{stripe},{ins[0]},o_base,row_stride,arena+{scratch['offset_bytes']});")
             entry.update(primitive="close_shared128", scratch_offset_bytes=scratch["offset_bytes"], scratch_bytes=8192)
             unreleased.clear()  # the close has a CTA barrier between its shared writes and reads
             unreleased.append((scratch["id"], span(scratch)))
         elif kind == "store_lse":
-            emit(f"store_lse(ctx,{ins[0]},{ins[1]},lse_base);")
+            write(f"store_lse(ctx,{ins[0]},{ins[1]},lse_base);")
         else:
             raise ValueError("Unsupported action")
         event_lines[event["id"]]["last_line"] = len(lines)
