@@ -22,6 +22,8 @@ reference's saved Qwen3 projections). A step is one forward over that batch.
                  it as ``c5_nccl``), as HBM GB/s with their own roofline.
 * ``project``    the step before decode (fused QKV projection + head RMS norm + RoPE, 4 tokens, Qwen3-4B
                  shapes) as HBM GB/s of streamed weights.
+* ``layer_chain`` projection then config-4 decode as a layer runs them, microseconds per layer, with the plain
+                 decode entry and with the cache-stable promise (K/V streamed while the projection finishes).
 * ``prefill_sharded`` (N > 1) config 2 itself split by KV-head group over the ranks (strong scaling).
 * ``cpu_baseline`` the CPU oracle (the reference's only CPU attention, ``bench_exchange.py:54-60``)
                  timed on this host on a bounded sample.
@@ -469,6 +471,61 @@ def run_ours(args, rank, world, local_rank):
         print(f"projection step not measured: {error}", file=sys.stderr)
         project = {"unavailable": str(error)}
 
+    # ------------------------------------------------------------------ projection -> decode, as a layer runs them
+    def layer_chain_case(sets=8, graph_steps=16):
+        """One token's projection followed by the config-4 decode step on that layer's cache, `graph_steps`
+        layers back to back in a captured graph; once with the plain decode entry and once with the
+        cache-stable promise, under which the decode kernel streams K/V while the projection finishes."""
+        nonlocal launches
+        project_ops = cuda_runtime.ops_for(library, "project")
+        hidden, rows = 2560, (HQ + 2 * HKV) * DIM
+        capacity, valid = DECODE_C4["capacity"], DECODE_C4["valid"]
+        generator = torch.Generator(device=device).manual_seed(11 + rank)
+        weights = [(torch.randn((rows, hidden), generator=generator, device=device) / hidden ** 0.5).to(torch.bfloat16)
+                   for _ in range(sets)]
+        caches = [tuple(torch.randn((1, capacity, HKV, DIM), generator=generator, device=device, dtype=torch.bfloat16)
+                        for _ in range(2)) for _ in range(sets)]
+        x = torch.randn((1, hidden), generator=generator, device=device).to(torch.bfloat16)
+        angles = torch.rand((capacity, DIM // 2), generator=generator, device=device)
+        cos, sin = angles.cos(), angles.sin()
+        old = torch.full((1,), valid, dtype=torch.int32, device=device)
+        q, knew, vnew = (torch.empty((1, 1, heads, DIM), device=device, dtype=torch.bfloat16) for heads in (HQ, HKV, HKV))
+        out, lse = torch.empty_like(q), torch.empty((1, HQ, 1), device=device, dtype=torch.float32)
+        spec = decode_ops.workspace_spec(q, caches[0][0], old, 0, 1, True)
+        workspace = [torch.empty(n, device=device, dtype=torch.float32) for n in spec[1:3]]
+        result = {"workload": "per layer: fused QKV projection (1 token, hidden 2560) then config4 decode step on that "
+                              f"layer's cache; {sets} rotating weight and cache sets (larger than L2), {graph_steps} "
+                              "layers per captured graph"}
+        for key, promise in (("us_per_layer", False), ("us_per_layer_cache_stable", True)):
+            steps = [decode_ops.bind_forward_out(q, kc, vc, knew, vnew, old, out, lse, *workspace, 0, 1, True,
+                                                 cache_stable=promise) for kc, vc in caches]
+
+            def chain():
+                for layer in range(graph_steps):
+                    project_ops.forward_out(x, weights[layer % sets], old, q, knew, vnew, rope_cos=cos, rope_sin=sin)
+                    steps[layer % sets]()
+
+            chain()
+            torch.cuda.synchronize(device)
+            stream = torch.cuda.Stream(device)
+            with torch.cuda.stream(stream):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    chain()
+            replays = 10
+            result[key] = timed(graph.replay, replays, 3) / (replays * graph_steps) * 1e3
+            launches += replays * graph_steps * 2
+        moved = rows * hidden * 2 + decode_bytes(1, valid + 1)
+        result["bytes_per_layer"] = moved
+        result["hbm_gbs_cache_stable"] = moved / (result["us_per_layer_cache_stable"] * 1e-6) / 1e9
+        return result
+
+    try:
+        layer_chain = layer_chain_case()
+    except RuntimeError as error:
+        print(f"projection -> decode chain not measured: {error}", file=sys.stderr)
+        layer_chain = {"unavailable": str(error)}
+
     status = library.device_status(device.index)
     if status != 0:
         raise RuntimeError(f"a kernel reported an expired wait (status {status}); results are invalid")
@@ -493,6 +550,7 @@ def run_ours(args, rank, world, local_rank):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                     "ms_per_step": e2e_ms / args.steps},
             "clocks": clocks, "gpu_launches": launches, "decode": decode, "project": project,
+            "layer_chain": layer_chain,
         }
         if prefill_sharded:
             line["prefill_sharded"] = prefill_sharded

@@ -103,6 +103,20 @@ int tc_decode_forward_out(int device, void* stream, const void* q, void* kcache,
                           int64_t workspace_lse_elems, int64_t batch, int64_t capacity, int64_t kv_heads,
                           int64_t num_splits, int64_t mapping, int append);
 
+/* tc_decode_forward_out with option flags. TC_DECODE_CACHE_STABLE is the caller's promise that the kernel
+ * launched immediately before this call on the same stream writes none of: the cache rows below
+ * old_lengths[b], old_lengths itself (and, where used, index tables). The launch uses programmatic dependent
+ * launch; with the flag the K/V stream and the length read start while that preceding kernel is still
+ * finishing, and only q, knew, vnew and all writes wait for it. Typical case: the preceding kernel is the
+ * projection that produces q / knew / vnew. Without the promise (a kernel that appended to the same cache one
+ * launch earlier) results are undefined; flags = 0 is tc_decode_forward_out. No counterpart in the reference. */
+#define TC_DECODE_CACHE_STABLE 1
+int tc_decode_forward_out_flags(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                                const void* vnew, const int32_t* old_lengths, void* out, float* lse,
+                                float* workspace_o, int64_t workspace_o_elems, float* workspace_lse,
+                                int64_t workspace_lse_elems, int64_t batch, int64_t capacity, int64_t kv_heads,
+                                int64_t num_splits, int64_t mapping, int append, int64_t flags);
+
 /* Allocation-free decode step. It has no counterpart in the reference; it exists for callers that
  * are not allowed to allocate device memory at all: code running inside a fixed memory budget that
  * was carved up at start-up (an inference server whose allocator owns every byte), code that must not

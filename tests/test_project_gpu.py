@@ -93,6 +93,46 @@ def test_feeds_the_decode_operator(project, library, gpu_device):
         assert torch.equal(dk[b, old[b]].cpu().view(torch.int16), knew[b, 0].view(torch.int16))
 
 
+def test_decode_may_stream_the_cache_while_the_projection_finishes(project, library, gpu_device):
+    """Projection -> decode chains on one stream, twenty layers' worth of them back to back with a
+    different token slab each time: the decode step launched with the cache-stable promise (its K/V stream
+    starts while the projection is still running) gives bit for bit the results, and the appended rows, of
+    the plain step."""
+    tokens, capacity, layers = 1, 8192, 20
+    device = gpu_device
+    decode = cuda_runtime.ops_for(library, "decode")
+    cos, sin = (t.to(device) for t in oracle.rope_tables(capacity))
+    old = torch.tensor([capacity - 2], dtype=torch.int32, device=device)
+    slabs, weights = [], []
+    for layer in range(layers):
+        x, w, _, _ = make_inputs(200 + layer, tokens, 2560)
+        slabs.append(x.to(device))
+        weights.append(w.to(device))
+    prefix_k, prefix_v = oracle.seeded_normal(77, (tokens, capacity, 8, 128), (tokens, capacity, 8, 128))
+    results = {}
+    for promise in (False, True):
+        caches = [(prefix_k.to(device), prefix_v.to(device)) for _ in range(layers)]
+        q, knew, vnew = (torch.empty((tokens, 1, h, 128), device=device, dtype=torch.bfloat16) for h in (32, 8, 8))
+        outs = torch.full((layers, tokens, 1, 32, 128), float("nan"), device=device, dtype=torch.bfloat16)
+        lses = torch.full((layers, tokens, 32, 1), float("nan"), device=device)
+        spec = decode.workspace_spec(q, caches[0][0], old, 0, 1, True)
+        ws = [torch.empty(n, device=device, dtype=torch.float32) for n in spec[1:3]]
+        torch.cuda.synchronize()
+        for layer in range(layers):
+            project.forward_out(slabs[layer], weights[layer], old, q, knew, vnew, rope_cos=cos, rope_sin=sin)
+            decode.forward_out(q, *caches[layer], knew, vnew, old, outs[layer], lses[layer], *ws, 0, 1, True,
+                               cache_stable=promise)
+        torch.cuda.synchronize()
+        assert library.device_status(device.index) == 0
+        results[promise] = (outs.cpu(), lses.cpu(), [k[:, capacity - 2].cpu() for k, _ in caches])
+    plain, early = results[False], results[True]
+    assert not torch.isnan(plain[0].float()).any()
+    assert torch.equal(plain[0].view(torch.int16), early[0].view(torch.int16))
+    assert torch.equal(plain[1].view(torch.int32), early[1].view(torch.int32))
+    for a, b in zip(plain[2], early[2]):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
 def test_argument_checks(project, gpu_device):
     x, w, _, _ = make_inputs(1, 2, 128)
     outs = [torch.empty((2, 1, h, 128), device=gpu_device, dtype=torch.bfloat16) for h in (32, 8, 8)]

@@ -107,6 +107,10 @@ struct DecodeParams {
     const float* rope_cos;
     const float* rope_sin;
     int rope_positions;
+    // Caller's promise that the kernel launched just before this one on the stream writes neither the
+    // caches' visible rows, nor old_lengths, nor the index tables: the K/V stream then starts before
+    // the stream dependency resolves.
+    int cache_stable;
 };
 
 // Rotate-half RoPE of one (x[i], x[i + 64]) pair, i < 64, with every product and sum rounded to fp32
@@ -215,8 +219,12 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     // kernel parameters, so it may overlap the tail of the preceding kernel in the stream. Nothing
     // below (lengths, caches, tickets) is read before that kernel has completed. The next kernel
     // may start its own preamble as soon as every CTA of this grid is resident.
-    tc::grid_dependency_wait();
-    tc::grid_launch_dependents();
+    // With cache_stable the lengths, the index tables and the K/V rows may be read at once; q, the new
+    // rows and every write still wait (further down, consumer warps only).
+    if (!p.cache_stable) {
+        tc::grid_dependency_wait();
+        tc::grid_launch_dependents();
+    }
 
     // Device-side lengths: no host read. Values outside the contract are clamped so that no
     // address leaves the cache.
@@ -241,6 +249,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     const int n_tiles = tile_end - tile_begin;
 
     __syncthreads();
+    if (p.cache_stable && warp != kConsumerWarps) {
+        tc::grid_dependency_wait();
+        tc::grid_launch_dependents();  // after the wait: the next launch can overlap this one only
+    }
 
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------------ producer warp
@@ -281,6 +293,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
                 }
             }
         }
+        if (p.cache_stable) tc::grid_launch_dependents();
         return;
     }
 
@@ -796,7 +809,7 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
                   float* workspace_o, int64_t workspace_o_elems, float* workspace_lse, int64_t workspace_lse_elems,
                   int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping, int append,
                   int partial, int64_t shard_start, const PeerArgs* peer = nullptr,
-                  const IndexedCache* indexed = nullptr, const RopeTables* rope = nullptr) {
+                  const IndexedCache* indexed = nullptr, const RopeTables* rope = nullptr, int cache_stable = 0) {
     tc::DeviceInfo info;
     int splits = 1;
     int status = check_geometry(device, batch, capacity, kv_heads, num_splits, mapping, append, &info, &splits);
@@ -882,6 +895,7 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
     p.partial_o = partial_o;
     p.page_size = int(slot_rows);
     p.cache_slots = int(cache_slots);
+    p.cache_stable = cache_stable ? 1 : 0;
     if (rope) {
         TC_REQUIRE(rope->cos && rope->sin && rope->positions >= 1 && rope->positions <= (int64_t(1) << 30),
                    "RoPE needs cos/sin tables FP32[positions,64] with positions >= 1");
@@ -1135,6 +1149,17 @@ int tc_decode_rope_forward_out(int device, void* stream, const void* q, void* kc
     return decode_common(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, nullptr, workspace_o,
                          workspace_o_elems, workspace_lse, workspace_lse_elems, batch, capacity, kv_heads, num_splits,
                          mapping, append, 0, 0, nullptr, nullptr, &rope);
+}
+
+int tc_decode_forward_out_flags(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
+                                const void* vnew, const int32_t* old_lengths, void* out, float* lse,
+                                float* workspace_o, int64_t workspace_o_elems, float* workspace_lse,
+                                int64_t workspace_lse_elems, int64_t batch, int64_t capacity, int64_t kv_heads,
+                                int64_t num_splits, int64_t mapping, int append, int64_t flags) {
+    TC_REQUIRE((flags & ~int64_t(TC_DECODE_CACHE_STABLE)) == 0, "unknown decode flag");
+    return decode_common(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, nullptr, workspace_o,
+                         workspace_o_elems, workspace_lse, workspace_lse_elems, batch, capacity, kv_heads, num_splits,
+                         mapping, append, 0, 0, nullptr, nullptr, nullptr, (flags & TC_DECODE_CACHE_STABLE) != 0);
 }
 
 int tc_peer_block_bytes(int64_t batch, int64_t kv_heads, int64_t world, int64_t* bytes) {

@@ -178,6 +178,9 @@ class Library:
         "tc_decode_forward_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int)),
+        "tc_decode_forward_out_flags": (ctypes.c_int, (
+            ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
+            ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, ctypes.c_int64)),
         "tc_decode_forward_out_static": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, *[ctypes.c_int64] * 5, ctypes.c_int)),
         "tc_decode_partial_out": (ctypes.c_int, (
@@ -361,6 +364,10 @@ class PrefillOps:
         return list(values[:count.value])
 
 
+#: ``flags`` bit of ``tc_decode_forward_out_flags``; same value as TC_DECODE_CACHE_STABLE in the header.
+DECODE_CACHE_STABLE = 1
+
+
 class DecodeOps:
     """``forward_out`` / ``workspace_spec`` / ``resources`` with the reference's decode schemas
     (``tilecadence/cuda/decode/binding.cpp:17-24``), plus the sharded ``partial_out`` and
@@ -423,17 +430,24 @@ class DecodeOps:
                  and tuple(lse.shape) == (q.size(0), q.size(2), 1) and not lse.requires_grad, "Invalid full float32 LSE")
 
     def forward_out(self, q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse,
-                    num_splits, mapping, append):
+                    num_splits, mapping, append, *, cache_stable=False):
+        """One decode step. ``cache_stable=True`` is the caller's promise that the kernel enqueued just
+        before this call writes neither the caches' visible rows nor ``old_lengths``; the K/V stream then
+        starts while that kernel is still finishing (``TC_DECODE_CACHE_STABLE``)."""
         self._check_call(q, kcache, vcache, knew, vnew, old_lengths, workspace_o, workspace_lse)
         self._check_out(q, out, lse)
-        self.library.call(
-            "tc_decode_forward_out", q.device.index, _stream(q), _pointer(q), _pointer(kcache), _pointer(vcache),
+        arguments = (
+            q.device.index, _stream(q), _pointer(q), _pointer(kcache), _pointer(vcache),
             _pointer(knew), _pointer(vnew), _pointer(old_lengths), _pointer(out), _pointer(lse),
             _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse), workspace_lse.numel(),
             q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping), int(bool(append)))
+        if cache_stable:
+            self.library.call("tc_decode_forward_out_flags", *arguments, DECODE_CACHE_STABLE)
+        else:
+            self.library.call("tc_decode_forward_out", *arguments)
 
     def bind_forward_out(self, q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse,
-                         num_splits, mapping, append):
+                         num_splits, mapping, append, *, cache_stable=False):
         """Validate once and return a zero-argument callable that repeats this exact call.
 
         A decode step on a short cache takes a few microseconds on the GPU, less than the tensor
@@ -453,7 +467,10 @@ class DecodeOps:
                 _pointer(out), _pointer(lse), _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse),
                 workspace_lse.numel(), q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping),
                 int(bool(append)))
-        function = self.library.handle.tc_decode_forward_out
+        if cache_stable:
+            function, tail = self.library.handle.tc_decode_forward_out_flags, tail + (DECODE_CACHE_STABLE,)
+        else:
+            function = self.library.handle.tc_decode_forward_out
         library, device = self.library, q.device
         current_stream = torch.cuda.current_stream
 
