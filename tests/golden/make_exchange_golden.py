@@ -58,7 +58,9 @@ def frontier_case():
 
 
 def main():
-    ref_model, ref_exchange = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit(f"usage: python {sys.argv[0]} /path/to/TileCadence")
+    ref_model, ref_exchange = load_reference(sys.argv[1])
     golden = {"arms": {}}
     for arm in exchange.ARMS:
         problem = exchange.build_problem(arm)

@@ -82,7 +82,9 @@ def normal(generator, shape, dtype):
 
 
 def main():
-    reference = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit(f"usage: python {sys.argv[0]} /path/to/TileCadence")
+    reference = load_reference(sys.argv[1])
     arrays = {}
 
     # Two-tile exchange config: batch 1, 8 heads, 64 tokens, fp16, non-causal, seed 0.
