@@ -306,13 +306,17 @@ def run_ours(args, rank, world, local_rank):
         sv = shared[2][:, :, kv_slice].contiguous().to(device)
         shard_ops = cuda_runtime.ops_for(library, "prefill", q_heads=HQ // world)
         sout, slse = torch.empty_like(sq), torch.empty((batch, HQ // world, tokens), device=device)
-        shard_ms = timed(lambda: shard_ops.forward_out(sq, sk, sv, sout, slse, empty, empty, 0, 1, SCALE, True),
+        # A shard of few heads cannot fill the GPU with one CTA per query tile: the key-split entry then
+        # gives every tile to two CTAs (its own choice; one CTA per tile is the plain kernel).
+        split_ws = torch.empty(shard_ops.key_split_workspace_bytes(sq), device=device, dtype=torch.uint8)
+        key_splits = shard_ops.key_split_forward_out(sq, sk, sv, sout, slse, split_ws, 1, SCALE, 0)
+        shard_ms = timed(lambda: shard_ops.key_split_forward_out(sq, sk, sv, sout, slse, split_ws, 1, SCALE, 0),
                          args.steps, args.warmup)
         launches += args.steps
         prefill_sharded = {"workload": "config2 split by KV-head group over the ranks (strong scaling, no collective)",
                            "value": step_flops / (shard_ms / args.steps * 1e-3) / 1e12, "unit": UNIT,
-                           "ms_per_step": shard_ms / args.steps}
-        del sq, sk, sv, sout, slse, shared
+                           "ms_per_step": shard_ms / args.steps, "ctas_per_query_tile": key_splits}
+        del sq, sk, sv, sout, slse, shared, split_ws
     del q, k, v, out, lse
     torch.cuda.empty_cache()
 

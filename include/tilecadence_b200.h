@@ -68,6 +68,24 @@ int tc_prefill_forward_out(int device, void* stream, const void* q, const int64_
                            int64_t tokens, int64_t q_heads, int64_t num_splits, int64_t mapping, double scale,
                            int causal);
 
+/* Prefill for launches that cannot fill the GPU with one CTA per query tile (a KV-head-group shard of a
+ * sequence, few heads): every 128-row query tile is given to two CTAs that each take half of its key tiles,
+ * and the CTA that finishes a head second merges the other's normalised O and LSE into its own (the
+ * LSE-weighted merge of the decode split) before it stores. Same tensors and checks as tc_prefill_forward_out
+ * (causal, num_splits 0). `workspace` is caller-owned, 256-byte aligned, of at least
+ * tc_prefill_key_split_workspace_bytes(batch, tokens, q_heads) bytes and disjoint from the tensors; its ticket
+ * words are cleared on the stream by this call. key_splits: 1 = one CTA per tile (the workspace is unused and
+ * the result is bit-identical to tc_prefill_forward_out), 2 = two, 0 = chosen from the tile and SM counts;
+ * *key_splits_used (may be NULL) receives the choice. With two CTAs the accumulation order differs, so results
+ * agree with the single-CTA result to rounding, not bit for bit. No counterpart in the reference, whose
+ * prefill requires a single split (prefill.cu:109). */
+int tc_prefill_key_split_workspace_bytes(int64_t batch, int64_t tokens, int64_t q_heads, int64_t* bytes);
+int tc_prefill_key_split_forward_out(int device, void* stream, const void* q, const int64_t q_strides[3], const void* k,
+                                     const int64_t k_strides[3], const void* v, const int64_t v_strides[3], void* out,
+                                     float* lse, void* workspace, int64_t workspace_bytes, int64_t batch,
+                                     int64_t tokens, int64_t q_heads, int64_t mapping, double scale, int64_t key_splits,
+                                     int64_t* key_splits_used);
+
 /* Replaces `resources(q,k,v,num_splits,mapping,causal) -> int[]` (prefill.cu:154-167): 12 header
  * values, 8 kernel attributes (threads, dynamic smem, static smem, registers/thread, local
  * bytes/thread, binary version, PTX version, active CTAs/SM), 8 zeros, 18 layout values. */

@@ -86,6 +86,65 @@ def test_head_group_shard(library, gpu_device):
     oracle.check_outputs(got_o, got_lse, want_o[:, :, 8:16], want_lse[:, 8:16])
 
 
+def run_key_split(ops, device, q, k, v, key_splits, mapping=1, scale=128 ** -0.5, repeats=1):
+    dq, dk, dv = q.to(device), k.to(device), v.to(device)
+    out = torch.full(dq.shape, float("nan"), device=device, dtype=torch.bfloat16)
+    lse = torch.full((q.size(0), q.size(2), q.size(1)), float("nan"), device=device, dtype=torch.float32)
+    # The workspace starts as garbage: the call itself has to clear what it relies on.
+    workspace = torch.full((ops.key_split_workspace_bytes(dq),), 0xA5, device=device, dtype=torch.uint8)
+    for _ in range(repeats):
+        used = ops.key_split_forward_out(dq, dk, dv, out, lse, workspace, mapping, scale, key_splits)
+    torch.cuda.synchronize()
+    assert ops.library.device_status(device.index) == 0
+    return out.cpu(), lse.cpu(), used
+
+
+@pytest.mark.parametrize("heads,batch,tokens", [(4, 1, 128), (4, 1, 256), (8, 1, 193), (4, 4, 384), (4, 1, 1537),
+                                                (32, 1, 1024)])
+def test_two_ctas_per_query_tile_match_the_oracle(library, gpu_device, heads, batch, tokens):
+    """Key-split prefill: one, two, three (uneven halves), ragged and many key tiles per query tile."""
+    shard_ops = cuda_runtime.ops_for(library, "prefill", q_heads=heads)
+    q, k, v = oracle.seeded_normal(4000 + tokens, (batch, tokens, heads, 128), (batch, tokens, heads // 4, 128),
+                                   (batch, tokens, heads // 4, 128))
+    want_o, want_lse = oracle.attention(q, k, v, causal=True)
+    got_o, got_lse, used = run_key_split(shard_ops, gpu_device, q, k, v, key_splits=2, repeats=2)
+    assert used == 2
+    oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+
+
+def test_key_split_of_one_is_the_plain_kernel_and_mappings_agree(library, gpu_device):
+    shard_ops = cuda_runtime.ops_for(library, "prefill", q_heads=8)
+    q, k, v = oracle.seeded_normal(11, (1, 896, 8, 128), (1, 896, 2, 128), (1, 896, 2, 128))
+    plain_o, plain_lse = run_prefill(shard_ops, gpu_device, q, k, v)
+    one_o, one_lse, used = run_key_split(shard_ops, gpu_device, q, k, v, key_splits=1)
+    assert used == 1
+    assert torch.equal(bits(plain_o), bits(one_o)) and torch.equal(bits(plain_lse, torch.int32), bits(one_lse, torch.int32))
+    two_o, two_lse, _ = run_key_split(shard_ops, gpu_device, q, k, v, key_splits=2)
+    oracle.check_outputs(two_o, two_lse, plain_o.float(), plain_lse)
+    # Which CTA of a pair finishes second is a race, and the merge is not symmetric in rounding, so two
+    # runs are compared to tolerance; the two staging mappings of one run order agree to tolerance too.
+    other_o, other_lse, _ = run_key_split(shard_ops, gpu_device, q, k, v, key_splits=2, mapping=0)
+    oracle.check_outputs(other_o, other_lse, two_o.float(), two_lse)
+
+
+def test_key_split_is_chosen_for_a_head_group_shard_of_config2(library, gpu_device):
+    """One KV head's shard of config 2 (what each of 8 GPUs holds): 128 query-tile CTAs cannot fill 148 SMs,
+    so the automatic choice is two CTAs per tile; the full 32-head problem keeps one."""
+    tokens = 8192
+    q, k, v = oracle.seeded_normal(1, (1, tokens, 32, 128), (1, tokens, 8, 128), (1, tokens, 8, 128))
+    shard_ops = cuda_runtime.ops_for(library, "prefill", q_heads=4)
+    sq, sk, sv = q[:, :, 4:8].contiguous(), k[:, :, 1:2].contiguous(), v[:, :, 1:2].contiguous()
+    got_o, got_lse, used = run_key_split(shard_ops, gpu_device, sq, sk, sv, key_splits=0)
+    assert used == 2
+    want_o, want_lse = oracle.attention(sq, sk, sv, causal=True, row_block=512)
+    oracle.check_outputs(got_o, got_lse, want_o, want_lse)
+    full_ops = cuda_runtime.ops_for(library, "prefill")
+    dq, dk, dv = (t.to(gpu_device) for t in (q, k, v))
+    out, lse = torch.empty_like(dq), torch.empty((1, 32, tokens), device=gpu_device)
+    workspace = torch.empty(full_ops.key_split_workspace_bytes(dq), device=gpu_device, dtype=torch.uint8)
+    assert full_ops.key_split_forward_out(dq, dk, dv, out, lse, workspace, 1, 128 ** -0.5, 0) == 1
+
+
 def test_config2_full_size(ops, gpu_device):
     """BASELINE config 2: batch 1, 8192 tokens, 32 query / 8 KV heads, seed 1."""
     q, k, v = oracle.seeded_normal(1, (1, 8192, 32, 128), (1, 8192, 8, 128), (1, 8192, 8, 128))

@@ -83,6 +83,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     }
 }
 
+// One-word hand-off between two CTAs of a launch: the writer publishes with a release store after its
+// data, the reader polls with acquire loads. The reader must only be used when the writer is known to
+// be running already (it cannot be waiting for an SM); the wait is bounded like mbar_wait.
+__device__ __forceinline__ void store_release_gpu(int32_t* address, int32_t value) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(address), "r"(value) : "memory");
+}
+__device__ __forceinline__ bool wait_word_gpu(const int32_t* address, int32_t expected) {
+    const uint64_t start = global_timer_ns();
+    for (uint32_t poll = 1;; ++poll) {
+        int32_t seen;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(address) : "memory");
+        if (seen == expected) return true;
+        if ((poll & 15u) == 0 && global_timer_ns() - start > TC_WAIT_LIMIT_NS) return false;
+    }
+}
+
 // Programmatic dependent launch (no-ops when the kernel was launched without the attribute).
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

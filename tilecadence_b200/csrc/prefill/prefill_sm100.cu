@@ -72,6 +72,7 @@ struct Barriers {
     uint64_t s_full[2], s_free[2], p_half[2][2], p_lo_free[2], o_done[2];
     uint32_t tmem_base;
     int32_t abort;
+    int32_t role[2];  // key-split only: which of the two CTAs of a query tile claimed each head first
 };
 static_assert(sizeof(Barriers) <= kBarrierBytes, "barrier block");
 
@@ -80,6 +81,11 @@ struct PrefillParams {
     int32_t* status;
     int batch, tokens, q_heads, kv_heads, m_blocks;
     float scale, scale_log2;
+    // Key-split launches only: per (query tile, head) a claim counter and a ready word (zeroed before the
+    // launch), 128 x 128 normalised fp32 O values stored as [32 column groups][128 rows] float4, 128 LSEs.
+    int32_t* tickets;
+    float4* part_o;
+    float* part_lse;
 };
 
 __device__ __forceinline__ void wg_barrier(int head) {
@@ -92,7 +98,11 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
-template <bool kHandoff>
+// kSplit: two CTAs per query tile, the first takes the key tiles nearest the diagonal (rounded up), the
+// second the rest; whichever finishes a head second merges the other's normalised O and LSE into its own
+// (LSE-weighted) and stores. For launches whose query tiles are too few to fill the GPU, where the longest
+// tile alone would set the run time.
+template <bool kHandoff, bool kSplit = false>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap,
@@ -104,15 +114,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // Longest query tiles first; neighbouring CTAs share a KV head so K/V tiles hit in L2.
-    const int per_block = p.batch * p.kv_heads * 2;
+    const int per_block = p.batch * p.kv_heads * 2 * (kSplit ? 2 : 1);
     const int m_block = p.m_blocks - 1 - int(blockIdx.x) / per_block;
-    const int rest = int(blockIdx.x) % per_block;
+    int rest = int(blockIdx.x) % per_block;
+    const int part = kSplit ? (rest & 1) : 0;
+    if (kSplit) rest >>= 1;
     const int pair = rest & 1;
     const int kvh = (rest >> 1) % p.kv_heads;
     const int b = rest / (2 * p.kv_heads);
     const int head0 = kvh * kGroup + pair * 2;
     const int m0 = m_block * kBlockM;
-    const int n_tiles = m_block + 1;  // key tiles m_block, m_block-1, ..., 0
+    // Key tiles m_block, m_block-1, ..., 0; this CTA's share is n_tiles of them starting at key_block0.
+    const int all_tiles = m_block + 1;
+    const int near_tiles = kSplit ? (all_tiles + 1) / 2 : all_tiles;
+    const int n_tiles = part == 0 ? near_tiles : all_tiles - near_tiles;
+    const int key_block0 = part == 0 ? m_block : m_block - near_tiles;
+    if (kSplit && n_tiles == 0) return;  // a one-tile row block has nothing to split
 
     // The TMA producer owns the operand barriers: it initialises them itself and sends for Q and for
     // the first ring stages at once, so the first loads are in flight while the other warps set up
@@ -120,7 +137,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     const uint64_t keep = tc::policy_evict_last(), stream_once = tc::policy_evict_first();
     auto load_kv = [&](int it) {
         const int stage = (n_tiles - 1 - it) % kStages;
-        const int n0 = (m_block - it) * kBlockN;
+        const int n0 = (key_block0 - it) * kBlockN;
         uint8_t* kdst = smem + kKOffset + stage * kTileBytes;
         tc::mbar_arrive_expect_tx(&bars->k_full[stage], kTileBytes);
         tc::tma_load_4d(kdst, &kmap, &bars->k_full[stage], 0, kvh, n0, b, keep);
@@ -128,7 +145,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         return stage;
     };
     auto load_v = [&](int it, int stage) {
-        const int n0 = (m_block - it) * kBlockN;
+        const int n0 = (key_block0 - it) * kBlockN;
         uint8_t* vdst = smem + kVOffset + stage * kTileBytes;
         tc::mbar_arrive_expect_tx(&bars->v_full[stage], kTileBytes);
         tc::tma_load_4d(vdst, &vmap, &bars->v_full[stage], 0, kvh, n0, b, keep);
@@ -293,7 +310,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             tc::tmem_wait_ld();
             tc::tc_fence_before_sync();
             tc::mbar_arrive(&bars->s_free[h]);  // the score buffer may be overwritten by the other head
-            if (it == 0) {
+            if (it == 0 && part == 0) {
                 // Diagonal tile: key column j is visible to query row i only if j <= i.
 #pragma unroll
                 for (int j = 0; j < 128; ++j) s[j] = j > row ? -INFINITY : s[j];
@@ -316,7 +333,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             float alpha = 1.f;
             bool rescale = false;
             if (it == 0) {
-                m_used = tile_max;  // finite: column `row` of the diagonal tile is always visible
+                m_used = tile_max;  // finite: column `row` of the diagonal tile is always visible, other tiles fully
             } else {
                 const float m_new = fmaxf(m_used, tile_max);
                 const bool grow = (m_new - m_used) * p.scale_log2 > kRescaleThreshold;
@@ -412,6 +429,57 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         }
         tc::tc_fence_after_sync();
         const float inv = l > 0.f ? 1.f / l : 0.f;
+        float row_lse = l > 0.f ? fmaf(m_used, p.scale, logf(l)) : INFINITY;
+        float own_weight = inv;        // what this CTA's accumulator is multiplied by in the stored O
+        float other_weight = 0.f;      // key-split, second finisher: weight of the other CTA's normalised O
+        const float4* other_o = nullptr;
+        bool stores = true;
+        if constexpr (kSplit) {
+            if (all_tiles >= 2) {
+                const int unit = ((((m_block * p.batch + b) * p.kv_heads + kvh) * 2 + pair) * 2) + h;
+                int32_t* claim = p.tickets + 2 * unit;
+                int32_t* ready = claim + 1;
+                float4* slot_o = p.part_o + size_t(unit) * (kBlockM * kDim / 4);
+                float* slot_lse = p.part_lse + size_t(unit) * kBlockM;
+                if (row == 0) bars->role[h] = atomicAdd(claim, 1);
+                wg_barrier(h);
+                if (bars->role[h] == 0) {
+                    // First to finish this head: publish normalised O (coalesced: a warp's rows are
+                    // consecutive float4s of one column group) and LSE, then raise the ready word.
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t acc[32];
+                        tc::tmem_ld32(o_tmem + c * 32, acc);
+                        tc::tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            slot_o[(c * 8 + i) * kBlockM + row] =
+                                make_float4(__uint_as_float(acc[i * 4 + 0]) * inv, __uint_as_float(acc[i * 4 + 1]) * inv,
+                                            __uint_as_float(acc[i * 4 + 2]) * inv, __uint_as_float(acc[i * 4 + 3]) * inv);
+                    }
+                    slot_lse[row] = row_lse;
+                    __threadfence();
+                    wg_barrier(h);
+                    if (row == 0) tc::store_release_gpu(ready, 1);
+                    stores = false;
+                } else {
+                    // Second: the first is past its key loop (it claimed), so this wait is short.
+                    if (row == 0 && !tc::wait_word_gpu(ready, 1)) {
+                        atomicCAS(p.status, 0, 16 + h);
+                        bars->abort = 1;
+                    }
+                    wg_barrier(h);
+                    const float other_lse = __ldcg(slot_lse + row);
+                    const float top = fmaxf(row_lse, other_lse);
+                    const float merged = top + logf(expf(row_lse - top) + expf(other_lse - top));
+                    own_weight = inv * expf(row_lse - merged);
+                    other_weight = expf(other_lse - merged);
+                    row_lse = merged;
+                    other_o = slot_o;
+                }
+            }
+        }
+        if (stores) {
         // O (bf16) is staged over this head's own Q tile in the TMA store layout; LSE goes to the
         // planner's region in the released terminal K stage (or to the dedicated area).
         uint8_t* o_stage = smem + kQOffset + h * kTileBytes;
@@ -423,19 +491,33 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             uint32_t acc[32];
             tc::tmem_ld32(o_tmem + c * 32, acc);
             tc::tmem_wait_ld();
+            float value[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) value[j] = __uint_as_float(acc[j]) * own_weight;
+            if constexpr (kSplit) {
+                if (other_o != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 other = __ldcg(other_o + (c * 8 + i) * kBlockM + row);
+                        value[i * 4 + 0] = fmaf(other.x, other_weight, value[i * 4 + 0]);
+                        value[i * 4 + 1] = fmaf(other.y, other_weight, value[i * 4 + 1]);
+                        value[i * 4 + 2] = fmaf(other.z, other_weight, value[i * 4 + 2]);
+                        value[i * 4 + 3] = fmaf(other.w, other_weight, value[i * 4 + 3]);
+                    }
+                }
+            }
             uint8_t* half = o_stage + (c >> 1) * kHalfBytes + row * 128;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 uint4 word;
-                word.x = tc::pack_bf16x2(__uint_as_float(acc[i * 8 + 0]) * inv, __uint_as_float(acc[i * 8 + 1]) * inv);
-                word.y = tc::pack_bf16x2(__uint_as_float(acc[i * 8 + 2]) * inv, __uint_as_float(acc[i * 8 + 3]) * inv);
-                word.z = tc::pack_bf16x2(__uint_as_float(acc[i * 8 + 4]) * inv, __uint_as_float(acc[i * 8 + 5]) * inv);
-                word.w = tc::pack_bf16x2(__uint_as_float(acc[i * 8 + 6]) * inv, __uint_as_float(acc[i * 8 + 7]) * inv);
+                word.x = tc::pack_bf16x2(value[i * 8 + 0], value[i * 8 + 1]);
+                word.y = tc::pack_bf16x2(value[i * 8 + 2], value[i * 8 + 3]);
+                word.z = tc::pack_bf16x2(value[i * 8 + 4], value[i * 8 + 5]);
+                word.w = tc::pack_bf16x2(value[i * 8 + 6], value[i * 8 + 7]);
                 const int chunk = (c & 1) * 4 + i;
                 *reinterpret_cast<uint4*>(half + ((chunk ^ (row & 7)) << 4)) = word;
             }
         }
-        const float row_lse = l > 0.f ? fmaf(m_used, p.scale, logf(l)) : INFINITY;
         lse_stage[row] = row_lse;
         tc::fence_proxy_async_smem();
         wg_barrier(h);  // one barrier publishes the O tile and the LSE array of this head
@@ -450,6 +532,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             tc::bulk_wait_read_all();  // shared memory must outlive the stores' reads; the writes finish on their own
         }
         if (!bulk_lse && row < rows_here) lse_out[row] = row_lse;
+        }
     }
 
     tc::tc_fence_before_sync();
@@ -490,10 +573,35 @@ size_t span_bytes(const int64_t strides[3], int64_t batch, int64_t tokens, int64
     return size_t((batch - 1) * strides[0] + (tokens - 1) * strides[1] + (heads - 1) * strides[2] + kDim) * 2;
 }
 
-template <bool kHandoff>
+// Key-split workspace: [claim, ready] words per unit (a unit is one head of one query tile), padded to 256
+// bytes, then the units' 64 KiB O slots, then their 512-byte LSE slots.
+struct SplitLayout {
+    int64_t units, ticket_bytes, o_offset, lse_offset, total;
+};
+SplitLayout split_layout(int64_t batch, int64_t tokens, int64_t q_heads) {
+    SplitLayout w;
+    w.units = ((tokens + kBlockM - 1) / kBlockM) * batch * q_heads;
+    w.ticket_bytes = (w.units * 8 + 255) / 256 * 256;
+    w.o_offset = w.ticket_bytes;
+    w.lse_offset = w.o_offset + w.units * int64_t(kBlockM) * kDim * 4;
+    w.total = w.lse_offset + w.units * int64_t(kBlockM) * 4;
+    return w;
+}
+
+// Two CTAs per query tile pay off when the longest tile alone (m_blocks key tiles) would outlast an even
+// share of all tiles per SM by a quarter or more, i.e. when the grid is too small to hide it, and the tiles
+// are long enough (16 key tiles) to carry a second CTA's fixed cost and the merge. Measured on 148 SMs at
+// 8192 tokens: 4 query heads 109 -> 71 us with two CTAs per tile, 8 heads 111 -> 133 us (not chosen).
+bool split_pays_off(const tc::DeviceInfo& info, int64_t batch, int64_t tokens, int64_t q_heads) {
+    const int64_t m_blocks = (tokens + kBlockM - 1) / kBlockM;
+    const int64_t tile_pairs = batch * (q_heads / 2) * m_blocks * (m_blocks + 1) / 2;
+    return m_blocks >= 16 && m_blocks * int64_t(info.sms) * 4 > tile_pairs * 5;
+}
+
+template <bool kHandoff, bool kSplit>
 int launch(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& omap,
            const PrefillParams& p, cudaStream_t stream) {
-    auto kernel = &prefill_kernel<kHandoff>;
+    auto kernel = &prefill_kernel<kHandoff, kSplit>;
     constexpr int shared = shared_bytes(kHandoff);
     static thread_local int configured_device = -1;
     int device = 0;
@@ -502,11 +610,17 @@ int launch(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& 
         TC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared));
         configured_device = device;
     }
-    const unsigned grid = unsigned(p.m_blocks) * p.batch * p.kv_heads * 2;
+    const unsigned grid = unsigned(p.m_blocks) * p.batch * p.kv_heads * 2 * (kSplit ? 2 : 1);
     kernel<<<grid, kThreads, shared, stream>>>(qmap, kmap, vmap, omap, p);
     TC_CUDA(cudaGetLastError());
     return TC_OK;
 }
+
+int prefill_common(int device, void* stream, const void* q, const int64_t q_strides[3], const void* k,
+                   const int64_t k_strides[3], const void* v, const int64_t v_strides[3], void* out, float* lse,
+                   int64_t batch, int64_t tokens, int64_t q_heads, int64_t num_splits, int64_t mapping, double scale,
+                   int causal, void* workspace, int64_t workspace_bytes, int key_splits,
+                   int64_t* key_splits_used = nullptr);
 
 }  // namespace
 
@@ -529,12 +643,47 @@ int tc_prefill_forward_out(int device, void* stream, const void* q, const int64_
                            float* lse, int64_t workspace_o_elems, int64_t workspace_lse_elems, int64_t batch,
                            int64_t tokens, int64_t q_heads, int64_t num_splits, int64_t mapping, double scale,
                            int causal) {
+    TC_REQUIRE(workspace_o_elems == 0 && workspace_lse_elems == 0, "Generated long prefill uses no split workspace");
+    return prefill_common(device, stream, q, q_strides, k, k_strides, v, v_strides, out, lse, batch, tokens, q_heads,
+                          num_splits, mapping, scale, causal, nullptr, 0, 1);
+}
+
+int tc_prefill_key_split_workspace_bytes(int64_t batch, int64_t tokens, int64_t q_heads, int64_t* bytes) {
+    TC_REQUIRE(bytes && batch >= 1 && tokens >= 1 && q_heads >= 4 && q_heads % 4 == 0, "invalid geometry");
+    *bytes = split_layout(batch, tokens, q_heads).total;
+    return TC_OK;
+}
+
+int tc_prefill_key_split_forward_out(int device, void* stream, const void* q, const int64_t q_strides[3], const void* k,
+                                     const int64_t k_strides[3], const void* v, const int64_t v_strides[3], void* out,
+                                     float* lse, void* workspace, int64_t workspace_bytes, int64_t batch,
+                                     int64_t tokens, int64_t q_heads, int64_t mapping, double scale, int64_t key_splits,
+                                     int64_t* key_splits_used) {
+    TC_REQUIRE(key_splits >= 0 && key_splits <= 2, "key_splits must be 0 (choose), 1 or 2");
+    return prefill_common(device, stream, q, q_strides, k, k_strides, v, v_strides, out, lse, batch, tokens, q_heads, 0,
+                          mapping, scale, 1, workspace, workspace_bytes, int(key_splits), key_splits_used);
+}
+
+}  // extern "C"
+
+namespace {
+
+int prefill_common(int device, void* stream, const void* q, const int64_t q_strides[3], const void* k,
+                   const int64_t k_strides[3], const void* v, const int64_t v_strides[3], void* out, float* lse,
+                   int64_t batch, int64_t tokens, int64_t q_heads, int64_t num_splits, int64_t mapping, double scale,
+                   int causal, void* workspace, int64_t workspace_bytes, int key_splits, int64_t* key_splits_used) {
     tc::DeviceInfo info;
     int status = check_geometry(device, batch, tokens, q_heads, num_splits, mapping, causal, &info);
     if (status != TC_OK) return status;
     const int64_t kv_heads = q_heads / kGroup;
     TC_REQUIRE(q && k && v && out && lse, "null tensor pointer");
-    TC_REQUIRE(workspace_o_elems == 0 && workspace_lse_elems == 0, "Generated long prefill uses no split workspace");
+    if (key_splits == 0) key_splits = split_pays_off(info, batch, tokens, q_heads) ? 2 : 1;
+    if (key_splits_used) *key_splits_used = key_splits;
+    const SplitLayout split = split_layout(batch, tokens, q_heads);
+    if (key_splits == 2) {
+        TC_REQUIRE(workspace && reinterpret_cast<uintptr_t>(workspace) % 256 == 0 && workspace_bytes >= split.total,
+                   "key-split prefill needs a 256-byte aligned workspace of tc_prefill_key_split_workspace_bytes bytes");
+    }
     TC_REQUIRE(std::isfinite(scale) && scale > 0, "Finite positive model attention scale required");
     if ((status = check_strides("q", q_strides, batch, tokens, q_heads)) != TC_OK) return status;
     if ((status = check_strides("k", k_strides, batch, tokens, kv_heads)) != TC_OK) return status;
@@ -573,9 +722,25 @@ int tc_prefill_forward_out(int device, void* stream, const void* q, const int64_
     p.scale = float(scale);
     p.scale_log2 = float(scale) * float(M_LOG2E);
     TC_REQUIRE(std::isfinite(p.scale_log2) && p.scale > 0.f, "attention scale is not a positive finite FP32 value");
-    return mapping == 1 ? launch<true>(qmap, kmap, vmap, omap, p, static_cast<cudaStream_t>(stream))
-                        : launch<false>(qmap, kmap, vmap, omap, p, static_cast<cudaStream_t>(stream));
+    cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+    if (key_splits == 2) {
+        uint8_t* base = static_cast<uint8_t*>(workspace);
+        for (const void* pointer : {q, k, v, static_cast<const void*>(out), static_cast<const void*>(lse)})
+            TC_REQUIRE(!tc::ranges_overlap(workspace, size_t(split.total), pointer, 1), "workspace aliases a tensor");
+        p.tickets = reinterpret_cast<int32_t*>(base);
+        p.part_o = reinterpret_cast<float4*>(base + split.o_offset);
+        p.part_lse = reinterpret_cast<float*>(base + split.lse_offset);
+        TC_CUDA(cudaMemsetAsync(base, 0, size_t(split.ticket_bytes), cuda_stream));
+        return mapping == 1 ? launch<true, true>(qmap, kmap, vmap, omap, p, cuda_stream)
+                            : launch<false, true>(qmap, kmap, vmap, omap, p, cuda_stream);
+    }
+    return mapping == 1 ? launch<true, false>(qmap, kmap, vmap, omap, p, cuda_stream)
+                        : launch<false, false>(qmap, kmap, vmap, omap, p, cuda_stream);
 }
+
+}  // namespace
+
+extern "C" {
 
 int tc_prefill_resources(int device, const int64_t q_strides[3], const int64_t k_strides[3],
                          const int64_t v_strides[3], int64_t batch, int64_t tokens, int64_t q_heads,

@@ -170,6 +170,13 @@ class Library:
             ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64), ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64),
             ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64), ctypes.c_void_p, ctypes.c_void_p,
             *[ctypes.c_int64] * 7, ctypes.c_double, ctypes.c_int)),
+        "tc_prefill_key_split_workspace_bytes": (ctypes.c_int, (*[ctypes.c_int64] * 3, ctypes.POINTER(ctypes.c_int64))),
+        "tc_prefill_key_split_forward_out": (ctypes.c_int, (
+            ctypes.c_int, ctypes.c_void_p,
+            ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64), ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64),
+            ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64), ctypes.c_void_p, ctypes.c_void_p,
+            ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 4, ctypes.c_double, ctypes.c_int64,
+            ctypes.POINTER(ctypes.c_int64))),
         "tc_prefill_resources": (ctypes.c_int, (
             ctypes.c_int, *[ctypes.POINTER(ctypes.c_int64)] * 3, *[ctypes.c_int64] * 5, ctypes.c_int,
             ctypes.POINTER(ctypes.c_int64), ctypes.c_int64, ctypes.POINTER(ctypes.c_int64))),
@@ -353,6 +360,33 @@ class PrefillOps:
                 raise RuntimeError("tc_prefill_forward_out: " + library.handle.tc_last_error().decode("utf-8", "replace"))
 
         return invoke
+
+    def key_split_workspace_bytes(self, q):
+        """Bytes of the uint8 workspace :meth:`key_split_forward_out` needs for ``q``'s geometry."""
+        size = ctypes.c_int64(0)
+        self.library.call("tc_prefill_key_split_workspace_bytes", q.size(0), q.size(1), q.size(2), ctypes.byref(size))
+        return size.value
+
+    def key_split_forward_out(self, q, k, v, out, lse, workspace, mapping, scale, key_splits=0):
+        """Prefill with up to two CTAs per query tile (``tc_prefill_key_split_forward_out``): for launches that
+        cannot fill the GPU otherwise, such as a KV-head-group shard. ``workspace`` is a uint8 CUDA tensor of
+        :meth:`key_split_workspace_bytes` bytes. Returns the number of key splits used (1 or 2)."""
+        import torch
+
+        self._check_inputs(q, k, v, True)
+        _require(out.device == q.device and out.dtype == q.dtype and out.shape == q.shape and out.is_contiguous()
+                 and not out.requires_grad, "Common complete output must be contiguous BNHD with Q shape")
+        _require(lse.device == q.device and lse.dtype == torch.float32 and lse.is_contiguous() and not lse.requires_grad
+                 and tuple(lse.shape) == (q.size(0), q.size(2), q.size(1)),
+                 f"Complete natural-log LSE must be FP32[B,{q.size(2)},Tq]")
+        _require(workspace.device == q.device and workspace.dtype == torch.uint8 and workspace.is_contiguous(),
+                 "Contiguous CUDA uint8 workspace required")
+        used = ctypes.c_int64(0)
+        self.library.call(
+            "tc_prefill_key_split_forward_out", q.device.index, _stream(q), _pointer(q), _strides(q), _pointer(k),
+            _strides(k), _pointer(v), _strides(v), _pointer(out), _pointer(lse), _pointer(workspace), workspace.numel(),
+            q.size(0), q.size(1), q.size(2), int(mapping), float(scale), int(key_splits), ctypes.byref(used))
+        return used.value
 
     def resources(self, q, k, v, num_splits, mapping, causal):
         self._check_inputs(q, k, v, causal)
