@@ -9,11 +9,12 @@ Headline workload (``config.workload``): BASELINE config 2, causal prefill, BF16
 tokens, 32 query / 8 KV heads, D = 128, N(0,1) inputs from seed 1 (synthetic stand-ins for the
 reference's saved Qwen3 projections). A step is one forward over that batch.
 
-* ``value``      TFLOP/s (4*B*Hq*S^2*D/2 per step) with inputs resident in HBM, all ranks together.
-                 At N > 1 every rank runs its own batch of the same shape (the units are (batch, KV-head
-                 group) pairs, eight per rank, no collective): weak scaling.
+* ``value``      TFLOP/s (4*B*Hq*S^2*D/2 per step) with inputs resident in HBM. At N > 1 that ONE batch is
+                 split by KV-head group over the ranks (rank r holds KV heads [8r/N, 8(r+1)/N) and their
+                 query heads; no collective): strong scaling, value = the batch's FLOPs / the slowest rank's
+                 time. ``prefill_replicas`` (N > 1) is the other experiment, one whole batch per rank.
 * ``e2e``        the same metric through the operator API with HOST buffers: every step copies its
-                 Q/K/V from pinned host memory and reads O and LSE back; copies and kernels of
+                 (slice of) Q/K/V from pinned host memory and reads O and LSE back; copies and kernels of
                  neighbouring steps overlap on three streams.
 * ``roofline``   the prefill kernel against the measured dense BF16 peak.
 * ``decode``     split-KV decode with fused append: config 4 (batch 1, 8192 of 32768 rows valid) and
@@ -24,11 +25,15 @@ reference's saved Qwen3 projections). A step is one forward over that batch.
                  shapes) as HBM GB/s of streamed weights.
 * ``layer_chain`` projection then config-4 decode as a layer runs them, microseconds per layer, with the plain
                  decode entry and with the cache-stable promise (K/V streamed while the projection finishes).
-* ``prefill_sharded`` (N > 1) config 2 itself split by KV-head group over the ranks (strong scaling).
+* ``checks``     (N > 1) results of the sharded paths compared outside the timed regions: the sharded prefill
+                 against the CPU oracle on sampled rows, both sharded decode routes bit for bit against the
+                 standalone combine of the same shards' partials and against the CPU oracle on sampled heads.
+                 A miss ends the run with a non-zero exit code.
 * ``cpu_baseline`` the CPU oracle (the reference's only CPU attention, ``bench_exchange.py:54-60``)
                  timed on this host on a bounded sample.
 
-``--impl reference`` times that CPU attention alone, on rank 0, with all host threads.
+``--impl reference`` times that CPU attention alone on the whole config-2 batch, on rank 0, with all host
+threads.
 """
 from __future__ import annotations
 
@@ -54,6 +59,7 @@ DECODE_C4 = dict(batch=1, capacity=32768, valid=8192, seed=3)
 DECODE_C5 = dict(batch=4, capacity=32768, valid=32767, seed=4)
 METRIC = "causal_prefill_tflops"
 UNIT = "TFLOP/s"
+WORKLOAD = "config2 causal GQA prefill B1 S8192 Hq32 Hkv8 D128 seed1"
 
 
 def prefill_flops(batch, tokens, heads=HQ):
@@ -65,6 +71,35 @@ def decode_bytes(batch, attended, kv_heads=HKV):
     q_heads = kv_heads * 4
     return (2 * batch * attended * kv_heads * DIM * 2 + 2 * batch * q_heads * DIM * 2 + batch * q_heads * 4
             + 4 * batch * kv_heads * DIM * 2)
+
+
+def prefill_rank_bytes(world):
+    """Bytes of one rank's Q, K, V, O and LSE for its KV-head-group share of the headline batch."""
+    batch, tokens = PREFILL["batch"], PREFILL["tokens"]
+    heads_q, heads_kv = HQ // world, HKV // world
+    return batch * tokens * ((2 * heads_q + 2 * heads_kv) * DIM * 2 + heads_q * 4)
+
+
+def prefill_buffer_sets(world):
+    """Rotating buffer sets per rank: a shard smaller than L2 would be re-read from L2 by the next step, so enough
+    sets rotate that a set is evicted before its turn comes again. One rank's whole batch (169 MB) exceeds L2."""
+    rank_bytes = prefill_rank_bytes(world)
+    return 1 if rank_bytes > 130e6 else -(-int(2.2 * 126e6) // rank_bytes)
+
+
+def bench_config(world):
+    """The ``config`` object of the JSON line: both arms state the same workload."""
+    if world == 1:
+        return {"workload": WORKLOAD + ", one GPU",
+                "l2": "inputs+outputs 161 MiB per step, larger than the 126 MB L2",
+                "decode_l2": "rotating cache sets larger than L2",
+                "timing": "direct operator calls back to back"}
+    return {"workload": WORKLOAD + f", the one batch split by KV-head group over {world} GPUs ({HKV // world} KV / "
+                        f"{HQ // world} query heads per GPU, no collective)",
+            "l2": f"{prefill_buffer_sets(world)} rotating buffer sets of {prefill_rank_bytes(world) / 2**20:.0f} MiB per "
+                  "GPU, together larger than twice the 126 MB L2",
+            "decode_l2": "rotating cache sets larger than L2",
+            "timing": "one captured graph per buffer set, replayed back to back"}
 
 
 def measured_peaks():
@@ -121,16 +156,20 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------- CPU arm
-def cpu_attention_sample(torch, oracle, seconds_hint=10.0, steps=None, warmup=0):
-    """Time the CPU oracle on one KV-head group (4 query heads) of the headline workload.
+def cpu_attention_sample(torch, oracle, seconds_hint=10.0, steps=None, warmup=0, kv_groups=1):
+    """Time the CPU oracle on `kv_groups` KV-head groups (4 query heads each) of the headline workload;
+    8 groups is the whole config-2 batch.
 
-    Returns (TFLOP/s, threads, description, seconds per pass). The sample is 1/8 of a step's FLOPs;
-    throughput is per FLOP, so no scaling is applied.
+    Returns (TFLOP/s, threads, description, seconds per pass). Throughput is per FLOP, so a sample of
+    fewer groups needs no scaling.
     """
+    from tilecadence_b200.synthetic import seeded_normal
+
     torch.set_num_threads(os.cpu_count() or 1)
     tokens = PREFILL["tokens"]
-    q, k, v = oracle.seeded_normal(PREFILL["seed"], (1, tokens, 4, DIM), (1, tokens, 1, DIM), (1, tokens, 1, DIM))
-    flops = prefill_flops(1, tokens, heads=4)
+    q, k, v = seeded_normal(PREFILL["seed"], (1, tokens, HQ, DIM), (1, tokens, HKV, DIM), (1, tokens, HKV, DIM))
+    q, k, v = q[:, :, :4 * kv_groups].contiguous(), k[:, :, :kv_groups].contiguous(), v[:, :, :kv_groups].contiguous()
+    flops = prefill_flops(1, tokens, heads=4 * kv_groups)
     oracle.attention(q[:, :1024], k[:, :1024], v[:, :1024], causal=True)  # warm the thread pool
     for _ in range(warmup):
         oracle.attention(q, k, v, causal=True)
@@ -146,8 +185,9 @@ def cpu_attention_sample(torch, oracle, seconds_hint=10.0, steps=None, warmup=0)
         elif time.perf_counter() - started > seconds_hint or len(times) >= 50:
             break
     best = statistics.median(times)
-    description = (f"one KV-head group (4 of 32 query heads, all {tokens} rows) of the config-2 prefill, "
-                   f"{len(times)} passes, median")
+    what = "the whole config-2 prefill batch (32 query / 8 KV heads" if kv_groups == HKV else \
+        f"{kv_groups} KV-head group(s) ({4 * kv_groups} of 32 query heads"
+    description = f"{what}, all {tokens} rows), {len(times)} passes, median"
     return flops / best / 1e12, torch.get_num_threads(), description, best
 
 
@@ -157,14 +197,17 @@ def run_reference(args, rank):
     import torch
     from oracle import attention as oracle
 
+    # The whole batch per step (about 1.6 s on 16 threads), so that this arm runs the config it states.
     value, threads, description, seconds = cpu_attention_sample(torch, oracle, steps=max(1, args.steps),
-                                                                warmup=args.warmup)
+                                                                warmup=args.warmup, kv_groups=HKV)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config2 causal GQA prefill B1 S8192 Hq32 Hkv8 D128 seed1 (CPU sample)"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": description},
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": bench_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": description + "; fp32 torch attention restating the reference's "
+                                   "bench_exchange._reference, host threads only, rank 0"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -175,8 +218,9 @@ def run_reference(args, rank):
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
-    from oracle import attention as oracle  # CPU baseline leg only
+    from oracle import attention as oracle  # the checker (N > 1 result checks) and the timed CPU baseline leg
     from tilecadence_b200 import cuda_runtime, sharding
+    from tilecadence_b200.synthetic import seeded_normal
 
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
@@ -188,7 +232,6 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     library = cuda_runtime.default_library()
-    prefill_ops = cuda_runtime.ops_for(library, "prefill")
     decode_ops = cuda_runtime.ops_for(library, "decode")
     peaks = measured_peaks()
     launches = 0
@@ -219,18 +262,74 @@ def run_ours(args, rank, world, local_rank):
         barrier()
         return max_over_ranks(start.elapsed_time(end))
 
-    # ------------------------------------------------------------------ prefill, resident inputs
-    batch, tokens = PREFILL["batch"], PREFILL["tokens"]
-    host = oracle.seeded_normal(PREFILL["seed"] + 1000 * rank, (batch, tokens, HQ, DIM), (batch, tokens, HKV, DIM),
-                                (batch, tokens, HKV, DIM))
-    host = [tensor.pin_memory() for tensor in host]
-    q, k, v = (tensor.to(device) for tensor in host)
-    out = torch.empty_like(q)
-    lse = torch.empty((batch, HQ, tokens), device=device, dtype=torch.float32)
-    empty = torch.empty(0, device=device, dtype=torch.float32)
+    check_failures = []
 
-    def prefill_step():
-        prefill_ops.forward_out(q, k, v, out, lse, empty, empty, 0, 1, SCALE, True)
+    def checked(name, fn):
+        """Run a result check outside the timed regions; a miss is recorded and ends the run at the end."""
+        try:
+            return fn()
+        except AssertionError as error:
+            check_failures.append(f"rank {rank}: {name}: {error}")
+            print(f"CHECK FAILED on rank {rank}: {name}: {error}", file=sys.stderr, flush=True)
+            return None
+
+    def graph_of(fn):
+        """One call of `fn` captured as a CUDA graph (the call runs once un-captured first)."""
+        stream = torch.cuda.Stream(device)
+        with torch.cuda.stream(stream):
+            fn()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                fn()
+        return graph
+
+    # ------------------------------------------------------------------ prefill, resident inputs
+    # The headline batch, split by KV-head group over the ranks (all of it at N = 1).
+    batch, tokens = PREFILL["batch"], PREFILL["tokens"]
+    if HKV % world:
+        raise SystemExit(f"{HKV} KV heads do not divide over {world} ranks")
+    kv_slice, q_slice = sharding.kv_head_slice(rank, world, HKV)
+    local_hq = HQ // world
+    whole = seeded_normal(PREFILL["seed"], (batch, tokens, HQ, DIM), (batch, tokens, HKV, DIM), (batch, tokens, HKV, DIM))
+    host = [whole[0][:, :, q_slice].contiguous().pin_memory(), whole[1][:, :, kv_slice].contiguous().pin_memory(),
+            whole[2][:, :, kv_slice].contiguous().pin_memory()]
+    prefill_ops = cuda_runtime.ops_for(library, "prefill", q_heads=local_hq)
+    empty = torch.empty(0, device=device, dtype=torch.float32)
+    sets = prefill_buffer_sets(world)
+    buffers = []
+    for _ in range(sets):
+        dq, dk, dv = (tensor.to(device) for tensor in host)
+        buffers.append(dict(q=dq, k=dk, v=dv, out=torch.empty_like(dq),
+                            lse=torch.empty((batch, local_hq, tokens), device=device, dtype=torch.float32)))
+    split_ws = None
+    if world == 1:
+        def prefill_call(slot):
+            prefill_ops.forward_out(slot["q"], slot["k"], slot["v"], slot["out"], slot["lse"], empty, empty, 0, 1,
+                                    SCALE, True)
+            return 1
+    else:
+        # A shard of few heads cannot fill the GPU with one CTA per query tile: the key-split entry then gives
+        # every tile to two CTAs (its own choice; with one CTA per tile it is the plain kernel).
+        split_ws = torch.empty(prefill_ops.key_split_workspace_bytes(buffers[0]["q"]), device=device, dtype=torch.uint8)
+
+        def prefill_call(slot):
+            return prefill_ops.key_split_forward_out(slot["q"], slot["k"], slot["v"], slot["out"], slot["lse"], split_ws,
+                                                     1, SCALE, 0)
+    ctas_per_query_tile = prefill_call(buffers[0])
+    turn = [0]
+    if world == 1:
+        def prefill_step():
+            prefill_call(buffers[turn[0] % sets])
+            turn[0] += 1
+    else:
+        # A shard's step is shorter than the Python call path, so each buffer set's step is captured once and the
+        # timed region replays those graphs back to back.
+        graphs = [graph_of(lambda slot=slot: prefill_call(slot)) for slot in buffers]
+
+        def prefill_step():
+            graphs[turn[0] % sets].replay()
+            turn[0] += 1
 
     uuid = str(torch.cuda.get_device_properties(device).uuid)
     uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
@@ -240,14 +339,13 @@ def run_ours(args, rank, world, local_rank):
     launches += args.steps
     ms_per_step = prefill_ms / args.steps
     step_flops = prefill_flops(batch, tokens)
-    value = world * step_flops / (ms_per_step * 1e-3) / 1e12
-    achieved = step_flops / (ms_per_step * 1e-3) / 1e12
+    value = step_flops / (ms_per_step * 1e-3) / 1e12                 # the one batch, all ranks together
+    achieved = step_flops / world / (ms_per_step * 1e-3) / 1e12      # the kernel on one GPU
 
     # ------------------------------------------------------------------ prefill, host buffers (e2e)
-    host_out = [torch.empty(out.shape, dtype=out.dtype).pin_memory() for _ in range(2)]
-    host_lse = [torch.empty(lse.shape, dtype=lse.dtype).pin_memory() for _ in range(2)]
-    slots = [dict(q=torch.empty_like(q), k=torch.empty_like(k), v=torch.empty_like(v), out=torch.empty_like(out),
-                  lse=torch.empty_like(lse)) for _ in range(2)]
+    host_out = [torch.empty(buffers[0]["out"].shape, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    host_lse = [torch.empty(buffers[0]["lse"].shape, dtype=torch.float32).pin_memory() for _ in range(2)]
+    slots = [{name: torch.empty_like(tensor) for name, tensor in buffers[0].items()} for _ in range(2)]
     copy_in, compute, copy_out = (torch.cuda.Stream(device) for _ in range(3))
 
     def e2e_run(steps):
@@ -270,8 +368,7 @@ def run_ours(args, rank, world, local_rank):
                 compute.wait_event(loaded[index % 2])
                 if drained[index % 2] is not None:
                     compute.wait_event(drained[index % 2])  # the previous result left this slot
-                prefill_ops.forward_out(slot["q"], slot["k"], slot["v"], slot["out"], slot["lse"], empty, empty, 0, 1,
-                                        SCALE, True)
+                prefill_call(slot)
                 computed[index % 2] = torch.cuda.Event()
                 computed[index % 2].record(compute)
             with torch.cuda.stream(copy_out):
@@ -290,37 +387,116 @@ def run_ours(args, rank, world, local_rank):
     launches += args.steps
     sampler.__exit__(None, None, None)
     clocks = sampler.summary()
-    e2e_value = world * step_flops / (e2e_ms / args.steps * 1e-3) / 1e12
-    h2d_bytes = sum(t.numel() * t.element_size() for t in host)
-    d2h_bytes = out.numel() * out.element_size() + lse.numel() * lse.element_size()
-    del slots, host_out, host_lse
+    e2e_value = step_flops / (e2e_ms / args.steps * 1e-3) / 1e12
+    h2d_bytes = world * sum(t.numel() * t.element_size() for t in host)
+    d2h_bytes = world * (host_out[0].numel() * 2 + host_lse[0].numel() * 4)
 
-    # ------------------------------------------------------------------ prefill sharded by KV-head group (N > 1)
-    prefill_sharded = None
-    if world > 1 and HKV % world == 0:
-        kv_slice, q_slice = sharding.kv_head_slice(rank, world, HKV)
-        shared = oracle.seeded_normal(PREFILL["seed"], (batch, tokens, HQ, DIM), (batch, tokens, HKV, DIM),
-                                      (batch, tokens, HKV, DIM))
-        sq = shared[0][:, :, q_slice].contiguous().to(device)
-        sk = shared[1][:, :, kv_slice].contiguous().to(device)
-        sv = shared[2][:, :, kv_slice].contiguous().to(device)
-        shard_ops = cuda_runtime.ops_for(library, "prefill", q_heads=HQ // world)
-        sout, slse = torch.empty_like(sq), torch.empty((batch, HQ // world, tokens), device=device)
-        # A shard of few heads cannot fill the GPU with one CTA per query tile: the key-split entry then
-        # gives every tile to two CTAs (its own choice; one CTA per tile is the plain kernel).
-        split_ws = torch.empty(shard_ops.key_split_workspace_bytes(sq), device=device, dtype=torch.uint8)
-        key_splits = shard_ops.key_split_forward_out(sq, sk, sv, sout, slse, split_ws, 1, SCALE, 0)
-        shard_ms = timed(lambda: shard_ops.key_split_forward_out(sq, sk, sv, sout, slse, split_ws, 1, SCALE, 0),
-                         args.steps, args.warmup)
+    # ------------------------------------------------------------------ the sharded prefill's result, checked
+    checks = {}
+    if world > 1:
+        def check_prefill(got_o, got_lse, label):
+            """Sampled 64-row blocks of this rank's first and last KV-head group against the CPU oracle."""
+            worst = [0.0, 0.0]
+            local_kv = HKV // world
+            for r0 in (0, 4032, tokens - 64):
+                rows = slice(r0, r0 + 64)
+                for g in sorted({0, local_kv - 1}):
+                    qh = host[0][0, rows, g * 4:(g + 1) * 4].float().permute(1, 0, 2)
+                    scores = (qh @ host[1][0, :r0 + 64, g].float().T) * SCALE
+                    scores.masked_fill_(torch.arange(r0 + 64)[None, :] > torch.arange(r0, r0 + 64)[:, None], float("-inf"))
+                    want_o = (scores.softmax(-1) @ host[2][0, :r0 + 64, g].float()).permute(1, 0, 2)
+                    errors = oracle.check_outputs(got_o[0, rows, g * 4:(g + 1) * 4], got_lse[0, g * 4:(g + 1) * 4, rows],
+                                                  want_o, scores.logsumexp(-1))
+                    worst = [max(a, b) for a, b in zip(worst, errors)]
+            assert torch.isfinite(got_lse).all() and torch.isfinite(got_o.float()).all(), f"{label}: non-finite output"
+            return worst
+
+        torch.cuda.synchronize(device)
+        resident = checked("sharded prefill (resident buffers)",
+                           lambda: check_prefill(buffers[-1]["out"].cpu(), buffers[-1]["lse"].cpu(), "resident"))
+        through_host = checked("sharded prefill (host buffers)",
+                               lambda: check_prefill(host_out[(args.steps - 1) % 2], host_lse[(args.steps - 1) % 2], "e2e"))
+        ok = resident is not None and through_host is not None
+        worst = [max(a, b) for a, b in zip(resident, through_host)] if ok else [float("inf")] * 2
+        worst = [max_over_ranks(x) for x in worst]  # every rank takes part, whatever its own outcome
+        ok = all(x != float("inf") for x in worst)
+        checks["prefill"] = {"checked": ok, "against": "CPU oracle, three 64-row blocks of two KV-head groups per rank, "
+                                                      "resident and host-buffer results",
+                             "o_max_abs": worst[0] if ok else None, "lse_rel": worst[1] if ok else None}
+    del slots, host_out, host_lse, buffers, split_ws
+    if world > 1:
+        del graphs
+    torch.cuda.empty_cache()
+
+    # ------------------------------------------------------------------ N > 1: one whole batch per rank (replicas)
+    prefill_replicas = None
+    if world > 1:
+        full_ops = cuda_runtime.ops_for(library, "prefill")
+        fq, fk, fv = (tensor.to(device) for tensor in whole)
+        fout, flse = torch.empty_like(fq), torch.empty((batch, HQ, tokens), device=device, dtype=torch.float32)
+        replica_ms = timed(lambda: full_ops.forward_out(fq, fk, fv, fout, flse, empty, empty, 0, 1, SCALE, True),
+                           args.steps, args.warmup)
         launches += args.steps
-        prefill_sharded = {"workload": "config2 split by KV-head group over the ranks (strong scaling, no collective)",
-                           "value": step_flops / (shard_ms / args.steps * 1e-3) / 1e12, "unit": UNIT,
-                           "ms_per_step": shard_ms / args.steps, "ctas_per_query_tile": key_splits}
-        del sq, sk, sv, sout, slse, shared, split_ws
-    del q, k, v, out, lse
+        prefill_replicas = {"workload": WORKLOAD + ", one whole batch per GPU (weak scaling, no shared work)",
+                            "value": world * step_flops / (replica_ms / args.steps * 1e-3) / 1e12, "unit": UNIT,
+                            "ms_per_step": replica_ms / args.steps}
+        del fq, fk, fv, fout, flse
+    del whole
     torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ decode
+    def verify_sharded(driver, cache, dq, dkn, dvn, old, dout, dlse, shard_start, route):
+        """One more step of a sharded route, outside any timed region, compared (a) bit for bit with the
+        standalone combine of every rank's partial of the same shard (all-gathered), and (b) with the CPU oracle
+        on two KV-head groups whose cache rows are gathered from all ranks."""
+        kc, vc = cache
+        cbatch, rows = dq.size(0), dq.size(0) * HQ
+        dout.fill_(float("nan"))
+        dlse.fill_(float("nan"))
+        driver.step(dq, kc, vc, dkn, dvn, old, dout, dlse)
+        packed = torch.empty(rows * (DIM + 1), device=device, dtype=torch.float32)
+        part_o, part_lse = packed[:rows * DIM].view(rows, DIM), packed[rows * DIM:]
+        spec = decode_ops.workspace_spec(dq, kc, old, 0, 1, True)
+        scratch = [torch.empty(n, device=device, dtype=torch.float32) for n in spec[1:3]]
+        decode_ops.partial_out(dq, kc, vc, dkn, dvn, old, part_o, part_lse, *scratch, 0, 1, True, shard_start)
+        gathered = torch.empty((world, packed.numel()), device=device, dtype=torch.float32)
+        dist.all_gather_into_tensor(gathered, packed)
+        ref_o, ref_lse = torch.empty_like(dout), torch.empty_like(dlse)
+        decode_ops.combine_partials(gathered[:, :rows * DIM].unflatten(1, (rows, DIM)), gathered[:, rows * DIM:], ref_o,
+                                    ref_lse)
+        torch.cuda.synchronize(device)
+
+        def bits():
+            assert torch.equal(dout.view(torch.int16), ref_o.view(torch.int16)), "O differs from the standalone combine"
+            assert torch.equal(dlse.view(torch.int32), ref_lse.view(torch.int32)), "LSE differs from the standalone combine"
+            return True
+
+        def against_oracle():
+            worst = [0.0, 0.0]
+            for g in (0, 5):
+                full = []
+                for cache_part in (kc, vc):
+                    mine = cache_part[:, :, g:g + 1].contiguous()
+                    everyone = torch.empty((world, *mine.shape), device=device, dtype=mine.dtype)
+                    dist.all_gather_into_tensor(everyone, mine)
+                    full.append(everyone.permute(1, 0, 2, 3, 4).flatten(1, 2).cpu())  # [B, capacity, 1, 128]
+                heads = slice(g * 4, (g + 1) * 4)
+                want_o, want_lse, _, _ = oracle.decode_step(dq[:, :, heads].cpu(), full[0], full[1], dkn[:, :, g:g + 1].cpu(),
+                                                            dvn[:, :, g:g + 1].cpu(), old.cpu())
+                errors = oracle.check_outputs(dout[:, :, heads].cpu(), dlse[:, heads].cpu(), want_o, want_lse)
+                worst = [max(a, b) for a, b in zip(worst, errors)]
+            return worst
+
+        bit_equal = checked(f"sharded decode ({route} route) vs standalone combine", bits) is not None
+        worst = checked(f"sharded decode ({route} route) vs CPU oracle", against_oracle) or [float("inf")] * 2
+        worst = [max_over_ranks(x) for x in worst]
+        bit_equal = max_over_ranks(0.0 if bit_equal else 1.0) == 0.0
+        ok = bit_equal and all(x != float("inf") for x in worst)
+        return {"checked": ok, "bitwise_equal_to_standalone_combine": bit_equal,
+                "against": "tc_combine_partials of the all-gathered per-rank partials (bits); CPU oracle on KV-head "
+                           "groups 0 and 5 with cache rows gathered from all ranks",
+                "o_max_abs": worst[0] if ok else None, "lse_rel": worst[1] if ok else None}
+
     def decode_case(case, sets, graph_steps, sharded):
         nonlocal launches
         cbatch, capacity, valid = case["batch"], case["capacity"], case["valid"]
@@ -365,6 +541,16 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize(device)
         eager_ms = timed(step, graph_steps * 4, 3) / (graph_steps * 4)
         launches += graph_steps * 4 * per_launch
+        checked_call_ms = None
+        if not sharded:
+            # The same steps through the reference-signature call, which validates its tensors every time.
+            def checked_step():
+                kc, vc = caches[counter[0] % sets]
+                counter[0] += 1
+                decode_ops.forward_out(dq, kc, vc, dkn, dvn, old, dout, dlse, *workspace, 0, 1, True)
+
+            checked_call_ms = timed(checked_step, graph_steps * 4, 3) / (graph_steps * 4)
+            launches += graph_steps * 4
         graph_ms = None
         try:
             # The kernel is a few microseconds long, so host launch cost hides it; replaying a captured
@@ -392,6 +578,12 @@ def run_ours(args, rank, world, local_rank):
         gbs = rank_bytes / (best_ms * 1e-3) / 1e9
         result = {"batch": cbatch, "capacity": capacity, "attended_rows": valid + 1, "splits": splits,
                   "us_per_step_eager": eager_ms * 1e3, "us_per_step_graph": None if graph_ms is None else graph_ms * 1e3,
+                  "entry": ("sharding.ShardedDecode.step" if sharded else
+                            "us_per_step_eager: DecodeOps.bind_forward_out (buffers validated once, then launches "
+                            "only; not in the reference); us_per_step_eager_forward_out: DecodeOps.forward_out, the "
+                            "reference-signature call; us_per_step_graph: graph replay of the same launches, which "
+                            "holds no host call path at all. hbm_gbs_per_gpu uses the fastest of them"),
+                  "us_per_step_eager_forward_out": None if checked_call_ms is None else checked_call_ms * 1e3,
                   "hbm_gbs_per_gpu": gbs, "bytes_per_step_per_gpu": rank_bytes,
                   "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
                                "frac": gbs / peaks["hbm"],
@@ -399,6 +591,7 @@ def run_ours(args, rank, world, local_rank):
                                "peak_source": peaks["source"]},
                   "cache_sets": sets}
         if driver is not None:
+            result["check"] = verify_sharded(driver, caches[0], dq, dkn, dvn, old, dout, dlse, shard_start, sharded)
             torch.cuda.synchronize(device)
             driver.close()
         del caches
@@ -533,31 +726,43 @@ def run_ours(args, rank, world, local_rank):
     status = library.device_status(device.index)
     if status != 0:
         raise RuntimeError(f"a kernel reported an expired wait (status {status}); results are invalid")
+    if world > 1:
+        for key in ("c5", "c5_nccl"):
+            if decode.get(key) and "check" in decode[key]:
+                checks[key] = decode[key]["check"]
+        failed = max_over_ranks(float(len(check_failures)))
+        if failed:
+            if rank == 0:
+                print("result checks failed; no benchmark line is printed", file=sys.stderr, flush=True)
+            dist.barrier()
+            dist.destroy_process_group()
+            raise SystemExit(1)
 
     # ------------------------------------------------------------------ CPU baseline (rank 0, N = 1)
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
-        cpu_value, threads, description, _ = cpu_attention_sample(torch, oracle, seconds_hint=12.0)
+        cpu_value, threads, description, _ = cpu_attention_sample(torch, oracle, seconds_hint=12.0, kv_groups=HKV)
         cpu_baseline = {"value": cpu_value, "unit": UNIT, "cores": threads, "kind": "port", "sample": description}
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "config2 causal GQA prefill B1 S8192 Hq32 Hkv8 D128 seed1, one batch per GPU",
-                       "l2": "inputs+outputs 161 MiB per step, larger than the 126 MB L2",
-                       "decode_l2": "rotating cache sets larger than L2"},
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": bench_config(world), "prefill": {"ctas_per_query_tile": ctas_per_query_tile, "buffer_sets": sets},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16"], "frac_of_sustained": achieved / peaks["bf16_sustained"],
-                         "traffic": NCU_TRAFFIC_BYTES["prefill_c2"], "peak_source": peaks["source"] + " burst"},
+                         "traffic": NCU_TRAFFIC_BYTES["prefill_c2"] if world == 1 else None,
+                         "peak_source": peaks["source"] + " burst", "per": "GPU"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
-                    "ms_per_step": e2e_ms / args.steps},
+                    "ms_per_step": e2e_ms / args.steps, "bytes": "all ranks together"},
             "clocks": clocks, "gpu_launches": launches, "decode": decode, "project": project,
             "layer_chain": layer_chain,
         }
-        if prefill_sharded:
-            line["prefill_sharded"] = prefill_sharded
+        if prefill_replicas:
+            line["prefill_replicas"] = prefill_replicas
+        if checks:
+            line["checks"] = checks
         if cpu_baseline:
             line["cpu_baseline"] = cpu_baseline
         json_out.write(json.dumps(line) + "\n")

@@ -37,9 +37,11 @@ extern "C" {
 const char* tc_last_error(void);
 int tc_abi_version(void);
 
-/* Reads and clears the per-device kernel status word (synchronises the device). *status is 0
- * when no kernel wait expired since the previous call. Has no counterpart in the reference,
- * whose kernels have no bounded waits. */
+/* Reads and clears the kernel status of a device (synchronises the device). *status is 0 when no
+ * kernel wait expired since the previous call, else the first code found. It covers the library's
+ * per-device block (if a decode call created it) and the status word of tc_decode_forward_out_static;
+ * it never allocates: a device on which no call has been made yet reports 0. Has no counterpart in
+ * the reference, whose kernels have no bounded waits. */
 int tc_device_status(int device, int32_t* status);
 
 /* ---------------------------------------------------------------------------------- prefill
@@ -148,11 +150,17 @@ int tc_decode_forward_out_flags(int device, void* stream, const void* q, void* k
  * maps on the stack and clears the tickets with cudaMemsetAsync on `stream`. The first call on a
  * device looks up the array's device address (cudaGetSymbolAddress, once per device): make that first
  * call before any stream capture. All calls on a device share the one array, which keeps the previous
- * call's partials: two calls that overlap on the GPU (different streams) race; serialise them. */
+ * call's partials: two calls that overlap on the GPU (different streams) race; serialise them.
+ * A bounded wait that expires inside a static call is recorded in a status word of the same array (not in
+ * the per-device block, which such a caller never creates). The word keeps the first code until it is read:
+ * tc_device_status reads and clears it without allocating, and tc_decode_static_status_word gives its device
+ * address (also without allocating; it does the same first-call address look-up) to callers that prefer to
+ * copy the 4 bytes on a stream of their own. */
 int tc_decode_forward_out_static(int device, void* stream, const void* q, void* kcache, void* vcache,
                                  const void* knew, const void* vnew, const int32_t* old_lengths, void* out,
                                  float* lse, int64_t batch, int64_t capacity, int64_t kv_heads, int64_t num_splits,
                                  int64_t mapping, int append);
+int tc_decode_static_status_word(int device, int32_t** word);
 
 /* KV-sequence-sharded variant for multi-GPU decode; no counterpart in the reference (it has no
  * distributed path). The caches hold global rows [kv_shard_start, kv_shard_start + capacity) of each
@@ -219,7 +227,9 @@ int tc_decode_rope_forward_out(int device, void* stream, const void* q, void* kc
  * store and its remote read. Every rank ends with the full result in out (BF16 [B,1,Hq,128]) and lse
  * (fp32 [B,Hq]). peer_blocks[r] is rank r's exchange block as mapped into this process
  * (peer_blocks[rank] is this rank's own block). All ranks must make the same sequence of calls with
- * the same batch, kv_heads and world on the same blocks. splits * Hkv * B CTAs must be resident at
+ * the same batch, kv_heads and world on the same blocks. peer_block_size is the size in bytes every one of
+ * those blocks was created with; a call whose (batch, kv_heads, world) needs more than that is rejected,
+ * because its stores would leave the blocks on the other GPUs. splits * Hkv * B CTAs must be resident at
  * once (rejected otherwise). Plain stores only; no collective library call is involved.
  *
  * Exchange blocks: tc_peer_block_bytes gives the size for (batch, kv_heads, world);
@@ -230,7 +240,8 @@ int tc_decode_exchange_out(int device, void* stream, const void* q, void* kcache
                            const void* vnew, const int32_t* old_lengths, void* out, float* lse, float* workspace_o,
                            int64_t workspace_o_elems, float* workspace_lse, int64_t workspace_lse_elems, int64_t batch,
                            int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping, int append,
-                           int64_t kv_shard_start, int64_t world, int64_t rank, void* const* peer_blocks);
+                           int64_t kv_shard_start, int64_t world, int64_t rank, void* const* peer_blocks,
+                           int64_t peer_block_size);
 int tc_peer_block_bytes(int64_t batch, int64_t kv_heads, int64_t world, int64_t* bytes);
 int tc_peer_block_create(int device, int64_t bytes, void** block, unsigned char* handle64);
 int tc_peer_block_open(int device, const unsigned char* handle64, void** block);

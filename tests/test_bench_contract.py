@@ -28,10 +28,29 @@ def test_reference_arm_prints_one_line_on_rank_zero_only():
     assert line["cpu_baseline"]["value"] == line["value"] and "sample" in line["cpu_baseline"]
     assert line["e2e"] == {"value": line["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert "workload" in line["config"] and "model" not in line["config"]
+    sys.path.insert(0, str(ROOT))
+    import bench
+
+    assert line["config"] == bench.bench_config(1)  # both arms state one and the same workload
+    assert "whole config-2 prefill batch" in line["cpu_baseline"]["sample"]
 
     other = run_bench("--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "0",
                       env={"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1"})
     assert other.returncode == 0 and other.stdout.strip() == ""
+
+
+def test_benchmark_inputs_are_the_oracles_inputs():
+    """The package's generator (what the GPU arm draws from) and the oracle's give the same bits."""
+    import torch
+
+    from oracle import attention as oracle
+    from tilecadence_b200.synthetic import seeded_normal
+
+    shapes = ((1, 64, 32, 128), (1, 64, 8, 128), (3, 5))
+    for ours, theirs in zip(seeded_normal(1, *shapes), oracle.seeded_normal(1, *shapes)):
+        assert ours.dtype == torch.bfloat16 and torch.equal(ours.view(torch.int16), theirs.view(torch.int16))
+    half = seeded_normal(0, (4, 4), dtype=torch.float16)[0]
+    assert torch.equal(half, oracle.seeded_normal(0, (4, 4), dtype=torch.float16)[0])
 
 
 def test_gpu_arm_fails_loudly_without_a_device():

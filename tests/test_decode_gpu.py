@@ -359,7 +359,10 @@ def test_missing_rank_ends_the_exchange_with_a_status(ops, gpu_device):
         lse = torch.empty((batch, 32, 1), device=device, dtype=torch.float32)
         spec = ops.workspace_spec(dq, dk, dold, 0, 1, True)
         ws = [torch.empty(n, device=device, dtype=torch.float32) for n in spec[1:3]]
-        ops.exchange_out(dq, dk, dv, dkn, dvn, dold, out, lse, *ws, 0, 1, True, 0, 0, table)
+        # blocks smaller than this call's geometry needs are refused before anything is launched
+        with pytest.raises(RuntimeError, match="too small"):
+            ops.exchange_out(dq, dk, dv, dkn, dvn, dold, out, lse, *ws, 0, 1, True, 0, 0, table, size.value - 256)
+        ops.exchange_out(dq, dk, dv, dkn, dvn, dold, out, lse, *ws, 0, 1, True, 0, 0, table, size.value)
         torch.cuda.synchronize()
         assert library.device_status(device.index) == 5   # "a rank never delivered"
         assert library.device_status(device.index) == 0   # reading clears it

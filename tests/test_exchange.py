@@ -67,6 +67,16 @@ def test_reference_plan_fields_are_enough_for_the_verifier():
         exchange.verify(exchange.build_contract(arm), golden["plan"])
 
 
+def test_verifier_refuses_a_plan_that_recomputes_probabilities():
+    """``P recomputation is excluded`` (reference exchange.py:186): a ``recover_p`` event voids the certificate."""
+    plan = deepcopy(GOLDEN["arms"]["one"]["plan"])
+    extra = deepcopy(plan["events"][-1])
+    extra.update(id="recover_P0#0", kind="recover_p", start=extra["end"], end=extra["end"] + 1)
+    plan["events"].append(extra)
+    with pytest.raises(ValueError, match="P recomputation is excluded"):
+        exchange.verify(exchange.build_contract("one"), plan)
+
+
 @pytest.fixture(scope="module")
 def two_checkpoints():
     problem = exchange.build_problem("relocated_two_p")

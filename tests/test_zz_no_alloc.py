@@ -8,6 +8,9 @@ so their results are compared with the tolerances of the decode parity tests (O 
 1e-3 relative, caches bit-exact). Two consecutive steps are run because the built-in array keeps the
 first call's contents when the second call starts.
 
+The status word of a static call sits in that same array; ``tc_device_status`` and
+``tc_decode_static_status_word`` are the two documented ways to reach it, and neither allocates.
+
 Collected last so that a run stopping at the first failure has already run every other test.
 """
 import ctypes
@@ -77,6 +80,54 @@ def test_static_entry_matches_regular_entry_on_two_steps(library, gpu_device, ba
     assert library.device_status(device.index) == 0
 
 
+def static_status_word(library, device):
+    word = ctypes.c_void_p()
+    library.call("tc_decode_static_status_word", device.index, ctypes.byref(word))
+    assert word.value
+    return word
+
+
+def test_static_status_word_is_what_device_status_reads(library, gpu_device):
+    """A code left in the static array's status word (here put there by the test with a 4-byte copy, standing
+    in for a kernel whose bounded wait ran out) comes back from tc_device_status exactly once."""
+    device = gpu_device
+    cudart = ctypes.CDLL("libcudart.so.12")
+    cudart.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+    with torch.cuda.device(device):
+        word = static_status_word(library, device)
+        assert library.device_status(device.index) == 0
+        code = ctypes.c_int32(2)  # what the kernel stores when a consumer's wait for a K/V stage expires
+        assert cudart.cudaMemcpy(word, ctypes.byref(code), 4, 1) == 0  # host -> device
+        assert library.device_status(device.index) == 2
+        assert library.device_status(device.index) == 0  # reading cleared it
+        seen = ctypes.c_int32(-1)
+        assert cudart.cudaMemcpy(ctypes.byref(seen), word, 4, 2) == 0  # device -> host
+        assert seen.value == 0
+
+
+def test_static_entry_and_its_status_readers_allocate_nothing(library, gpu_device):
+    """Free device memory is the same before and after a warmed-up static call and both status readers."""
+    device = gpu_device
+    batch, capacity = 2, 2048
+    prefix_k, prefix_v = oracle.seeded_normal(5, (batch, capacity, 8, 128), (batch, capacity, 8, 128))
+    q, knew, vnew = oracle.seeded_normal(6, (batch, 1, 32, 128), (batch, 1, 8, 128), (batch, 1, 8, 128))
+    dk, dv, dq, dkn, dvn = (t.to(device) for t in (prefix_k, prefix_v, q, knew, vnew))
+    old = torch.tensor([1500, 900], dtype=torch.int32, device=device)
+    out = torch.empty_like(dq)
+    lse = torch.empty((batch, 32, 1), device=device, dtype=torch.float32)
+    call_static(library, dq, dk, dv, dkn, dvn, old, out, lse)  # first call: address look-up, kernel load
+    static_status_word(library, device)
+    library.device_status(device.index)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(device)
+    call_static(library, dq, dk, dv, dkn, dvn, old + 1, out, lse)
+    static_status_word(library, device)
+    assert library.device_status(device.index) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(device)
+    assert free_after == free_before
+
+
 def test_static_entry_rejects_sizes_beyond_its_scratch(library, gpu_device):
     device = gpu_device
     batch = 5  # 5 * 32 = 160 rows > 128
@@ -92,3 +143,8 @@ def test_static_entry_rejects_sizes_beyond_its_scratch(library, gpu_device):
     with pytest.raises(RuntimeError, match="splits exceed the built-in scratch"):
         call_static(library, q[:1], cache_k[:1], cache_v[:1], new_k[:1], new_v[:1], old[:1], out[:1], lse[:1],
                     num_splits=64)
+    misaligned = torch.empty(33, device=device, dtype=torch.float32).view(torch.uint8)[1:129].view(torch.uint8)
+    with pytest.raises(RuntimeError, match="misaligned old_lengths or LSE"):
+        library.call("tc_decode_forward_out_static", device.index, stream_of(q), pointer(q[:1]), pointer(cache_k[:1]),
+                     pointer(cache_v[:1]), pointer(new_k[:1]), pointer(new_v[:1]), pointer(old[:1]), pointer(out[:1]),
+                     ctypes.c_void_p(misaligned.data_ptr()), 1, 128, 8, 0, 1, 1)

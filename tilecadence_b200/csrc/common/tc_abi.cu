@@ -14,12 +14,21 @@ int tc_device_status(int device, int32_t* status) {
     if (result != TC_OK) return result;
     tc::DeviceGuard guard(device);
     TC_CUDA(guard.status);
-    tc::DeviceScratch scratch;
-    result = tc::device_scratch(device, &scratch);
-    if (result != TC_OK) return result;
+    // Every status word that exists for this device: the per-device block's (if a decode call ever created
+    // the block; reading the status never allocates it) and words registered by allocation-free entries.
+    int32_t* words[8];
+    const int count = tc::known_status_words(device, words, 8);
+    *status = 0;
+    if (count == 0) return TC_OK;
     TC_CUDA(cudaDeviceSynchronize());
-    TC_CUDA(cudaMemcpy(status, scratch.status, sizeof(int32_t), cudaMemcpyDeviceToHost));
-    if (*status != 0) TC_CUDA(cudaMemset(scratch.status, 0, sizeof(int32_t)));
+    for (int i = 0; i < count; ++i) {
+        int32_t value = 0;
+        TC_CUDA(cudaMemcpy(&value, words[i], sizeof(int32_t), cudaMemcpyDeviceToHost));
+        if (value != 0) {
+            TC_CUDA(cudaMemset(words[i], 0, sizeof(int32_t)));
+            if (*status == 0) *status = value;
+        }
+    }
     return TC_OK;
 }
 

@@ -147,12 +147,21 @@ struct DeviceScratch {
     int32_t* status = nullptr;
 };
 
+struct ScratchRegistry {
+    std::mutex lock;
+    std::unordered_map<int, DeviceScratch> blocks;               // allocated on a device's first decode call
+    std::unordered_multimap<int, int32_t*> extra_status_words;   // status words that live elsewhere
+};
+inline ScratchRegistry& scratch_registry() {
+    static ScratchRegistry registry;
+    return registry;
+}
+
 inline int device_scratch(int device, DeviceScratch* out) {
-    static std::mutex lock;
-    static std::unordered_map<int, DeviceScratch> cache;
-    std::lock_guard<std::mutex> guard(lock);
-    auto found = cache.find(device);
-    if (found == cache.end()) {
+    ScratchRegistry& registry = scratch_registry();
+    std::lock_guard<std::mutex> guard(registry.lock);
+    auto found = registry.blocks.find(device);
+    if (found == registry.blocks.end()) {
         int32_t* block = nullptr;
         TC_CUDA(cudaMalloc(&block, sizeof(int32_t) * (kTicketSlots + 64)));
         TC_CUDA(cudaMemset(block, 0, sizeof(int32_t) * (kTicketSlots + 64)));
@@ -160,10 +169,34 @@ inline int device_scratch(int device, DeviceScratch* out) {
         DeviceScratch fresh;
         fresh.tickets = block;
         fresh.status = block + kTicketSlots;
-        found = cache.emplace(device, fresh).first;
+        found = registry.blocks.emplace(device, fresh).first;
     }
     *out = found->second;
     return TC_OK;
+}
+
+// A translation unit whose kernels report into a status word outside the per-device block (a word
+// inside a file-scope device array, for one) announces its device address here once per device, so
+// that tc_device_status finds it. Nothing is allocated on the device.
+inline void register_status_word(int device, int32_t* word) {
+    ScratchRegistry& registry = scratch_registry();
+    std::lock_guard<std::mutex> guard(registry.lock);
+    auto range = registry.extra_status_words.equal_range(device);
+    for (auto it = range.first; it != range.second; ++it)
+        if (it->second == word) return;
+    registry.extra_status_words.emplace(device, word);
+}
+
+// Device addresses of every status word that exists for `device` right now; never creates the block.
+inline int known_status_words(int device, int32_t** words, int capacity) {
+    ScratchRegistry& registry = scratch_registry();
+    std::lock_guard<std::mutex> guard(registry.lock);
+    int count = 0;
+    auto block = registry.blocks.find(device);
+    if (block != registry.blocks.end() && count < capacity) words[count++] = block->second.status;
+    auto range = registry.extra_status_words.equal_range(device);
+    for (auto it = range.first; it != range.second && count < capacity; ++it) words[count++] = it->second;
+    return count;
 }
 
 inline bool ranges_overlap(const void* a, size_t a_bytes, const void* b, size_t b_bytes) {

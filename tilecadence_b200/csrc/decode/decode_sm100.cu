@@ -944,7 +944,8 @@ constexpr int kStaticMaxSplits = 32;
 constexpr size_t kStaticOFloats = size_t(kStaticMaxSplits) * kStaticMaxRows * kDim;
 constexpr size_t kStaticLseFloats = size_t(kStaticMaxSplits) * kStaticMaxRows;
 constexpr size_t kStaticTicketWords = kStaticMaxRows / kGroup;
-constexpr size_t kStaticWords = kStaticOFloats + kStaticLseFloats + kStaticTicketWords + 64;
+constexpr size_t kStaticStatusWord = kStaticOFloats + kStaticLseFloats + kStaticTicketWords;
+constexpr size_t kStaticWords = kStaticStatusWord + 64;
 static __device__ __align__(256) float g_static_scratch[kStaticWords];  // 2.1 MiB per GPU that loads the library
 
 int static_scratch_address(int device, float** address) {
@@ -957,6 +958,8 @@ int static_scratch_address(int device, float** address) {
         TC_CUDA(cudaGetSymbolAddress(&pointer, g_static_scratch));
         TC_REQUIRE(pointer != nullptr, "cudaGetSymbolAddress returned a null scratch address");
         found = known.emplace(device, static_cast<float*>(pointer)).first;
+        // The kernel status word of static calls lives in the array too: tell tc_device_status where.
+        tc::register_status_word(device, reinterpret_cast<int32_t*>(found->second + kStaticStatusWord));
     }
     *address = found->second;
     return TC_OK;
@@ -988,6 +991,8 @@ int decode_static(int device, void* stream, const void* q, void* kcache, void* v
                        "All nonempty ABI tensor allocations must be disjoint");
     for (int i = 0; i < 7; ++i)
         TC_REQUIRE(reinterpret_cast<uintptr_t>(pointers[i]) % 16 == 0 || i == 5, "16-byte aligned storage required");
+    TC_REQUIRE(reinterpret_cast<uintptr_t>(old_lengths) % 4 == 0 && reinterpret_cast<uintptr_t>(lse) % 4 == 0,
+               "misaligned old_lengths or LSE");
 
     tc::DeviceGuard guard(device);
     TC_CUDA(guard.status);
@@ -1000,7 +1005,8 @@ int decode_static(int device, void* stream, const void* q, void* kcache, void* v
     if ((status = tc::make_rows_map(&vmap, vcache, false, kv_heads, capacity, batch, kDim, kv_heads * kDim,
                                     capacity * kv_heads * kDim, kTileN, 2)) != TC_OK) return status;
     // The tickets must start at zero; the kernel leaves them at zero, but a launch that was cut short
-    // must not poison the next one, so they are cleared on the stream every time.
+    // must not poison the next one, so they are cleared on the stream every time. The status word next
+    // to them is NOT cleared here: it keeps the first non-zero code until tc_device_status reads it.
     TC_CUDA(cudaMemsetAsync(tickets, 0, kStaticTicketWords * sizeof(int32_t), static_cast<cudaStream_t>(stream)));
 
     DecodeParams p{};
@@ -1016,7 +1022,7 @@ int decode_static(int device, void* stream, const void* q, void* kcache, void* v
     p.ws_o = scratch;
     p.ws_lse = scratch + kStaticOFloats;
     p.tickets = tickets;
-    p.status = tickets + kStaticTicketWords;
+    p.status = reinterpret_cast<int32_t*>(scratch + kStaticStatusWord);
     p.batch = int(batch);
     p.capacity = int(capacity);
     p.kv_heads = int(kv_heads);
@@ -1124,6 +1130,19 @@ int tc_decode_forward_out_static(int device, void* stream, const void* q, void* 
                          kv_heads, num_splits, mapping, append);
 }
 
+int tc_decode_static_status_word(int device, int32_t** word) {
+    TC_REQUIRE(word, "null output");
+    tc::DeviceInfo info;
+    int status = tc::require_sm100(device, &info);
+    if (status != TC_OK) return status;
+    tc::DeviceGuard guard(device);
+    TC_CUDA(guard.status);
+    float* scratch = nullptr;
+    if ((status = static_scratch_address(device, &scratch)) != TC_OK) return status;
+    *word = reinterpret_cast<int32_t*>(scratch + kStaticStatusWord);
+    return TC_OK;
+}
+
 int tc_decode_indexed_forward_out(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
                                   const void* vnew, const int32_t* old_lengths, void* out, float* lse,
                                   float* workspace_o, int64_t workspace_o_elems, float* workspace_lse,
@@ -1219,8 +1238,17 @@ int tc_decode_exchange_out(int device, void* stream, const void* q, void* kcache
                            const void* vnew, const int32_t* old_lengths, void* out, float* lse, float* workspace_o,
                            int64_t workspace_o_elems, float* workspace_lse, int64_t workspace_lse_elems, int64_t batch,
                            int64_t capacity, int64_t kv_heads, int64_t num_splits, int64_t mapping, int append,
-                           int64_t kv_shard_start, int64_t world, int64_t rank, void* const* peer_blocks) {
+                           int64_t kv_shard_start, int64_t world, int64_t rank, void* const* peer_blocks,
+                           int64_t peer_block_size) {
     TC_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, "need 1 <= world <= 8, 0 <= rank < world");
+    // The kernel derives every slot and epoch offset from (batch, kv_heads, world) and stores into every
+    // rank's block: a block made for a smaller geometry would take stores past its end, on another GPU.
+    TC_REQUIRE(batch >= 1 && batch <= 65535 && kv_heads >= 1 && kv_heads <= 8, "batch or kv_heads out of range");
+    TC_REQUIRE(peer_block_size >= int64_t(peer_block_bytes(int(world), int(batch * kv_heads))),
+               "exchange blocks of %lld bytes are too small for batch %lld, %lld KV heads, %lld ranks (need %lld)",
+               static_cast<long long>(peer_block_size), static_cast<long long>(batch),
+               static_cast<long long>(kv_heads), static_cast<long long>(world),
+               static_cast<long long>(peer_block_bytes(int(world), int(batch * kv_heads))));
     const PeerArgs peer{peer_blocks, int(world), int(rank)};
     return decode_common(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, nullptr, workspace_o,
                          workspace_o_elems, workspace_lse, workspace_lse_elems, batch, capacity, kv_heads, num_splits,

@@ -725,8 +725,11 @@ int prefill_common(int device, void* stream, const void* q, const int64_t q_stri
     cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
     if (key_splits == 2) {
         uint8_t* base = static_cast<uint8_t*>(workspace);
-        for (const void* pointer : {q, k, v, static_cast<const void*>(out), static_cast<const void*>(lse)})
-            TC_REQUIRE(!tc::ranges_overlap(workspace, size_t(split.total), pointer, 1), "workspace aliases a tensor");
+        const void* tensors[5] = {q, k, v, out, lse};
+        const size_t tensor_bytes[5] = {input_bytes[0], input_bytes[1], input_bytes[2], out_bytes, lse_bytes};
+        for (int i = 0; i < 5; ++i)
+            TC_REQUIRE(!tc::ranges_overlap(workspace, size_t(split.total), tensors[i], tensor_bytes[i]),
+                       "workspace aliases a tensor");
         p.tickets = reinterpret_cast<int32_t*>(base);
         p.part_o = reinterpret_cast<float4*>(base + split.o_offset);
         p.part_lse = reinterpret_cast<float*>(base + split.lse_offset);

@@ -207,7 +207,8 @@ class Library:
         "tc_decode_exchange_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, *[ctypes.c_int64] * 3,
-            ctypes.POINTER(ctypes.c_void_p))),
+            ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64)),
+        "tc_decode_static_status_word": (ctypes.c_int, (ctypes.c_int, ctypes.POINTER(ctypes.c_void_p))),
         "tc_peer_block_bytes": (ctypes.c_int, (*[ctypes.c_int64] * 3, ctypes.POINTER(ctypes.c_int64))),
         "tc_peer_block_create": (ctypes.c_int, (ctypes.c_int, ctypes.c_int64, ctypes.POINTER(ctypes.c_void_p),
                                                 ctypes.c_char_p)),
@@ -599,9 +600,10 @@ class DecodeOps:
         return list(spec)
 
     def exchange_out(self, q, kcache, vcache, knew, vnew, old_lengths, out, lse, workspace_o, workspace_lse,
-                     num_splits, mapping, append, kv_shard_start, rank, peer_blocks):
+                     num_splits, mapping, append, kv_shard_start, rank, peer_blocks, peer_block_bytes):
         """Sharded decode step with the cross-GPU merge inside the launch; ``peer_blocks`` is the
-        ctypes array of every rank's exchange block (see :class:`tilecadence_b200.sharding.PeerBlocks`)."""
+        ctypes array of every rank's exchange block (see :class:`tilecadence_b200.sharding.PeerBlocks`)
+        and ``peer_block_bytes`` the size each of them was created with."""
         self._check_call(q, kcache, vcache, knew, vnew, old_lengths, workspace_o, workspace_lse)
         self._check_out(q, out, lse)
         self.library.call(
@@ -609,7 +611,7 @@ class DecodeOps:
             _pointer(knew), _pointer(vnew), _pointer(old_lengths), _pointer(out), _pointer(lse),
             _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse), workspace_lse.numel(),
             q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping), int(bool(append)),
-            int(kv_shard_start), len(peer_blocks), int(rank), peer_blocks)
+            int(kv_shard_start), len(peer_blocks), int(rank), peer_blocks, int(peer_block_bytes))
 
     def combine_partials(self, partial_o, partial_lse, out, lse):
         """Merge partial_o [parts, rows, 128] / partial_lse [parts, rows] (fp32; the part dimension may be

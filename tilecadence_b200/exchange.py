@@ -169,6 +169,7 @@ def verify(contract, result):
     # -- what every arm shares: the action set, the two Q reads, the original Q copy
     score_actions = {event["id"] for event in events.values() if event["kind"] == "qk"}
     check(score_actions == {"qk_0#0", "qk_1#0"}, "exactly one required QK per tile")
+    check(not any(event["kind"] == "recover_p" for event in events.values()), "P recomputation is excluded")
     allowed_repeats = {"load_Q#1"} if arm == "retain" else {"load_Q#1", "copy_Q#1"}
     check(all(identity.endswith("#0") or identity in allowed_repeats for identity in events),
           "unexpected repeated action outside the common graph")

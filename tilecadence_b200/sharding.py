@@ -155,7 +155,7 @@ class ShardedDecode:
             self.workspace = tuple(torch.empty(n, device=q.device, dtype=torch.float32) for n in spec[1:3])
         if self.peers is not None:
             self.ops.exchange_out(q, kcache, vcache, knew, vnew, old_lengths, out, lse, *self.workspace, num_splits,
-                                  mapping, True, self.shard_start, self.rank, self.peers.table)
+                                  mapping, True, self.shard_start, self.rank, self.peers.table, self.peers.bytes)
             return
         partial_o, partial_lse = self.views(self.packed)
         self.ops.partial_out(q, kcache, vcache, knew, vnew, old_lengths, partial_o, partial_lse, *self.workspace,
