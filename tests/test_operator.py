@@ -40,6 +40,29 @@ def test_emitted_config_carries_the_solved_offsets(tmp_path, phase):
         replay(HANDOFFS[phase], collided)
 
 
+def test_emitted_prefill_config_carries_the_tensor_memory_map(tmp_path: Path):
+    """The prefill kernel's tensor-memory columns come from the planner the way its LSE offsets do."""
+    import json
+
+    from tilecadence_b200.operator import TMEM_ALLOCATION, TMEM_COLUMNS
+    from tilecadence_b200.placement import TMEM_MAPS, replay_tmem
+
+    emit("prefill", tmp_path / "prefill")
+    macros = defines_of((tmp_path / "prefill" / "config.cuh").read_text())
+    solved = json.loads((tmp_path / "prefill" / "tmem_placement.json").read_text())
+    columns = {}
+    for region, macro in TMEM_COLUMNS["prefill"].items():
+        columns[region] = solved["regions"][region]["offset_columns"]
+        assert macros[macro] == columns[region]
+    assert macros[TMEM_ALLOCATION["prefill"]] == solved["allocation_columns"] == 512
+    replay_tmem(TMEM_MAPS["prefill"], columns)
+    source = (tmp_path / "prefill" / "prefill_sm100.cu").read_text()
+    for macro in list(TMEM_COLUMNS["prefill"].values()) + [TMEM_ALLOCATION["prefill"]]:
+        assert macro in source  # the kernel reads its map from the emitted macros, not from constants of its own
+    emit("decode", tmp_path / "decode")
+    assert not (tmp_path / "decode" / "tmem_placement.json").exists()  # the decode kernel uses no tensor memory
+
+
 def test_emit_is_self_contained_and_never_overwrites(tmp_path: Path):
     target = tmp_path / "decode"
     emit("decode", target)

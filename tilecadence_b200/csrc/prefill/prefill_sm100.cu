@@ -48,11 +48,40 @@ constexpr int kSoftmaxThreads = 128;
 constexpr int kThreads = 3 * kSoftmaxThreads;   // two softmax warpgroups + one data/MMA warpgroup
 constexpr int kSoftmaxRegisters = 216, kDataRegisters = 72;  // 256*216 + 128*72 = 64512 <= 65536
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
-constexpr uint32_t kTmemColumns = 512;
-constexpr uint32_t kSColumn = 0, kPColumn = 128, kOColumn = 256;  // S (shared) | P0 P1 | O0 O1
+// Tensor-memory map, solved by the planner (placement.TMEM_MAPS["prefill"]) and emitted into config.cuh.
+constexpr uint32_t kTmemColumns = PREFILL_TMEM_ALLOCATION_COLUMNS;
+constexpr uint32_t kSColumns = 128, kPColumns = 64, kOColumns = 128;  // FP32 scores, BF16 pairs, FP32 output
+__host__ __device__ constexpr uint32_t s_column(int h) { return h == 0 ? PREFILL_TMEM_S_HEAD0_COLUMN : PREFILL_TMEM_S_HEAD1_COLUMN; }
+__host__ __device__ constexpr uint32_t p_column(int h) { return h == 0 ? PREFILL_TMEM_P_HEAD0_COLUMN : PREFILL_TMEM_P_HEAD1_COLUMN; }
+__host__ __device__ constexpr uint32_t o_column(int h) { return h == 0 ? PREFILL_TMEM_O_HEAD0_COLUMN : PREFILL_TMEM_O_HEAD1_COLUMN; }
+constexpr bool columns_disjoint(uint32_t a, uint32_t a_columns, uint32_t b, uint32_t b_columns) {
+    return a + a_columns <= b || b + b_columns <= a;
+}
 constexpr float kRescaleThreshold = 8.f;      // log2 units: P stays below 2^8
 
 static_assert(kBlockM == 128 && kBlockN == 128 && PREFILL_GROUP_HEADS == 2 && kStages == 2, "fixed tile schedule");
+static_assert(kTmemColumns >= 32 && kTmemColumns <= 512 && (kTmemColumns & (kTmemColumns - 1)) == 0,
+              "a tensor-memory allocation is a power of two between 32 and 512 columns");
+static_assert(s_column(0) % 32 == 0 && s_column(1) % 32 == 0 && o_column(0) % 32 == 0 && o_column(1) % 32 == 0 &&
+                  p_column(0) % 16 == 0 && p_column(1) % 16 == 0, "tile column alignment");
+static_assert(s_column(0) + kSColumns <= kTmemColumns && s_column(1) + kSColumns <= kTmemColumns &&
+                  p_column(0) + kPColumns <= kTmemColumns && p_column(1) + kPColumns <= kTmemColumns &&
+                  o_column(0) + kOColumns <= kTmemColumns && o_column(1) + kOColumns <= kTmemColumns,
+              "tiles must lie inside the allocation");
+// The score buffers of the two heads are never alive together (the kernel hands them over 0,1,0,1,...), so
+// they may coincide; if they do not coincide they must not partly overlap. Everything else is alive together.
+static_assert(s_column(0) == s_column(1) || columns_disjoint(s_column(0), kSColumns, s_column(1), kSColumns),
+              "score buffers are either one shared buffer or disjoint");
+static_assert(columns_disjoint(p_column(0), kPColumns, p_column(1), kPColumns) &&
+                  columns_disjoint(o_column(0), kOColumns, o_column(1), kOColumns),
+              "per-head probability and output tiles must not overlap");
+static_assert(columns_disjoint(s_column(0), kSColumns, p_column(0), kPColumns) && columns_disjoint(s_column(0), kSColumns, p_column(1), kPColumns) &&
+                  columns_disjoint(s_column(1), kSColumns, p_column(0), kPColumns) && columns_disjoint(s_column(1), kSColumns, p_column(1), kPColumns) &&
+                  columns_disjoint(s_column(0), kSColumns, o_column(0), kOColumns) && columns_disjoint(s_column(0), kSColumns, o_column(1), kOColumns) &&
+                  columns_disjoint(s_column(1), kSColumns, o_column(0), kOColumns) && columns_disjoint(s_column(1), kSColumns, o_column(1), kOColumns) &&
+                  columns_disjoint(p_column(0), kPColumns, o_column(0), kOColumns) && columns_disjoint(p_column(0), kPColumns, o_column(1), kOColumns) &&
+                  columns_disjoint(p_column(1), kPColumns, o_column(0), kOColumns) && columns_disjoint(p_column(1), kPColumns, o_column(1), kOColumns),
+              "score, probability and output tiles are alive together and must not overlap");
 static_assert(PREFILL_TERMINAL_K_OFFSET_BYTES == kKOffset && PREFILL_TERMINAL_K_BYTES == kTileBytes,
               "the planner's donor must be K stage 0");
 static_assert(PREFILL_LSE_HEAD0_OFFSET_BYTES % 128 == 0 && PREFILL_LSE_HEAD1_OFFSET_BYTES % 128 == 0, "alignment");
@@ -229,7 +258,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 // does not wait for any PV.
                 const uint32_t q_addr = tc::smem_u32(smem + kQOffset);
                 const uint32_t k_addr = tc::smem_u32(smem + kKOffset);
-                const uint32_t s_col = tmem + kSColumn;
                 ok = tc::mbar_wait(&bars->q_full, 0);
                 for (int it = 0; ok && it < n_tiles; ++it) {
                     if (!(ok = tc::mbar_wait(&bars->k_full[stage_of(it)], parity_of(it)))) break;
@@ -245,7 +273,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
 #pragma unroll
                         for (int ks = 0; ks < 8; ++ks) {
                             const uint32_t off = uint32_t(ks >> 2) * kHalfBytes + uint32_t(ks & 3) * 32;
-                            tc::umma_ss(s_col, tc::umma_desc_sw128(q_addr + h * kTileBytes + off, 16, 1024),
+                            tc::umma_ss(tmem + s_column(h), tc::umma_desc_sw128(q_addr + h * kTileBytes + off, 16, 1024),
                                         tc::umma_desc_sw128(kb + off, 16, 1024), idesc_qk, ks > 0);
                         }
                         tc::umma_commit(&bars->s_full[h]);
@@ -257,8 +285,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 // (row = key, 128 bytes per 64 d; the d halves 16 KiB apart, 8-key groups 1 KiB).
                 const int h = warp - (kMmaWarp + 1);
                 const uint32_t v_addr = tc::smem_u32(smem + kVOffset);
-                const uint32_t p_col = tmem + kPColumn + uint32_t(h) * 64;
-                const uint32_t o_col = tmem + kOColumn + uint32_t(h) * 128;
+                const uint32_t p_col = tmem + p_column(h);
+                const uint32_t o_col = tmem + o_column(h);
                 auto issue_pv_half = [&](int it, int half) {
                     const uint32_t vb = v_addr + stage_of(it) * kTileBytes;
 #pragma unroll
@@ -293,9 +321,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         const int h = warp >> 2;                        // head slot
         const int row = threadIdx.x & (kSoftmaxThreads - 1);
         const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
-        const uint32_t s_tmem = tmem + lane_field + kSColumn;
-        const uint32_t p_tmem = tmem + lane_field + kPColumn + uint32_t(h) * 64;
-        const uint32_t o_tmem = tmem + lane_field + kOColumn + uint32_t(h) * 128;
+        const uint32_t s_tmem = tmem + lane_field + s_column(h);
+        const uint32_t p_tmem = tmem + lane_field + p_column(h);
+        const uint32_t o_tmem = tmem + lane_field + o_column(h);
         const int head = head0 + h;
         const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
         float m_used = -INFINITY, l = 0.f;

@@ -3,7 +3,9 @@
 Public surface and behaviour follow ``tilecadence/operator.py`` (``OFFSETS`` :13-18, ``emit`` :21-38,
 command line :41-46): the phase's handoff is solved, each region's byte offset replaces the value of
 one macro in that phase's ``config.cuh``, every other source file is copied unchanged, and the solver's
-answer is stored as ``placement.json``. An existing output directory is an error. What is written here
+answer is stored as ``placement.json``. For the prefill kernel the tensor-memory map is solved as well
+(``placement.solve_tmem``): the first column of every tile and the allocation size replace their macros
+in the same ``config.cuh`` and the answer is stored as ``tmem_placement.json``. An existing output directory is an error. What is written here
 is self-contained (kernel, PTX helpers, host plumbing, C-ABI header): it is exactly what
 :func:`tilecadence_b200.cuda_runtime.build_cuda` compiles.
 """
@@ -28,6 +30,20 @@ OFFSETS = {
         "row_lse": "AB_DECODE_LSE_OFFSET_BYTES",
     },
 }
+
+#: tensor-memory tile -> macro that carries its first column, per phase (no counterpart in the reference,
+#: whose kernels have no tensor memory). ``TMEM_ALLOCATION`` names the macro of the allocation size.
+TMEM_COLUMNS = {
+    "prefill": {
+        "score_head0": "PREFILL_TMEM_S_HEAD0_COLUMN",
+        "score_head1": "PREFILL_TMEM_S_HEAD1_COLUMN",
+        "probability_head0": "PREFILL_TMEM_P_HEAD0_COLUMN",
+        "probability_head1": "PREFILL_TMEM_P_HEAD1_COLUMN",
+        "output_head0": "PREFILL_TMEM_O_HEAD0_COLUMN",
+        "output_head1": "PREFILL_TMEM_O_HEAD1_COLUMN",
+    },
+}
+TMEM_ALLOCATION = {"prefill": "PREFILL_TMEM_ALLOCATION_COLUMNS"}
 
 CONFIG_NAME = "config.cuh"
 
@@ -59,6 +75,12 @@ def emit(phase: str, out: Path) -> dict:
     solved = _placement.solve(_placement.HANDOFFS[phase])
     sources = staged_sources(phase)
     values = {macro: int(solved["regions"][region]["offset_bytes"]) for region, macro in macros.items()}
+    tensor_memory = None
+    if phase in TMEM_COLUMNS:
+        tensor_memory = _placement.solve_tmem(_placement.TMEM_MAPS[phase])
+        for region, macro in TMEM_COLUMNS[phase].items():
+            values[macro] = int(tensor_memory["regions"][region]["offset_columns"])
+        values[TMEM_ALLOCATION[phase]] = int(tensor_memory["allocation_columns"])
     config = _with_macro_values(sources[CONFIG_NAME].read_text(encoding="utf-8"), values)
 
     target = Path(out)
@@ -70,6 +92,8 @@ def emit(phase: str, out: Path) -> dict:
         else:
             destination.write_bytes(source.read_bytes())
     (target / "placement.json").write_text(json.dumps(solved, indent=2) + "\n", encoding="utf-8")
+    if tensor_memory is not None:
+        (target / "tmem_placement.json").write_text(json.dumps(tensor_memory, indent=2) + "\n", encoding="utf-8")
     return solved
 
 

@@ -8,7 +8,13 @@ that no two regions that are alive together share a byte. ``solve`` returns the 
 dictionary (same keys, same ``schema`` string, same objective text) and ``replay`` raises the same
 ``ValueError`` messages, so emitted ``placement.json`` files are interchangeable.
 
-Two things differ. The donors describe the sm_100a kernels' shared-memory maps, not the reference's.
+Three things differ. The donors describe the sm_100a kernels' shared-memory maps, not the reference's.
+There is a second address space: tensor memory (TMEM), 512 columns of 128 lanes x 32 bits per SM, which
+holds the score, probability and output tiles of the tcgen05 contractions. A ``TmemMap`` declares those
+tiles as regions (columns, column alignment, live interval over the steps of the key loop's steady-state
+period, which is cyclic); ``solve_tmem`` packs them with the same rule as the byte tier (regions that are
+never alive together may share columns, which is how a probability tile comes to sit in a retired score
+buffer) and ``replay_tmem`` checks a column map from first principles.
 And the optimum is found by exhaustive search instead of OR-tools CP-SAT: any feasible packing can be
 slid towards the donor's start until every region rests against the donor's start or against a region
 that is alive with it, without raising the high-water mark or the first region's offset; such
@@ -156,6 +162,151 @@ def solve(handoff: Handoff) -> dict:
     }
 
 
+# ----------------------------------------------------------------------------------- tensor memory
+TMEM_SCHEMA = "b200-tmem-placement-v1"
+TMEM_OBJECTIVE = "Minimum column high-water, then first region offset"
+TMEM_COLUMNS = 512          # per SM: 128 lanes x 512 columns x 32 bits
+TMEM_MIN_ALLOCATION = 32    # tcgen05.alloc hands out a power of two of at least 32 columns
+
+
+@dataclass(frozen=True)
+class TmemRegion:
+    """A tile in tensor memory: ``columns`` 32-bit columns (all 128 lanes) at a multiple of
+    ``alignment_columns``, alive during steps [start, end) of the map's timeline. With a cyclic timeline
+    ``end`` may exceed the period: the region then stays alive into the next round of the loop."""
+
+    name: str
+    columns: int
+    alignment_columns: int
+    start: int
+    end: int
+
+
+@dataclass(frozen=True)
+class TmemMap:
+    """The tensor-memory tiles of one kernel. ``timeline`` names the steps; ``cyclic`` says that they are
+    the steady-state period of a software-pipelined loop, so that step len(timeline) is step 0 again."""
+
+    name: str
+    regions: tuple[TmemRegion, ...]
+    timeline: tuple[str, ...]
+    cyclic: bool = True
+    capacity_columns: int = TMEM_COLUMNS
+
+    def alive_together(self, first: TmemRegion, second: TmemRegion) -> bool:
+        shifts = (-len(self.timeline), 0, len(self.timeline)) if self.cyclic else (0,)
+        return any(first.start < second.end + shift and second.start + shift < first.end for shift in shifts)
+
+
+#: Tensor-memory tiles of the prefill kernel, one 128-row query tile of two heads per CTA. Steady state of
+#: the key loop, one period = one key tile of both heads:
+#:   step 0  the score MMA of head 0 fills a score buffer and head 0's softmax warpgroup pulls it
+#:   step 1  the same for head 1, while head 0 exponentiates
+#: A score buffer is dead as soon as it has been pulled into registers, so the two heads' buffers are never
+#: alive together and may share columns. A probability tile P (BF16 pairs: 64 columns for 128 keys) is written
+#: after the pull and read by the PV MMA until the head's next pull, and the output accumulators live through
+#: the whole loop: neither can share with anything. The solved map is S (shared) | P0 P1 | O0 O1 = all 512
+#: columns.
+_PREFILL_STEPS = ("score_and_pull_head0", "score_and_pull_head1")
+TMEM_MAPS = {
+    "prefill": TmemMap(
+        name="prefill_two_heads_per_cta",
+        regions=(TmemRegion("score_head0", 128, 32, start=0, end=1), TmemRegion("score_head1", 128, 32, start=1, end=2),
+                 TmemRegion("probability_head0", 64, 16, start=0, end=2),
+                 TmemRegion("probability_head1", 64, 16, start=0, end=2),
+                 TmemRegion("output_head0", 128, 32, start=0, end=2), TmemRegion("output_head1", 128, 32, start=0, end=2)),
+        timeline=_PREFILL_STEPS),
+    # Candidate layouts that the planner can price without a kernel being written for them.
+    # Two private score buffers with P stored over the first half of its own retired score buffer: the score
+    # MMA of a head's next tile then has to wait for that head's PV, but never for the other head's pull.
+    "prefill_private_scores": TmemMap(
+        name="prefill_private_score_buffers",
+        regions=(TmemRegion("score_head0", 128, 32, start=0, end=1), TmemRegion("probability_head0", 64, 16, start=1, end=4),
+                 TmemRegion("score_head1", 128, 32, start=2, end=3), TmemRegion("probability_head1", 64, 16, start=3, end=6),
+                 TmemRegion("output_head0", 128, 32, start=0, end=4), TmemRegion("output_head1", 128, 32, start=0, end=4)),
+        timeline=("score_head0", "exp_head0", "score_head1", "exp_head1")),
+    # One head per CTA, three score/probability buffers in rotation and one output accumulator.
+    "prefill_one_head": TmemMap(
+        name="prefill_one_head_three_buffers",
+        regions=(TmemRegion("score_a", 128, 32, start=0, end=1), TmemRegion("probability_a", 64, 16, start=1, end=3),
+                 TmemRegion("score_b", 128, 32, start=1, end=2), TmemRegion("probability_b", 64, 16, start=2, end=4),
+                 TmemRegion("score_c", 128, 32, start=2, end=3), TmemRegion("probability_c", 64, 16, start=0, end=2),
+                 TmemRegion("output", 128, 32, start=0, end=3)),
+        timeline=("tile_a", "tile_b", "tile_c")),
+}
+
+
+def replay_tmem(tmem_map: TmemMap, columns: dict[str, int]) -> None:
+    """Check a column map from first principles; raises ``ValueError`` on the first violated rule."""
+    period = len(tmem_map.timeline)
+    checked: list[TmemRegion] = []
+    for region in tmem_map.regions:
+        offset = columns[region.name]
+        in_time = 0 <= region.start < region.end and (region.end - region.start <= period if tmem_map.cyclic
+                                                      else region.end <= period) and region.start < period
+        in_space = offset >= 0 and region.columns > 0 and offset + region.columns <= tmem_map.capacity_columns
+        aligned = region.alignment_columns > 0 and offset % region.alignment_columns == 0
+        if not (in_time and in_space and aligned):
+            raise ValueError(f"Invalid time/column placement for {region.name}")
+        for earlier in checked:
+            clash = offset < columns[earlier.name] + earlier.columns and columns[earlier.name] < offset + region.columns
+            if clash and tmem_map.alive_together(region, earlier):
+                raise ValueError(f"Live column ranges overlap for {region.name} and {earlier.name}")
+        checked.append(region)
+
+
+def solve_tmem(tmem_map: TmemMap) -> dict:
+    """Optimal column map: least column high-water mark, ties broken by the first region's offset. Same
+    search as :func:`solve`: every order of lowest-free-fit placements."""
+    regions = tmem_map.regions
+    for region in regions:
+        if region.columns <= 0 or region.alignment_columns <= 0:
+            raise ValueError(f"Invalid size or alignment for {region.name}")
+    by_name = {region.name: region for region in regions}
+
+    def lowest_free(region, taken):
+        offset = 0
+        while True:
+            blockers = [taken[name] + by_name[name].columns for name in taken
+                        if offset < taken[name] + by_name[name].columns and taken[name] < offset + region.columns
+                        and tmem_map.alive_together(region, by_name[name])]
+            if not blockers:
+                return offset
+            step = region.alignment_columns
+            offset = (max(blockers) + step - 1) // step * step
+
+    def pack(order):
+        taken: dict[str, int] = {}
+        for region in order:
+            offset = lowest_free(region, taken)
+            if offset + region.columns > tmem_map.capacity_columns:
+                return None
+            taken[region.name] = offset
+        return taken
+
+    def rank(candidate):
+        return (max(candidate[r.name] + r.columns for r in regions), candidate[regions[0].name],
+                [candidate[r.name] for r in regions])
+
+    feasible = [packing for packing in map(pack, itertools.permutations(regions)) if packing is not None]
+    if not feasible:
+        raise ValueError(f"No tensor-memory placement within {tmem_map.capacity_columns} columns")
+    chosen = min(feasible, key=rank)
+    replay_tmem(tmem_map, chosen)
+    high_water = rank(chosen)[0]
+    allocation = TMEM_MIN_ALLOCATION
+    while allocation < high_water:
+        allocation *= 2
+    placed = {}
+    for region in regions:
+        record = asdict(region)
+        record["offset_columns"] = chosen[region.name]
+        placed[region.name] = record
+    return {"schema": TMEM_SCHEMA, "status": "OPTIMAL", "map": tmem_map.name, "capacity_columns": tmem_map.capacity_columns,
+            "regions": placed, "timeline": tmem_map.timeline, "cyclic": tmem_map.cyclic,
+            "high_water_columns": high_water, "allocation_columns": allocation, "objective": TMEM_OBJECTIVE}
+
+
 def main(argv=None):
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--out", required=True, type=Path, help="directory to create; receives <phase>.json")
@@ -166,6 +317,9 @@ def main(argv=None):
         text = json.dumps(solve(HANDOFFS[phase]), indent=2) + "\n"
         with (arguments.out / f"{phase}.json").open("x", encoding="utf-8") as stream:
             stream.write(text)
+        if phase in TMEM_MAPS:
+            with (arguments.out / f"{phase}.tmem.json").open("x", encoding="utf-8") as stream:
+                stream.write(json.dumps(solve_tmem(TMEM_MAPS[phase]), indent=2) + "\n")
 
 
 if __name__ == "__main__":
