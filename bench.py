@@ -506,8 +506,11 @@ def run_ours(args, rank, world, local_rank):
         for _ in range(sets):  # rotating cache sets: together larger than L2, so no step re-reads cached rows
             caches.append(tuple(torch.randn((cbatch, shard_len, HKV, DIM), generator=generator, device=device,
                                             dtype=torch.bfloat16) for _ in range(2)))
-        dq = torch.randn((cbatch, 1, HQ, DIM), generator=generator, device=device, dtype=torch.bfloat16)
-        dkn, dvn = (torch.randn((cbatch, 1, HKV, DIM), generator=generator, device=device, dtype=torch.bfloat16)
+        # The query and the new rows are the same on every rank (a sharded step replicates them); only the cache
+        # shards differ from rank to rank.
+        shared_draws = torch.Generator(device=device).manual_seed(case["seed"] + 7919)
+        dq = torch.randn((cbatch, 1, HQ, DIM), generator=shared_draws, device=device, dtype=torch.bfloat16)
+        dkn, dvn = (torch.randn((cbatch, 1, HKV, DIM), generator=shared_draws, device=device, dtype=torch.bfloat16)
                     for _ in range(2))
         old = torch.full((cbatch,), valid, dtype=torch.int32, device=device)
         dout = torch.empty_like(dq)

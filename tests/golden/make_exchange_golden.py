@@ -10,6 +10,16 @@ reference's ``model.lowering_trace`` (``tilecadence/model.py:406-494``) for the 
 plan, and stores plan, certificate and trace in ``exchange_golden.json``. It also stores the trace the
 reference computes for the hand-built nine-event sequence of its own unit test
 (``tests/test_exchange.py:17-59``).
+
+The plan is then handed to the REFERENCE's full ``model.replay`` (``tilecadence/model.py:1205-1355``)
+together with the reference's own problem for that arm (``exchange.build_problem``, the reference
+geometry), and what ``replay`` returns is stored as ``reference_replay``. ``replay`` compares a result's
+declarations with its problem's, so ``reference_form`` first swaps in the reference problem's texts
+(provenance, cost records, value layout descriptions) and the reference's complete source-feature
+record, which is a superset of what this planner reports. Everything the planner decides, that is the
+events with their order and port bindings, the copies with lifetimes and byte offsets, the objective, its
+features and bound, goes through unchanged, and the script stops if the reference recomputes any of
+them differently.
 """
 import importlib.util
 import json
@@ -57,6 +67,33 @@ def frontier_case():
     return provenance, {"copies": copies, "events": events}
 
 
+def reference_form(ref_model, ref_problem, result):
+    """``result`` with the reference problem's declarative texts; see the module docstring."""
+    from dataclasses import asdict
+
+    converted = json.loads(json.dumps(result))
+    converted["actions"] = converted["events"]
+    values = {v.name: v for v in ref_problem.values}
+    actions = {a["id"]: a for a in ref_problem.actions}
+    for copy in converted["copies"]:
+        if copy["workspace"]:
+            copy["layout"] = ref_model._workspace_value(actions[copy["producer"]]).layout
+        else:
+            copy["layout"] = values[copy["value"]].layout
+    converted["profiles"] = {key: asdict(cost) for key, cost in ref_problem.profiles.items()}
+    converted["provenance"] = dict(ref_problem.provenance)
+    converted["source_features"] = ref_model.source_feature_values(ref_problem, converted)
+    ordered = sorted(converted["events"], key=lambda e: (e["start"], e["id"]))
+    # decisions and their prices must come out of the reference's own arithmetic unchanged
+    assert converted["objective"] == ref_model.evaluate_objective(ref_problem, ordered, converted)
+    assert converted["objective_features"] == ref_model.objective_features(ref_problem, ordered, converted)
+    assert converted["lowering_trace"] == ref_model.lowering_trace(ref_problem, converted)
+    assert converted["objective_model"]["spec"] == ref_problem.objective_spec
+    assert all(converted["source_features"][key] == value for key, value in result["source_features"].items()
+               if key in converted["source_features"])
+    return converted
+
+
 def main():
     if len(sys.argv) != 2:
         sys.exit(f"usage: python {sys.argv[0]} /path/to/TileCadence")
@@ -66,10 +103,13 @@ def main():
         problem = exchange.build_problem(arm)
         result = model.solve(problem, max_time_seconds=2)
         plan = {"events": result["events"], "copies": result["copies"], "status": result["status"]}
+        replayed = ref_model.replay(ref_exchange.build_problem(arm), reference_form(ref_model, ref_exchange.build_problem(arm), result))
+        replayed.pop("note")
         golden["arms"][arm] = {
             "plan": plan,
             "reference_certificate": ref_exchange.verify(ref_exchange.build_contract(arm), result),
             "reference_trace": ref_model.lowering_trace(problem, result),
+            "reference_replay": replayed,
         }
     provenance, record = frontier_case()
     golden["frontier"] = {"provenance": provenance, "record": record,

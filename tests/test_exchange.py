@@ -61,6 +61,30 @@ def test_plans_are_deterministic_and_match_the_reference_verifier(solved):
     assert result["objective"] == 128 * len(result["events"]) + result["source_features"]["rf_kib_steps"]
 
 
+def test_plans_are_accepted_by_the_reference_replay(solved):
+    """The reference's full ``model.replay`` (model.py:1205-1355) accepted each of these plans for its own
+    problem of the arm and reported the quantities stored in the fixture; this package's replay reports
+    the same ones for the same plan."""
+    arm, problem, result = solved
+    theirs = GOLDEN["arms"][arm]["reference_replay"]
+    ours = result["replay"]
+    assert theirs["valid"] is True and ours["valid"] is True
+    for key in ("peak_bytes", "executions", "q_global_loads", "source_order_steps", "objective", "objective_unit",
+                "objective_features"):
+        assert ours[key] == theirs[key], key
+    assert theirs["pure_p_recoveries"] == 0 and theirs["recomputations"] == {} and theirs["control_storage_bytes"] == 0
+    without_scope = lambda certificate: {k: v for k, v in certificate.items() if k != "scope"}  # a free-text note
+    assert without_scope(theirs["residency_exchange_v78"]) == without_scope(ours["residency_certificate"])
+    assert theirs["output_states"] == result["output_states"]
+    # the fields the reference's replay reads beyond events and copies
+    assert set(result) >= {"profiles", "best_bound", "lexicographic_objective", "objective_features",
+                           "cp_source_features", "model_sha256", "optimality_certified", "actions"}
+    assert all({"profile_key", "profile_cost"} <= set(event) for event in result["events"])
+    assert result["best_bound"] <= result["objective"]
+    assert result["optimality_certified"] == (result["best_bound"] == result["objective"]) == (result["status"] == "OPTIMAL")
+    assert len(result["model_sha256"]) == 64
+
+
 def test_reference_plan_fields_are_enough_for_the_verifier():
     """The verifier needs nothing but events and copies: it accepts the stored golden plan as is."""
     for arm, golden in GOLDEN["arms"].items():
@@ -134,7 +158,9 @@ def test_lowering_keeps_checkpoint_barriers_separate_from_copy_acquire(two_check
         assert f"Element* {match[1]}=reinterpret_cast<Element*>(arena+{address});" in source
     waits = sum(row["wait_before_load"] for row in result["lowering_trace"])
     assert source.count("acquire_copies<") == waits == result["source_features"]["consumer_wait_count"]
-    assert source.count("release_shared_reads();") == result["source_features"]["release_barrier_count"]
+    assert source.count("release_shared_reads();") == sum(row["release_before_write"] for row in result["lowering_trace"])
+    assert result["source_features"]["release_barrier_count"] == sum(
+        row["release_before_write"] for row in result["lowering_trace"] if row["kind"] in ("copy_g2s", "normalize_store"))
 
 
 def test_replay_rejects_tampering(two_checkpoints):

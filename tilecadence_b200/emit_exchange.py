@@ -124,7 +124,7 @@ def source_for(problem, result, *, output_cache="default"):
 
     for event in events:
         kind = event["kind"]
-        consumed = [copies[identity] for identity in event["inputs"]]
+        consumed = [copies[identity] for identity in event["inputs"] if copies[identity]["tier"] != "gmem"]
         produced = [copies[identity] for identity in event["outputs"]]
         ins = [names[copy["id"]] for copy in consumed]
         outs = [names[copy["id"]] for copy in produced]

@@ -97,8 +97,9 @@ def build_problem(arm):
     objective = {
         "unit": "cost_ticks",
         "constant": 0,
-        "terms": [{"feature": "source_actions", "coefficient": 128},
-                  {"feature": "rf_kib_steps", "coefficient": 1}],
+        # the reference's spelling (exchange.py:47-55), so that serialised problems are interchangeable
+        "terms": [{"feature": "source_actions", "coefficient": 128, "match": {}},
+                  {"feature": "rf_payload_kib_steps", "coefficient": 1, "source": {"kind": "rf_kib_steps"}}],
         "provenance": {"scope": "Same uncalibrated action-count and RF liveness proxy for every arm"},
     }
     return model.build_problem(arena_slabs=contract["arena_slabs"], allow_probability_spill=True,

@@ -9,8 +9,10 @@ reads and the 4 KiB slab every shared copy occupies.
 
 What is kept from the reference, because other modules and the tests speak this vocabulary:
 action and copy identities (``qk_0#0``, ``stats_1#0:out3``, ``copy_Q#1:out0`` ...; graph built at
-``model.py:201-354``), the result dictionary (``events``, ``copies``, ``output_states``,
-``lowering_trace``, ``source_features``; ``model.py:1131-1197``), the ordinal lowering oracle
+``model.py:201-354``), the result dictionary (``events`` with ``profile_key`` / ``profile_cost``,
+``copies`` including the initial global-memory copies, ``output_states``, ``lowering_trace``,
+``source_features``, ``objective_features``, ``profiles``, ``best_bound``, ``lexicographic_objective``,
+``model_sha256``; ``model.py:1131-1197``) in the form the reference's own ``replay`` accepts, the ordinal lowering oracle
 (``lowering_trace``, ``model.py:406-494``) and an independent ``replay`` (``model.py:1205-1355``)
 that raises ``ValueError`` on any inconsistency.
 
@@ -26,6 +28,7 @@ carry over unchanged).
 from __future__ import annotations
 
 from dataclasses import asdict, dataclass, field
+import hashlib
 import json
 import math
 from pathlib import Path
@@ -79,6 +82,7 @@ class Problem:
     objective_spec: Mapping[str, Any]
     provenance: Mapping[str, Any]
     plan: Mapping[str, Any] = field(default_factory=dict)  # declarative residency constraints
+    profiles: Mapping[str, Any] = field(default_factory=dict)  # profile_key -> declared cost record
 
 
 def _occupied(value, tier):
@@ -107,11 +111,22 @@ def build_problem(*, arena_slabs=8, register_budget_bytes=98304, allow_probabili
         values += [value(f"V{j}_{s}", "v", j, s, 4096, "N32xDv64 B operand, one swizzled box") for s in (0, 1)]
     values.append(value("alpha1", "alpha", 1, None, 256, "FP32 online rescale factor"))
     actions = []
+    roles = {v.name: v.role for v in values}
+
+    def profile_of(kind, inputs, outputs):
+        """Name of the action's cost record (the reference's primitive vocabulary, ``model.py:201-354``)."""
+        moved = roles[(outputs or inputs)[0][0]] if kind in ("copy_g2s", "load_s2r", "store_r2s") else None
+        wide = "64" if moved == "v" else ""
+        return {"copy_g2s": f"copy_{moved}{wide}", "load_s2r": f"load_{moved}{wide}", "store_r2s": f"store_{moved}",
+                "qk": "qk", "stats_first": "stats_emit_p_first", "stats_next": "stats_emit_p_next",
+                "pv_first": "pv64_first", "pv_next": "pv64_next", "rescale_o": "rescale_o64",
+                "normalize_store": "normalize_store64", "store_lse": "store_lse"}[kind]
 
     def add(name, kind, inputs, outputs, maximum=1, mandatory=False, tile=None, stripe=None, first=False):
         for instance in range(maximum):
             actions.append({"id": f"{name}#{instance}", "name": name, "instance": instance, "kind": kind,
                             "input_refs": [list(x) for x in inputs], "output_refs": [list(x) for x in outputs],
+                            "profile_key": profile_of(kind, inputs, outputs), "profile_cost": 0,
                             "duration": 1, "mandatory": mandatory, "tile": tile, "stripe": stripe, "first": first,
                             "value": outputs[0][0] if len(outputs) == 1 else None, "workspace_reg_bytes": 0,
                             "workspace_smem_bytes": close_workspace_smem_bytes if kind == "normalize_store" else 0})
@@ -153,7 +168,12 @@ def build_problem(*, arena_slabs=8, register_budget_bytes=98304, allow_probabili
                                         "close_workspace_smem_bytes": close_workspace_smem_bytes},
                        "O_state_bytes_per_stripe": OUTPUT_STRIPE_BYTES,
                        "limitation": "Source dependency and address intervals only; completion on the GPU is what the emitted waits enforce"},
-                   dict(plan or {}))
+                   dict(plan or {}),
+                   # Every primitive is unpriced: the objective is the affine whole-plan proxy, not a sum of latencies.
+                   {key: {"duration": 0, "kind": "derived", "unit": objective_spec.get("unit", "cost_ticks"),
+                          "provenance": {"scope": "Unpriced primitive; the affine whole-plan objective ignores it",
+                                         "not_a_primitive_latency": True}}
+                    for key in sorted({a["profile_key"] for a in actions})})
 
 
 def problem_to_dict(p):
@@ -164,7 +184,7 @@ def problem_from_dict(d):
     return Problem(tuple(Value(**v) for v in d["values"]), tuple(d["actions"]), d["arena_slabs"],
                    d["register_budget_bytes"], tuple(tuple(e) for e in d["precedence_edges"]),
                    tuple(tuple(c) for c in d["state_chains"]), tuple(d["kv_order"]), d["objective_spec"],
-                   d["provenance"], d.get("plan", {}))
+                   d["provenance"], d.get("plan", {}), d.get("profiles", {}))
 
 
 def validate_problem(p):
@@ -178,6 +198,7 @@ def validate_problem(p):
     require(len(ids) == len(set(ids)), "Duplicate action identities")
     for a in p.actions:
         require(a["kind"] in ACTION_KINDS and a["duration"] == 1, f"Bad action {a['id']}")
+        require(not p.profiles or a.get("profile_key") in p.profiles, f"Action {a['id']} names an undeclared cost record")
         for name, tier in [*a["input_refs"], *a["output_refs"]]:
             require(name in values and tier in ("gmem", "smem", "reg"), f"Unknown port value in {a['id']}")
         if a["kind"] == "copy_g2s":
@@ -298,20 +319,41 @@ def source_feature_values(p, r):
                            + sum(_kib(s["bytes"]) for s in r["output_states"] if s["start"] <= t < s["end"])
                            for t in steps),
         "consumer_wait_count": sum(row["wait_before_load"] for row in trace),
-        "release_barrier_count": sum(row["release_before_write"] for row in trace),
+        # releases in front of input copies and the close's scratch, as the reference counts them
+        # (model.py:507-510); a checkpoint store's release is part of the checkpoint's own cost
+        "release_barrier_count": sum(row["release_before_write"] and row["kind"] in ("copy_g2s", "normalize_store")
+                                     for row in trace),
         "last_commit_wait_hmma_sites": sum(row["last_commit_wait_hmma_sites"] for row in trace),
         "last_commit_wait_ex2_sites": sum(row["last_commit_wait_ex2_sites"] for row in trace),
         "source_actions": len(r["events"]),
     }
 
 
-def evaluate_objective(p, r):
+def _term_source(term):
+    """Which plan feature an objective term prices. Two spellings are read: this package's
+    ``{"feature": "rf_kib_steps"}`` and the reference's (``exchange.py:47-55``), where ``feature`` is a label, a
+    ``source`` record names an order-derived feature and an empty ``match`` counts every selected action."""
+    if "source" in term:
+        require(set(term["source"]) == {"kind"}, "Only plain source features are priced")
+        return term["source"]["kind"]
+    if "match" in term:
+        require(term["match"] == {}, "Only the all-actions match is priced")
+        return "source_actions"
+    return term["feature"]
+
+
+def objective_features(p, r):
+    """Value of every objective term, keyed by the term's label (``model.py:138-147``)."""
     features = source_feature_values(p, r)
-    total = p.objective_spec.get("constant", 0)
     for term in p.objective_spec["terms"]:
-        require(term["feature"] in features, f"Unknown objective feature {term['feature']}")
-        total += term["coefficient"] * features[term["feature"]]
-    return total
+        require(_term_source(term) in features, f"Unknown objective feature {term['feature']}")
+    return {term["feature"]: features[_term_source(term)] for term in p.objective_spec["terms"]}
+
+
+def evaluate_objective(p, r):
+    values = objective_features(p, r)
+    return p.objective_spec.get("constant", 0) + sum(term["coefficient"] * values[term["feature"]]
+                                                     for term in p.objective_spec["terms"])
 
 
 # --------------------------------------------------------------------------------------- planner
@@ -335,6 +377,7 @@ def _bound_graph(p, overrides):
                 **overrides}
     forbidden = set(p.plan.get("forbidden", ()))
     selected, frontier, inputs = {}, [a["id"] for a in p.actions if a["mandatory"]] + list(p.plan.get("selected", ())), {}
+    ports = {}  # every input port in declaration order, global-memory ports included (what the events record)
     while frontier:
         identity = frontier.pop()
         if identity in selected:
@@ -342,9 +385,10 @@ def _bound_graph(p, overrides):
         require(identity in actions and identity not in forbidden, f"Plan needs unavailable action {identity}")
         action = actions[identity]
         selected[identity] = action
-        bound = []
+        bound, ports[identity] = [], []
         for port, (name, tier) in enumerate(action["input_refs"]):
             if tier == "gmem":
+                ports[identity].append("gmem:" + name)
                 continue
             copy = explicit.get(f"{identity}:{port}", producers.get((name, tier)))
             require(copy is not None, f"No producer for port {port} of {identity}")
@@ -352,6 +396,7 @@ def _bound_graph(p, overrides):
             require(producer in actions and list(actions[producer]["output_refs"][int(out)]) == [name, tier],
                     f"{copy} does not carry ({name}, {tier}) for {identity}")
             bound.append(copy)
+            ports[identity].append(copy)
             frontier.append(producer)
         inputs[identity] = bound
     copies = {}
@@ -363,8 +408,8 @@ def _bound_graph(p, overrides):
                 logical_bytes=v.logical_bytes, nbytes=v.logical_bytes, occupied_bytes=_occupied(v, tier),
                 layout=v.layout, producer=identity, workspace=False)
         if action["workspace_smem_bytes"]:
-            copies[f"{identity}:workspace"] = dict(
-                id=f"{identity}:workspace", value="__workspace:" + identity, role="workspace", tile=None,
+            copies[_workspace_id(identity)] = dict(
+                id=_workspace_id(identity), value="__workspace:" + identity, role="workspace", tile=None,
                 stripe=action["stripe"], tier="smem", logical_bytes=action["workspace_smem_bytes"],
                 nbytes=action["workspace_smem_bytes"], occupied_bytes=action["workspace_smem_bytes"],
                 layout="close scratch, internal to the action", producer=identity, workspace=True)
@@ -373,7 +418,11 @@ def _bound_graph(p, overrides):
         for copy in bound:
             require(copy in copies, f"{identity} reads {copy}, which no selected action produces")
             consumers[copy].append(identity)
-    return selected, inputs, copies, consumers
+    return selected, inputs, copies, consumers, ports
+
+
+def _workspace_id(action_id):
+    return "workspace:" + action_id
 
 
 class _Search:
@@ -384,7 +433,7 @@ class _Search:
 
     def __init__(self, p, graph, node_budget):
         self.p, self.node_budget = p, node_budget
-        self.selected, self.inputs, self.copies, self.consumers = graph
+        self.selected, self.inputs, self.copies, self.consumers, _ = graph
         self.order = sorted(self.selected)
         self.bit = {identity: 1 << i for i, identity in enumerate(self.order)}
         plan = p.plan
@@ -414,9 +463,9 @@ class _Search:
         self.memo = {}
         self.fixed_cost = 0
         for term in p.objective_spec["terms"]:
-            if term["feature"] == "source_actions":
+            if _term_source(term) == "source_actions":
                 self.fixed_cost += term["coefficient"] * len(self.selected)
-            elif term["feature"] == "rf_kib_steps":
+            elif _term_source(term) == "rf_kib_steps":
                 self.rf_weight = term["coefficient"]
         self.rf_weight = getattr(self, "rf_weight", 0)
 
@@ -484,7 +533,7 @@ class _Search:
             freed = [c for c in self.inputs[identity] if all(done & self.bit[x] or x == identity for x in self.consumers[c])]
             freed += [c for c in outputs if not self.consumers[c]]
             writes = [c for c in outputs if self.copies[c]["tier"] == "smem"]
-            scratch = f"{identity}:workspace" if f"{identity}:workspace" in self.copies else None
+            scratch = _workspace_id(identity) if _workspace_id(identity) in self.copies else None
             occupied = {o + i for o, n in smem.values() for i in range(n)}
             placements = [dict()]
             if writes:
@@ -525,8 +574,9 @@ class _Search:
 
 
 def _materialise(p, graph, plan_trail, status, complete):
-    selected, inputs, copies, consumers = graph
+    selected, inputs, copies, consumers, ports = graph
     step_of = {identity: step for step, (identity, _, _) in enumerate(plan_trail)}
+    finish = len(plan_trail)
     offsets = {}
     for _, placement, _ in plan_trail:
         offsets.update(placement)
@@ -539,19 +589,28 @@ def _materialise(p, graph, plan_trail, status, complete):
         if c["workspace"]:
             row["end"] = producer_step + 1
         rows.append(row)
+    # The kernel's inputs: one global-memory copy per Q/K/V value, present for the whole plan.
+    for v in p.values:
+        if v.role in ("q", "k", "v"):
+            rows.append(dict(id="gmem:" + v.name, value=v.name, role=v.role, tile=v.tile, stripe=v.stripe, tier="gmem",
+                             logical_bytes=v.logical_bytes, nbytes=v.logical_bytes, occupied_bytes=v.logical_bytes,
+                             layout=v.layout, producer=None, workspace=False, start=0, available=0, end=finish,
+                             offset_bytes=None))
     events = []
     for identity, action in selected.items():
-        e = {k: action[k] for k in ("id", "name", "kind", "instance", "value", "tile", "stripe", "first", "duration",
-                                    "workspace_reg_bytes", "workspace_smem_bytes")}
-        e.update(start=step_of[identity], end=step_of[identity] + 1, inputs=list(inputs[identity]),
+        e = {k: action[k] for k in ("id", "name", "kind", "instance", "value", "tile", "stripe", "first", "profile_key",
+                                    "duration", "profile_cost", "workspace_reg_bytes", "workspace_smem_bytes")}
+        e.update(start=step_of[identity], end=step_of[identity] + 1, inputs=list(ports[identity]),
                  outputs=[c["id"] for c in rows if c["producer"] == identity and not c["workspace"]],
                  workspace_copies=[c["id"] for c in rows if c["producer"] == identity and c["workspace"]],
                  state_effect=any(identity in chain for chain in p.state_chains))
         events.append(e)
     events.sort(key=lambda e: (e["start"], e["id"]))
     r = dict(status=status, ordering_unit="source_steps", time_unit="source_steps",
-             objective_unit=p.provenance["objective_unit"], optimality_certified=complete,
-             finish_step=len(events), events=events, copies=rows, provenance=dict(p.provenance),
+             objective_unit=p.provenance["objective_unit"], objective=None, best_bound=None, finish_step=finish,
+             optimality_certified=complete, events=events, copies=rows, output_states=[],
+             profiles=json.loads(json.dumps(dict(p.profiles))), provenance=dict(p.provenance),
+             model_sha256=hashlib.sha256(json.dumps(problem_to_dict(p), sort_keys=True).encode()).hexdigest(),
              solver="depth-first branch and bound over source orders (no external solver)")
     r["actions"] = r["events"]
     r["output_states"] = [dict(stripe=s, tier="reg", bytes=OUTPUT_STRIPE_BYTES, start=step_of[chain[0]],
@@ -559,9 +618,30 @@ def _materialise(p, graph, plan_trail, status, complete):
                                effect_order=list(chain)) for s, chain in enumerate(p.state_chains)]
     r["source_features"] = source_feature_values(p, r)
     r["lowering_trace"] = lowering_trace(p, r)
+    r["cp_lowering_frontier"] = None  # the frontier certificate belongs to a constraint model; there is none here
     r["objective"] = evaluate_objective(p, r)
+    r["objective_features"] = objective_features(p, r)
+    r["cp_source_features"] = {json.dumps(term["source"], sort_keys=True): r["source_features"][term["source"]["kind"]]
+                               for term in p.objective_spec["terms"] if "source" in term}
     r["objective_model"] = {"kind": "affine_features", "spec": p.objective_spec, "unit": p.provenance["objective_unit"]}
     return r
+
+
+def objective_lower_bound(p, graph):
+    """A bound no source order of the bound graph can beat, whatever the slab addresses: every selected action
+    is counted; a register copy is alive at least in its producer's step and, if anything reads it, in one
+    later step; an output stripe's state at least one step per action of its chain."""
+    selected, _, copies, consumers, _ = graph
+    rf = sum(_kib(c["occupied_bytes"]) * (2 if consumers[identity] else 1)
+             for identity, c in copies.items() if c["tier"] == "reg")
+    rf += sum(_kib(OUTPUT_STRIPE_BYTES) * len(chain) for chain in p.state_chains)
+    floor = {"source_actions": len(selected), "rf_kib_steps": rf}
+    total = p.objective_spec.get("constant", 0)
+    for term in p.objective_spec["terms"]:
+        require(term["coefficient"] >= 0 and _term_source(term) in floor,
+                "The bound covers non-negative action-count and RF terms")
+        total += term["coefficient"] * floor[_term_source(term)]
+    return total
 
 
 def solve(p, max_time_seconds=15, artifact_dir=None):
@@ -578,8 +658,11 @@ def solve(p, max_time_seconds=15, artifact_dir=None):
     variants = p.plan.get("alternatives") or [{}]
     best = None
     complete = True
+    floor = None
     for overrides in variants:
         graph = _bound_graph(p, overrides)
+        bound = objective_lower_bound(p, graph)
+        floor = bound if floor is None else min(floor, bound)
         # The budget is counted in search nodes, not seconds, so that the same call returns the same
         # plan on every machine (about 20k nodes per second of the nominal budget).
         search = _Search(p, graph, int(NODES_PER_SECOND * max_time_seconds / len(variants)))
@@ -591,8 +674,17 @@ def solve(p, max_time_seconds=15, artifact_dir=None):
         r = dict(status="INFEASIBLE" if complete else "UNKNOWN", events=[], copies=[], output_states=[],
                  provenance=dict(p.provenance), finish_step=None, objective=None)
     else:
-        r = _materialise(p, best[2], best[1], "OPTIMAL" if complete else "FEASIBLE", complete)
+        # `complete` means the order space was exhausted under the slab-placement heuristic (three candidate
+        # offsets per write), which proves nothing about orders that need another address: the optimum is
+        # certified only when the objective meets the address-free lower bound.
+        certified = complete and best[0] == floor
+        r = _materialise(p, best[2], best[1], "OPTIMAL" if certified else "FEASIBLE", certified)
         require(r["objective"] == best[0], "Search cost and replayed objective differ")
+        multiplier = len(p.actions) + 1
+        r["best_bound"] = r["objective"] if certified else floor
+        r["lexicographic_objective"] = {"combined": r["objective"] * multiplier + r["finish_step"],
+                                        "combined_bound": r["best_bound"] * multiplier + (r["finish_step"] if certified else 0),
+                                        "cost_multiplier": multiplier}
         r["replay"] = replay(p, r)
     r["solver_wall_seconds"] = time.perf_counter() - started
     if artifact_dir is not None:
@@ -623,8 +715,10 @@ def replay(p, r):
     require({a["id"] for a in p.actions if a["mandatory"]} <= set(events), "A mandatory action is missing")
     for e in r["events"]:
         require(e["id"] in actions and actions[e["id"]]["kind"] == e["kind"], f"Unknown event {e['id']}")
-        ports = [ref for ref in actions[e["id"]]["input_refs"] if ref[1] != "gmem"]
+        ports = actions[e["id"]]["input_refs"]
         require(len(ports) == len(e["inputs"]), f"{e['id']} must bind every input port")
+        require(all(e[k] == actions[e["id"]][k] for k in ("profile_key", "profile_cost", "duration")),
+                f"{e['id']} changed its declared cost record")
         for (name, tier), source in zip(ports, e["inputs"]):
             require(source in copies, f"{e['id']} reads unknown copy {source}")
             c = copies[source]
@@ -634,7 +728,13 @@ def replay(p, r):
         require(sorted(produced) == sorted(e["outputs"]) and len(produced) == len(actions[e["id"]]["output_refs"]),
                 f"{e['id']} outputs disagree with its copies")
     consumers = {identity: [e for e in r["events"] if identity in e["inputs"]] for identity in copies}
+    inputs_wanted = {"gmem:" + v.name for v in p.values if v.role in ("q", "k", "v")}
+    require({c["id"] for c in r["copies"] if c["producer"] is None} == inputs_wanted, "Kernel inputs invented or missing")
     for c in r["copies"]:
+        if c["producer"] is None:
+            require(c["tier"] == "gmem" and c["id"] == "gmem:" + c["value"] and c["start"] == c["available"] == 0
+                    and c["end"] == r["finish_step"] and c["offset_bytes"] is None, f"{c['id']} is not a kernel input")
+            continue
         producer = events.get(c["producer"])
         require(producer is not None and c["start"] == producer["start"] and c["available"] == producer["end"],
                 f"{c['id']} lifetime does not start at its producer")
@@ -665,10 +765,30 @@ def replay(p, r):
         live += sum(s["bytes"] for s in r["output_states"] if s["start"] <= step < s["end"])
         require(live <= p.register_budget_bytes, f"Register budget exceeded at step {step}")
         peak = max(peak, live)
+    require(r["profiles"] == json.loads(json.dumps(dict(p.profiles))) and r["provenance"] == dict(p.provenance),
+            "Cost records or provenance differ from the problem's")
+    require(integer(r["best_bound"]) and r["best_bound"] <= r["objective"] and isinstance(r["optimality_certified"], bool)
+            and (not r["optimality_certified"] or r["best_bound"] == r["objective"]), "Invalid objective bound")
+    lex = r["lexicographic_objective"]
+    require(lex["cost_multiplier"] == len(p.actions) + 1
+            and lex["combined"] == r["objective"] * lex["cost_multiplier"] + r["finish_step"]
+            and lex["combined_bound"] <= lex["combined"], "Invalid lexicographic objective record")
+    require(r["objective_features"] == objective_features(p, r), "Stored objective features differ from the plan")
     require(r["source_features"] == source_feature_values(p, r), "Stored source features differ from the plan")
     require(r["objective"] == evaluate_objective(p, r), "Stored objective differs from the plan")
     require(r["lowering_trace"] == lowering_trace(p, r), "Stored lowering trace differs from the plan")
-    summary = {"events": len(events), "peak_register_bytes": peak,
+    peak_shared = max(sum(c["occupied_bytes"] for c in shared if c["start"] <= step < c["end"])
+                      for step in range(r["finish_step"]))
+    executions = {}
+    for e in sorted(r["events"], key=lambda e: e["start"]):
+        executions[e["name"]] = executions.get(e["name"], 0) + 1
+    # peak_bytes / executions / source_order_steps / objective are the quantities the reference's replay
+    # reports (model.py:1346-1355), so that the two replays can be compared field by field.
+    summary = {"valid": True, "events": len(events), "peak_register_bytes": peak,
+               "peak_bytes": {"reg": peak, "smem": peak_shared}, "executions": executions,
+               "q_global_loads": executions.get("copy_Q", 0), "source_order_steps": r["finish_step"],
+               "objective": r["objective"], "objective_unit": r["objective_unit"],
+               "objective_features": r["objective_features"],
                "shared_high_water_bytes": max(c["offset_bytes"] + c["occupied_bytes"] for c in shared)}
     if p.plan.get("contract"):
         from . import exchange
