@@ -126,11 +126,16 @@ int tc_decode_forward_out(int device, void* stream, const void* q, void* kcache,
 /* tc_decode_forward_out with option flags. TC_DECODE_CACHE_STABLE is the caller's promise that the kernel
  * launched immediately before this call on the same stream writes none of: the cache rows below
  * old_lengths[b], old_lengths itself (and, where used, index tables). The launch uses programmatic dependent
- * launch; with the flag the K/V stream and the length read start while that preceding kernel is still
- * finishing, and only q, knew, vnew and all writes wait for it. Typical case: the preceding kernel is the
- * projection that produces q / knew / vnew. Without the promise (a kernel that appended to the same cache one
- * launch earlier) results are undefined; flags = 0 is tc_decode_forward_out. No counterpart in the reference. */
+ * launch; with the flag the length read and the K/V stream start while that preceding kernel is still
+ * finishing (the first tiles into the shared-memory ring, the others as prefetches into L2), and only q, knew,
+ * vnew and all writes wait for it. Typical cases: the preceding kernel is the projection that produces q / knew
+ * / vnew, or the decode step of another layer (other caches). TC_DECODE_PREFIX_STABLE is the narrower promise
+ * for a preceding kernel that was the previous decode step of the SAME caches: it may have written row
+ * old_lengths[b] - 1 and nothing else of the above; then only the tiles that end below that row are fetched
+ * early. The two flags are alternatives. If the promise does not hold, results are undefined; flags = 0 is
+ * tc_decode_forward_out. No counterpart in the reference. */
 #define TC_DECODE_CACHE_STABLE 1
+#define TC_DECODE_PREFIX_STABLE 2
 int tc_decode_forward_out_flags(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,
                                 const void* vnew, const int32_t* old_lengths, void* out, float* lse,
                                 float* workspace_o, int64_t workspace_o_elems, float* workspace_lse,

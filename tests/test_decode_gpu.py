@@ -375,6 +375,78 @@ def test_missing_rank_ends_the_exchange_with_a_status(ops, gpu_device):
     oracle.check_outputs(got_o, got_lse, want_o, want_lse)
 
 
+@pytest.mark.parametrize("batch,capacity,base", [(1, 4096, 2045), (1, 16384, 12283), (2, 2048, 60)])
+def test_consecutive_steps_on_one_cache_may_overlap_under_the_prefix_promise(ops, gpu_device, batch, capacity, base):
+    """Twelve decode steps back to back on the same caches (each appends one row; the lengths of every step
+    are a tensor of their own). Launched with the prefix promise, a step streams the rows below the row its
+    predecessor appended while that predecessor is still finishing; outputs, LSE and the final caches must
+    equal, bit for bit, those of the same chain launched without any promise. Lengths cross tile boundaries."""
+    device, steps = gpu_device, 12
+    _, kcache, vcache, _, _ = make_case(51, batch, capacity)
+    q = oracle.seeded_normal(52, (steps, batch, 1, 32, 128))[0].to(device)
+    knew, vnew = (t.to(device) for t in oracle.seeded_normal(53, (steps, batch, 1, 8, 128), (steps, batch, 1, 8, 128)))
+    lengths = [torch.tensor([base + t - 17 * b for b in range(batch)], dtype=torch.int32, device=device)
+               for t in range(steps)]
+    results = {}
+    for promise in (False, "prefix"):
+        dk, dv = kcache.to(device), vcache.to(device)
+        outs = torch.full((steps, batch, 1, 32, 128), float("nan"), device=device, dtype=torch.bfloat16)
+        lses = torch.full((steps, batch, 32, 1), float("nan"), device=device)
+        spec = ops.workspace_spec(q[0], dk, lengths[0], 0, 1, True)
+        ws = [torch.empty(n, device=device, dtype=torch.float32) for n in spec[1:3]]
+        torch.cuda.synchronize()
+        for t in range(steps):
+            ops.forward_out(q[t], dk, dv, knew[t], vnew[t], lengths[t], outs[t], lses[t], *ws, 0, 1, True,
+                            cache_stable=promise)
+        torch.cuda.synchronize()
+        assert ops.library.device_status(device.index) == 0
+        results[promise] = (outs.cpu(), lses.cpu(), dk.cpu(), dv.cpu())
+    plain, early = results[False], results["prefix"]
+    assert not torch.isnan(plain[0].float()).any()
+    assert torch.equal(bits(plain[0]), bits(early[0])) and torch.equal(plain[1].view(torch.int32), early[1].view(torch.int32))
+    assert torch.equal(bits(plain[2]), bits(early[2])) and torch.equal(bits(plain[3]), bits(early[3]))
+    # and the last step agrees with the oracle on the caches as the chain left them before it
+    host_k, host_v = kcache.clone(), vcache.clone()
+    for t in range(steps - 1):
+        for b in range(batch):
+            host_k[b, int(lengths[t][b])] = knew[t, b, 0].cpu()
+            host_v[b, int(lengths[t][b])] = vnew[t, b, 0].cpu()
+    want_o, want_lse, want_k, want_v = oracle.decode_step(q[-1].cpu(), host_k, host_v, knew[-1].cpu(), vnew[-1].cpu(),
+                                                          lengths[-1].cpu())
+    oracle.check_outputs(early[0][-1], early[1][-1], want_o, want_lse)
+    assert torch.equal(bits(early[2]), bits(want_k)) and torch.equal(bits(early[3]), bits(want_v))
+
+
+def test_steps_on_different_caches_may_overlap_under_the_cache_stable_promise(ops, gpu_device):
+    """Decode steps of eight different caches back to back (the layers of a model): with the cache-stable promise
+    each step prefetches its whole share of its cache while the step before it runs. Same bits as without."""
+    device, layers, capacity = gpu_device, 8, 8192
+    old = torch.tensor([capacity - 100], dtype=torch.int32, device=device)
+    prefix = [oracle.seeded_normal(60 + layer, (1, capacity, 8, 128), (1, capacity, 8, 128)) for layer in range(layers)]
+    q, knew, vnew = (t.to(device) for t in oracle.seeded_normal(61, (1, 1, 32, 128), (1, 1, 8, 128), (1, 1, 8, 128)))
+    results = {}
+    for promise in (False, True):
+        caches = [(k.to(device), v.to(device)) for k, v in prefix]
+        outs = torch.full((layers, 1, 1, 32, 128), float("nan"), device=device, dtype=torch.bfloat16)
+        lses = torch.full((layers, 1, 32, 1), float("nan"), device=device)
+        spec = ops.workspace_spec(q, caches[0][0], old, 0, 1, True)
+        ws = [torch.empty(n, device=device, dtype=torch.float32) for n in spec[1:3]]
+        torch.cuda.synchronize()
+        for repeat in range(3):
+            for layer in range(layers):
+                ops.forward_out(q, *caches[layer], knew, vnew, old, outs[layer], lses[layer], *ws, 0, 1, True,
+                                cache_stable=promise)
+        torch.cuda.synchronize()
+        assert ops.library.device_status(device.index) == 0
+        results[promise] = (outs.cpu(), lses.cpu(), [k[:, capacity - 100].cpu() for k, _ in caches])
+    plain, early = results[False], results[True]
+    assert torch.equal(bits(plain[0]), bits(early[0])) and torch.equal(plain[1].view(torch.int32), early[1].view(torch.int32))
+    for a, b in zip(plain[2], early[2]):
+        assert torch.equal(bits(a), bits(b))
+    want_o, want_lse, _, _ = oracle.decode_step(q.cpu(), prefix[3][0], prefix[3][1], knew.cpu(), vnew.cpu(), old.cpu())
+    oracle.check_outputs(early[0][3], early[1][3], want_o, want_lse)
+
+
 def test_argument_checks(ops, gpu_device):
     q, kcache, vcache, knew, vnew = (t.to(gpu_device) for t in make_case(1, 1, 128))
     old = torch.zeros(1, dtype=torch.int32, device=gpu_device)

@@ -182,6 +182,12 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
         "r"(c2), "r"(c3), "l"(policy)
         : "memory");
 }
+// 4-D tiled prefetch into L2: the same box as a load, no shared-memory destination and no completion.
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
 // 2-D tiled load (innermost coordinate first), completion on an mbarrier of this CTA.
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
                                             uint64_t policy) {

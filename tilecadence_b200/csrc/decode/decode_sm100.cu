@@ -107,9 +107,10 @@ struct DecodeParams {
     const float* rope_cos;
     const float* rope_sin;
     int rope_positions;
-    // Caller's promise that the kernel launched just before this one on the stream writes neither the
-    // caches' visible rows, nor old_lengths, nor the index tables: the K/V stream then starts before
-    // the stream dependency resolves.
+    // Caller's promise about the kernel launched just before this one on the stream. 1: it writes neither the
+    // caches' visible rows, nor old_lengths, nor the index tables; 2: the same, except that it may have written
+    // row old_lengths[b] - 1 of these caches (the previous decode step of the same sequences). The K/V stream
+    // of the rows that are promised stable then starts before the stream dependency resolves.
     int cache_stable;
 };
 
@@ -249,7 +250,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     const int n_tiles = tile_end - tile_begin;
 
     __syncthreads();
-    if (p.cache_stable && warp != kConsumerWarps) {
+    if (p.cache_stable && (warp != kConsumerWarps || (p.cache_stable == 2 && p.block_table))) {
+        // (a paged cache under the narrower promise streams nothing early: its producer waits as well)
         tc::grid_dependency_wait();
         tc::grid_launch_dependents();  // after the wait: the next launch can overlap this one only
     }
@@ -257,6 +259,18 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------------ producer warp
         const uint64_t policy = tc::policy_evict_first();
+        // Tiles [0, early_tiles) of this CTA hold only rows the caller promised stable: they may be fetched
+        // before the stream dependency resolves. The ring takes the first kStages of them; the rest are
+        // prefetched into L2, from where they arrive at L2 speed once the consumers free ring stages.
+        int early_tiles = 0;
+        if (p.cache_stable == 1) {
+            early_tiles = n_tiles;
+        } else if (p.cache_stable == 2) {
+            const int64_t touched = old_len - 1 - p.shard_start;  // the one row the preceding kernel may have written
+            const int64_t stable_end = touched < 0 ? 0 : touched / kTileN;
+            const int64_t count = stable_end - tile_begin;
+            early_tiles = int(count < 0 ? 0 : (count > n_tiles ? n_tiles : count));
+        }
         auto issue_tile = [&](int it, int slot, int row0) {
             const int stage = (n_tiles - 1 - it) % kStages;  // the last tile always lands in stage 0
             const uint32_t generation = uint32_t(it / kStages);
@@ -274,8 +288,22 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
         };
         if (!p.block_table) {
             if (lane == 0) {
-                for (int it = 0; it < n_tiles; ++it)
-                    if (!issue_tile(it, slot_of_b, (tile_begin + it) * kTileN)) break;
+                const int ring_early = early_tiles < kStages ? early_tiles : kStages;
+                bool ok = true;
+                int it = 0;
+                for (; ok && it < ring_early; ++it) ok = issue_tile(it, slot_of_b, (tile_begin + it) * kTileN);
+                for (int ahead = kStages; ahead < early_tiles; ++ahead) {
+                    const int row0 = (tile_begin + ahead) * kTileN;
+                    tc::tma_prefetch_4d(&vmap, 0, kvh, row0, slot_of_b);
+                    tc::tma_prefetch_4d(&vmap, 64, kvh, row0, slot_of_b);
+                    tc::tma_prefetch_4d(&kmap, 0, kvh, row0, slot_of_b);
+                    tc::tma_prefetch_4d(&kmap, 64, kvh, row0, slot_of_b);
+                }
+                for (; ok && it < n_tiles; ++it) {
+                    // A tile outside the promise is fetched only after the preceding kernel has completed.
+                    if (p.cache_stable && it == early_tiles) tc::grid_dependency_wait();
+                    ok = issue_tile(it, slot_of_b, (tile_begin + it) * kTileN);
+                }
             }
         } else {
             // Paged cache: the whole warp looks up the pages of the next 32 tiles with one coalesced
@@ -895,7 +923,7 @@ int decode_common(int device, void* stream, const void* q, void* kcache, void* v
     p.partial_o = partial_o;
     p.page_size = int(slot_rows);
     p.cache_slots = int(cache_slots);
-    p.cache_stable = cache_stable ? 1 : 0;
+    p.cache_stable = cache_stable;
     if (rope) {
         TC_REQUIRE(rope->cos && rope->sin && rope->positions >= 1 && rope->positions <= (int64_t(1) << 30),
                    "RoPE needs cos/sin tables FP32[positions,64] with positions >= 1");
@@ -1175,10 +1203,13 @@ int tc_decode_forward_out_flags(int device, void* stream, const void* q, void* k
                                 float* workspace_o, int64_t workspace_o_elems, float* workspace_lse,
                                 int64_t workspace_lse_elems, int64_t batch, int64_t capacity, int64_t kv_heads,
                                 int64_t num_splits, int64_t mapping, int append, int64_t flags) {
-    TC_REQUIRE((flags & ~int64_t(TC_DECODE_CACHE_STABLE)) == 0, "unknown decode flag");
+    TC_REQUIRE((flags & ~int64_t(TC_DECODE_CACHE_STABLE | TC_DECODE_PREFIX_STABLE)) == 0, "unknown decode flag");
+    TC_REQUIRE(flags != (TC_DECODE_CACHE_STABLE | TC_DECODE_PREFIX_STABLE),
+               "TC_DECODE_CACHE_STABLE and TC_DECODE_PREFIX_STABLE are alternatives");
     return decode_common(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, nullptr, workspace_o,
                          workspace_o_elems, workspace_lse, workspace_lse_elems, batch, capacity, kv_heads, num_splits,
-                         mapping, append, 0, 0, nullptr, nullptr, nullptr, (flags & TC_DECODE_CACHE_STABLE) != 0);
+                         mapping, append, 0, 0, nullptr, nullptr, nullptr,
+                         (flags & TC_DECODE_CACHE_STABLE) ? 1 : ((flags & TC_DECODE_PREFIX_STABLE) ? 2 : 0));
 }
 
 int tc_peer_block_bytes(int64_t batch, int64_t kv_heads, int64_t world, int64_t* bytes) {

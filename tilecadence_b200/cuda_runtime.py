@@ -399,8 +399,17 @@ class PrefillOps:
         return list(values[:count.value])
 
 
-#: ``flags`` bit of ``tc_decode_forward_out_flags``; same value as TC_DECODE_CACHE_STABLE in the header.
+#: ``flags`` bits of ``tc_decode_forward_out_flags``; same values as TC_DECODE_CACHE_STABLE and
+#: TC_DECODE_PREFIX_STABLE in the header.
 DECODE_CACHE_STABLE = 1
+DECODE_PREFIX_STABLE = 2
+
+
+def _decode_flags(cache_stable):
+    if cache_stable == "prefix":
+        return DECODE_PREFIX_STABLE
+    _require(cache_stable is True, 'cache_stable must be False, True or "prefix"')
+    return DECODE_CACHE_STABLE
 
 
 class DecodeOps:
@@ -468,7 +477,9 @@ class DecodeOps:
                     num_splits, mapping, append, *, cache_stable=False):
         """One decode step. ``cache_stable=True`` is the caller's promise that the kernel enqueued just
         before this call writes neither the caches' visible rows nor ``old_lengths``; the K/V stream then
-        starts while that kernel is still finishing (``TC_DECODE_CACHE_STABLE``)."""
+        starts while that kernel is still finishing (``TC_DECODE_CACHE_STABLE``). ``cache_stable="prefix"``
+        is the narrower promise for a preceding kernel that was the previous decode step of the same caches
+        and appended row ``old_lengths - 1`` (``TC_DECODE_PREFIX_STABLE``)."""
         self._check_call(q, kcache, vcache, knew, vnew, old_lengths, workspace_o, workspace_lse)
         self._check_out(q, out, lse)
         arguments = (
@@ -477,7 +488,7 @@ class DecodeOps:
             _pointer(workspace_o), workspace_o.numel(), _pointer(workspace_lse), workspace_lse.numel(),
             q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping), int(bool(append)))
         if cache_stable:
-            self.library.call("tc_decode_forward_out_flags", *arguments, DECODE_CACHE_STABLE)
+            self.library.call("tc_decode_forward_out_flags", *arguments, _decode_flags(cache_stable))
         else:
             self.library.call("tc_decode_forward_out", *arguments)
 
@@ -503,7 +514,7 @@ class DecodeOps:
                 workspace_lse.numel(), q.size(0), kcache.size(1), kcache.size(2), int(num_splits), int(mapping),
                 int(bool(append)))
         if cache_stable:
-            function, tail = self.library.handle.tc_decode_forward_out_flags, tail + (DECODE_CACHE_STABLE,)
+            function, tail = self.library.handle.tc_decode_forward_out_flags, tail + (_decode_flags(cache_stable),)
         else:
             function = self.library.handle.tc_decode_forward_out
         library, device = self.library, q.device
