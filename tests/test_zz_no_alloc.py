@@ -113,6 +113,7 @@ def test_static_entry_and_its_status_readers_allocate_nothing(library, gpu_devic
     q, knew, vnew = oracle.seeded_normal(6, (batch, 1, 32, 128), (batch, 1, 8, 128), (batch, 1, 8, 128))
     dk, dv, dq, dkn, dvn = (t.to(device) for t in (prefix_k, prefix_v, q, knew, vnew))
     old = torch.tensor([1500, 900], dtype=torch.int32, device=device)
+    old_next = old + 1  # made before the measurement: creating a tensor may make torch's allocator grow
     out = torch.empty_like(dq)
     lse = torch.empty((batch, 32, 1), device=device, dtype=torch.float32)
     call_static(library, dq, dk, dv, dkn, dvn, old, out, lse)  # first call: address look-up, kernel load
@@ -120,7 +121,7 @@ def test_static_entry_and_its_status_readers_allocate_nothing(library, gpu_devic
     library.device_status(device.index)
     torch.cuda.synchronize()
     free_before, _ = torch.cuda.mem_get_info(device)
-    call_static(library, dq, dk, dv, dkn, dvn, old + 1, out, lse)
+    call_static(library, dq, dk, dv, dkn, dvn, old_next, out, lse)
     static_status_word(library, device)
     assert library.device_status(device.index) == 0
     torch.cuda.synchronize()

@@ -352,6 +352,18 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The same MMA for an A tile whose rows 8-15 are zero (operands a1 and a3): only rows 0-7 of D can be
+// non-zero, so only their two accumulator registers are carried; the lower half is fed zeros and dropped.
+__device__ __forceinline__ void mma_bf16_16816_rows8(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0,
+                                                     uint32_t b1) {
+    float unused2, unused3;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %5}, {%7, %8}, "
+        "{%0, %1, %9, %9};"
+        : "+f"(d0), "+f"(d1), "=f"(unused2), "=f"(unused3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.f));
+}
+
 // ----------------------------------------------------------------------------- conversions / math
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;

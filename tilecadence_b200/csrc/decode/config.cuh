@@ -4,6 +4,11 @@
 #pragma once
 #define V10_FAMILY_CODE 7901
 #define AB_DECODE_WARPS 4
+// Consumer groups of AB_DECODE_WARPS warps that take the tiles in turn. One group keeps 200 registers per
+// thread; two groups (288 threads, 112 registers, spills) were slower at every cache length measured.
+#ifndef AB_DECODE_WARP_GROUPS
+#define AB_DECODE_WARP_GROUPS 1
+#endif
 #define AB_DECODE_BLOCK_N 64
 #ifndef AB_DECODE_STAGES
 #define AB_DECODE_STAGES 3

@@ -7,9 +7,10 @@
 //
 // The kernel is HBM-bound: every visible K and V row is read exactly once, 256 bytes per row per
 // KV head. One CTA = (batch, KV head, split). A producer warp streams 64-key K/V tiles through a
-// ring of shared-memory stages with TMA (128-byte swizzle) and mbarriers; four consumer warps each
-// own 16 keys of a tile and run QK^T / PV on warp-level bf16 MMAs with an online softmax, so
-// arithmetic never limits the stream. Split ranges follow the device-side lengths. The per-warp
+// ring of shared-memory stages with TMA (128-byte swizzle) and mbarriers; the four warps of a consumer
+// group each own 16 keys of a tile and run QK^T / PV on warp-level bf16 MMAs with an online softmax, and
+// two such groups take the tiles in turn, so arithmetic does not limit the stream even when the tiles
+// come from L2. Split ranges follow the device-side lengths. The per-warp
 // partials are merged through the released terminal stage: the four output rows and their LSE
 // are staged at the planner's offsets inside the terminal V region, published with one barrier and
 // exported with one 16-byte vector per thread. The last CTA to finish a (batch, KV head) merges
@@ -34,12 +35,29 @@ constexpr int kStages = AB_DECODE_STAGES;
 constexpr int kStageBytes = AB_DECODE_STAGE_BYTES;
 constexpr int kHalfBytes = kTileN * 128;  // one 64-element half of the head dimension, all tile rows
 constexpr int kVBytes = 2 * kHalfBytes;
-constexpr int kConsumerWarps = AB_DECODE_WARPS;
+constexpr int kGroupWarps = AB_DECODE_WARPS;        // warps that share one tile, 16 keys each
+constexpr int kGroups = AB_DECODE_WARP_GROUPS;      // consumer groups that take the tiles in turn
+constexpr int kConsumerWarps = kGroupWarps * kGroups;
 constexpr int kConsumerThreads = 32 * kConsumerWarps;
 constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kMergeThreads = 128;                  // four output rows x 32 lanes run the CTA's epilogue
+// Tile `it` of a CTA's n tiles uses stage (n-1-it) % kStages and belongs to group (n-1-it) % kGroups, so the
+// same (stage, group) pair comes round every kRingPeriod tiles. Each pair has a "full" barrier of its own: a
+// group then sees every phase of the barriers it waits on, in order, and a parity wait can never mistake
+// the other group's tile in that stage for its own.
+constexpr int ring_period(int a, int b) {
+    int x = a, y = b;
+    while (y) { const int t = x % y; x = y; y = t; }
+    return a / x * b;
+}
+constexpr int kRingPeriod = ring_period(kStages, kGroups);
+// Registers per thread such that AB_DECODE_CTAS_PER_SM CTAs fit the 64 K registers of an SM (allocated per warp
+// in multiples of 8 per thread).
+constexpr int kMaxRegisters = 65536 / (AB_DECODE_CTAS_PER_SM * kThreads) / 8 * 8;
 constexpr int kGroup = 4;  // query heads per KV head
 constexpr int kDim = 128;
 constexpr int kMaxSplits = 128;
+constexpr int kPrefetchTiles = 12;  // tiles a CTA may prefetch into L2 beyond its shared-memory ring
 constexpr int kStagingBytes = 2304;  // dedicated O/LSE staging when the handoff is disabled
 constexpr int kBarrierBytes = 256;
 // Cross-GPU exchange of per-rank partials (KV sequence sharded over the ranks of one node). Every
@@ -62,7 +80,9 @@ __host__ __device__ constexpr size_t peer_block_bytes(int world, int units) {
 
 static_assert(kStageBytes == 2 * kVBytes, "a stage holds one V tile followed by one K tile");
 static_assert(kMaxSplits % 32 == 0 && kGroup * kMaxSplits * 4 <= kVBytes, "split weights fit the terminal K stage");
-static_assert(kTileN == 16 * kConsumerWarps, "each consumer warp owns 16 keys of a tile");
+static_assert(kTileN == 16 * kGroupWarps, "each warp of a consumer group owns 16 keys of a tile");
+static_assert(kGroups >= 1 && kGroups <= kStages, "every consumer group parks its partial in a stage of its own");
+static_assert(kMergeThreads <= kConsumerThreads && kMergeThreads == 32 * kGroupWarps, "epilogue threads");
 static_assert(AB_DECODE_TERMINAL_V_BYTES == kVBytes, "planner donor size must match the V tile");
 static_assert(AB_DECODE_O_OFFSET_BYTES % 16 == 0 && AB_DECODE_LSE_OFFSET_BYTES % 16 == 0, "vector export");
 static_assert(AB_DECODE_O_OFFSET_BYTES + 2048 <= kVBytes && AB_DECODE_LSE_OFFSET_BYTES + 16 <= kVBytes,
@@ -140,6 +160,7 @@ __device__ __forceinline__ void locate_row(const DecodeParams& p, int b, int slo
 }
 
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+__device__ __forceinline__ void merge_barrier() { asm volatile("bar.sync 2, %0;" ::"n"(kMergeThreads) : "memory"); }
 
 __device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t chunk16) {
     // Byte offset of 16-byte chunk `chunk16` (0..15 across the 128-element row) of tile row `row`
@@ -190,14 +211,29 @@ __device__ __forceinline__ void lse_weighted_merge(int parts, LoadLse load_lse, 
     lse = total > 0.f ? __fadd_rn(lse_max, logf(total)) : INFINITY;
 }
 
+// Build switch TC_TRACE (off in every shipped library): thread 0 and the producer's lane 0 of every CTA
+// record %globaltimer at the points named below into a device table that tc_debug_trace copies out. It is how
+// the time-line tables of a decode step are made; see tilecadence_b200/trace_decode.py.
+//   0 entry  1 CTA sequence number  2 split | kv head << 8 | tiles << 16  3 lengths known, barriers ready
+//   4+2t / 5+2t tile t arrived / consumed (t < 8)  20 key loop done  21 partial staged  22 ticket taken
+//   19 result stored  23 SM id  24 (producer) first ring tiles issued  25 prefetches issued  26 last tile issued
+//   27 stream dependency resolved (consumers)  28 last CTA of a head: split LSEs loaded  29 split partials merged
+#ifdef TC_TRACE
+__device__ unsigned long long g_trace[1024][32];
+__device__ unsigned int g_trace_ctas;
+#define TC_TRACE_POINT(slot) do { if (trace_row) trace_row[slot] = tc::global_timer_ns(); } while (0)
+#else
+#define TC_TRACE_POINT(slot) do { } while (0)
+#endif
+
 template <bool kHandoff, bool kPeer>
-__global__ void __launch_bounds__(kThreads, AB_DECODE_CTAS_PER_SM)
+__global__ void __maxnreg__(kMaxRegisters)
 decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                       const DecodeParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-    uint64_t* empty = full + kStages;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);  // [kGroups][kStages]
+    uint64_t* empty = full + kGroups * kStages;
     int* flag = reinterpret_cast<int*>(empty + kStages);
     uint8_t* staging = kHandoff ? smem : smem + kStages * kStageBytes + kBarrierBytes;
     float* stage_o = reinterpret_cast<float*>(staging + (kHandoff ? AB_DECODE_O_OFFSET_BYTES : 0));
@@ -206,11 +242,16 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q_heads = p.kv_heads * kGroup;
+#ifdef TC_TRACE
+    __shared__ unsigned int trace_cta;
+    const unsigned long long trace_entry = tc::global_timer_ns();
+    if (threadIdx.x == 0) trace_cta = atomicAdd(&g_trace_ctas, 1u);
+#endif
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            tc::mbar_init(&full[s], 1);
-            tc::mbar_init(&empty[s], kConsumerWarps);
+            for (int g = 0; g < kGroups; ++g) tc::mbar_init(&full[g * kStages + s], 1);
+            tc::mbar_init(&empty[s], kGroupWarps);
         }
         tc::mbar_fence_init();
         tc::tma_prefetch_desc(&kmap);
@@ -250,10 +291,23 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     const int n_tiles = tile_end - tile_begin;
 
     __syncthreads();
+#ifdef TC_TRACE
+    unsigned long long* trace_row = (threadIdx.x == 0 || (warp == kConsumerWarps && lane == 0)) ? g_trace[trace_cta % 1024u] : nullptr;
+    if (threadIdx.x == 0) {
+        unsigned int sm;
+        asm("mov.u32 %0, %%smid;" : "=r"(sm));
+        trace_row[0] = trace_entry;
+        trace_row[1] = trace_cta;
+        trace_row[2] = (unsigned long long)(split | (kvh << 8) | (n_tiles << 16));
+        trace_row[23] = sm;
+        trace_row[3] = tc::global_timer_ns();
+    }
+#endif
     if (p.cache_stable && (warp != kConsumerWarps || (p.cache_stable == 2 && p.block_table))) {
         // (a paged cache under the narrower promise streams nothing early: its producer waits as well)
         tc::grid_dependency_wait();
         tc::grid_launch_dependents();  // after the wait: the next launch can overlap this one only
+        TC_TRACE_POINT(27);
     }
 
     if (warp == kConsumerWarps) {
@@ -279,11 +333,12 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
                 return false;
             }
             uint8_t* base = smem + stage * kStageBytes;
-            tc::mbar_arrive_expect_tx(&full[stage], kStageBytes);
-            tc::tma_load_4d(base, &vmap, &full[stage], 0, kvh, row0, slot, policy);
-            tc::tma_load_4d(base + kHalfBytes, &vmap, &full[stage], 64, kvh, row0, slot, policy);
-            tc::tma_load_4d(base + kVBytes, &kmap, &full[stage], 0, kvh, row0, slot, policy);
-            tc::tma_load_4d(base + kVBytes + kHalfBytes, &kmap, &full[stage], 64, kvh, row0, slot, policy);
+            uint64_t* landed = &full[((n_tiles - 1 - it) % kGroups) * kStages + stage];  // the owning group's barrier
+            tc::mbar_arrive_expect_tx(landed, kStageBytes);
+            tc::tma_load_4d(base, &vmap, landed, 0, kvh, row0, slot, policy);
+            tc::tma_load_4d(base + kHalfBytes, &vmap, landed, 64, kvh, row0, slot, policy);
+            tc::tma_load_4d(base + kVBytes, &kmap, landed, 0, kvh, row0, slot, policy);
+            tc::tma_load_4d(base + kVBytes + kHalfBytes, &kmap, landed, 64, kvh, row0, slot, policy);
             return true;
         };
         if (!p.block_table) {
@@ -292,18 +347,25 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
                 bool ok = true;
                 int it = 0;
                 for (; ok && it < ring_early; ++it) ok = issue_tile(it, slot_of_b, (tile_begin + it) * kTileN);
-                for (int ahead = kStages; ahead < early_tiles; ++ahead) {
+                TC_TRACE_POINT(24);
+                // Only a share of at most kPrefetchTiles beyond the ring is prefetched (about 55 MB over a full
+                // grid, so it is still in the 126 MB L2 when its turn comes). A longer share streams at the HBM
+                // rate anyway, and prefetching a part of it only disturbed that stream when measured.
+                const int prefetch_end = early_tiles <= kStages + kPrefetchTiles ? early_tiles : kStages;
+                for (int ahead = kStages; ahead < prefetch_end; ++ahead) {
                     const int row0 = (tile_begin + ahead) * kTileN;
                     tc::tma_prefetch_4d(&vmap, 0, kvh, row0, slot_of_b);
                     tc::tma_prefetch_4d(&vmap, 64, kvh, row0, slot_of_b);
                     tc::tma_prefetch_4d(&kmap, 0, kvh, row0, slot_of_b);
                     tc::tma_prefetch_4d(&kmap, 64, kvh, row0, slot_of_b);
                 }
+                TC_TRACE_POINT(25);
                 for (; ok && it < n_tiles; ++it) {
                     // A tile outside the promise is fetched only after the preceding kernel has completed.
                     if (p.cache_stable && it == early_tiles) tc::grid_dependency_wait();
                     ok = issue_tile(it, slot_of_b, (tile_begin + it) * kTileN);
                 }
+                TC_TRACE_POINT(26);
             }
         } else {
             // Paged cache: the whole warp looks up the pages of the next 32 tiles with one coalesced
@@ -360,23 +422,28 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
             }
         }
     }
-    float o[16][4];
+    // Accumulators of query rows 0-7 only (rows 4-7 are padding, rows 8-15 of the MMA tile are fed zeros).
+    float o[16][2];
 #pragma unroll
-    for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = 0.f;
     float row_max = -INFINITY, row_sum = 0.f;
     bool failed = false;
+    // Tile `it` belongs to group (n_tiles - 1 - it) % kGroups: the last tile, which lands in stage 0, to group 0,
+    // the one before it (stage 1) to group 1. A group's last tile therefore sits in the stage of its own number.
+    const int group = warp / kGroupWarps, gw = warp % kGroupWarps;
+    const int first_tile = (((n_tiles - 1 - group) % kGroups) + kGroups) % kGroups;
 
-    for (int it = 0; it < n_tiles; ++it) {
+    for (int it = first_tile; it < n_tiles; it += kGroups) {
         const int stage = (n_tiles - 1 - it) % kStages;
-        const uint32_t generation = uint32_t(it / kStages);
-        if (!tc::mbar_wait(&full[stage], generation & 1)) {
+        if (!tc::mbar_wait(&full[group * kStages + stage], uint32_t(it / kRingPeriod) & 1)) {
             failed = true;
             break;
         }
+        if (it < 8) TC_TRACE_POINT(4 + 2 * it);
         uint8_t* vbase = smem + stage * kStageBytes;
         uint8_t* kbase = vbase + kVBytes;
         const int tile_row0 = (tile_begin + it) * kTileN;
-        const int warp_row0 = tile_row0 + warp * 16;  // first cache row owned by this warp
+        const int warp_row0 = tile_row0 + gw * 16;  // first cache row owned by this warp
         const int valid = n_valid - warp_row0;         // >= 16: all of this warp's keys are visible
 
         if (append_row >= warp_row0 && append_row < warp_row0 + 16) {
@@ -432,7 +499,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
             for (int idx = lane; idx < 256; idx += 32) {
                 const int rr = idx >> 4;
                 if (rr >= first)
-                    *reinterpret_cast<uint4*>(vbase + swizzled(uint32_t(warp * 16 + rr), uint32_t(idx & 15))) =
+                    *reinterpret_cast<uint4*>(vbase + swizzled(uint32_t(gw * 16 + rr), uint32_t(idx & 15))) =
                         make_uint4(0, 0, 0, 0);
             }
             tc::fence_proxy_async_smem();
@@ -440,21 +507,21 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
         }
 
         if (valid > 0) {
-            float s[2][4];
+            float s[2][2];
 #pragma unroll
-            for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+            for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = 0.f;
             const uint32_t kaddr = tc::smem_u32(kbase);
             const uint32_t vaddr = tc::smem_u32(vbase);
             const int mat = lane >> 3, mrow = lane & 7;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 // matrices: (keys 0-7, d lo) (keys 0-7, d hi) (keys 8-15, d lo) (keys 8-15, d hi)
-                const uint32_t r = uint32_t(warp * 16 + (mat >> 1) * 8 + mrow);
+                const uint32_t r = uint32_t(gw * 16 + (mat >> 1) * 8 + mrow);
                 const uint32_t chunk = uint32_t(ks * 2 + (mat & 1));
                 uint32_t b00, b01, b10, b11;
                 tc::ldmatrix_x4(kaddr + swizzled(r, chunk), b00, b01, b10, b11);
-                tc::mma_bf16_16816(s[0], qa[ks][0], 0u, qa[ks][1], 0u, b00, b01);
-                tc::mma_bf16_16816(s[1], qa[ks][0], 0u, qa[ks][1], 0u, b10, b11);
+                tc::mma_bf16_16816_rows8(s[0][0], s[0][1], qa[ks][0], qa[ks][1], b00, b01);
+                tc::mma_bf16_16816_rows8(s[1][0], s[1][1], qa[ks][0], qa[ks][1], b10, b11);
             }
             if (valid < 16) {
 #pragma unroll
@@ -486,27 +553,31 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
 #pragma unroll
             for (int np = 0; np < 8; ++np) {
                 // matrices: (keys 0-7, d n0) (keys 8-15, d n0) (keys 0-7, d n0+1) (keys 8-15, d n0+1)
-                const uint32_t r = uint32_t(warp * 16 + (mat & 1) * 8 + mrow);
+                const uint32_t r = uint32_t(gw * 16 + (mat & 1) * 8 + mrow);
                 const uint32_t chunk = uint32_t(np * 2 + (mat >> 1));
                 uint32_t v00, v01, v10, v11;
                 tc::ldmatrix_x4_trans(vaddr + swizzled(r, chunk), v00, v01, v10, v11);
-                tc::mma_bf16_16816(o[2 * np], pa0, 0u, pa2, 0u, v00, v01);
-                tc::mma_bf16_16816(o[2 * np + 1], pa0, 0u, pa2, 0u, v10, v11);
+                tc::mma_bf16_16816_rows8(o[2 * np][0], o[2 * np][1], pa0, pa2, v00, v01);
+                tc::mma_bf16_16816_rows8(o[2 * np + 1][0], o[2 * np + 1][1], pa0, pa2, v10, v11);
             }
         }
         __syncwarp();
+        if (it < 8) TC_TRACE_POINT(5 + 2 * it);
         if (it + 1 < n_tiles && lane == 0) tc::mbar_arrive(&empty[stage]);
     }
     if (failed) atomicCAS(p.status, 0, 2);
+    TC_TRACE_POINT(20);
 
     // ---------------------------------------------------------------------- CTA epilogue
-    // Quad-partial row sums become full sums; each warp parks its partial in the K rows it owns in
-    // the terminal stage (nobody else reads those rows), then one barrier releases the whole stage.
+    // Quad-partial row sums become full sums; each warp parks its partial in the K rows it owns in its
+    // group's terminal stage (nobody else reads those rows: the group is done with them and the other
+    // group never reads that stage again), then one barrier releases the stages.
     row_sum += __shfl_xor_sync(0xffffffffu, row_sum, 1);
     row_sum += __shfl_xor_sync(0xffffffffu, row_sum, 2);
-    uint8_t* terminal_k = smem + kVBytes;
-    float* part_o = reinterpret_cast<float*>(terminal_k + warp * 2048);                 // [4][128]
-    float* part_ml = reinterpret_cast<float*>(terminal_k + kHalfBytes + warp * 2048);   // [4][2]
+    uint8_t* terminal_k = smem + kVBytes;  // K tile of stage 0; group g parks in the K tile of stage g
+    uint8_t* group_k = terminal_k + group * kStageBytes;
+    float* part_o = reinterpret_cast<float*>(group_k + gw * 2048);                 // [4][128]
+    float* part_ml = reinterpret_cast<float*>(group_k + kHalfBytes + gw * 2048);   // [4][2]
     if (row_ok) {
 #pragma unroll
         for (int n = 0; n < 16; ++n)
@@ -514,6 +585,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
         if (quad == 0) *reinterpret_cast<float2*>(part_ml + qrow * 2) = make_float2(row_max, row_sum);
     }
     consumer_barrier();  // all K/V readers are done: the terminal V region changes owner here
+    if (threadIdx.x >= kMergeThreads) return;  // the epilogue is the work of four warps
 
     const int tid = threadIdx.x;
     const int row = tid >> 5;        // query head within the group
@@ -523,7 +595,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
         float m_all = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kConsumerWarps; ++w) {
-            const float2 ml = *reinterpret_cast<const float2*>(terminal_k + kHalfBytes + w * 2048 + row * 8);
+            const uint8_t* parked = terminal_k + (w / kGroupWarps) * kStageBytes + (w % kGroupWarps) * 2048;
+            const float2 ml = *reinterpret_cast<const float2*>(parked + kHalfBytes + row * 8);
             m_w[w] = ml.x;
             l_w[w] = ml.y;
             m_all = fmaxf(m_all, ml.x);
@@ -533,7 +606,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
 #pragma unroll
         for (int w = 0; w < kConsumerWarps; ++w) {
             const float weight = m_w[w] == -INFINITY ? 0.f : tc::fast_exp2((m_w[w] - m_all) * p.scale_log2);
-            const float4 v = *reinterpret_cast<const float4*>(terminal_k + w * 2048 + row * 512 + col4 * 16);
+            const float4 v = *reinterpret_cast<const float4*>(
+                terminal_k + (w / kGroupWarps) * kStageBytes + (w % kGroupWarps) * 2048 + row * 512 + col4 * 16);
             l_all = fmaf(weight, l_w[w], l_all);
             acc.x = fmaf(weight, v.x, acc.x);
             acc.y = fmaf(weight, v.y, acc.y);
@@ -545,7 +619,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
         *reinterpret_cast<float4*>(stage_o + row * kDim + col4 * 4) = acc;
         if (col4 == 0) stage_lse[row] = l_all > 0.f ? fmaf(m_all, p.scale, logf(l_all)) : -INFINITY;
     }
-    consumer_barrier();  // publish the four output rows and their LSE together
+    merge_barrier();  // publish the four output rows and their LSE together
+    TC_TRACE_POINT(21);
 
     const int64_t head_slot = int64_t(b) * p.kv_heads + kvh;  // index of the (batch, KV head) pair
     float4 final_o;
@@ -558,9 +633,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
             *reinterpret_cast<uint4*>(p.ws_lse + slot * kGroup) = *reinterpret_cast<const uint4*>(stage_lse);
         // The barrier orders every thread's partial stores before thread 0's release; the last
         // arriver's acquire, followed by the second barrier, orders them before the merge loads.
-        consumer_barrier();
+        merge_barrier();
         if (tid == 0) *flag = tc::atomic_add_acq_rel(p.tickets + head_slot, 1) == p.splits - 1;
-        consumer_barrier();
+        merge_barrier();
+        TC_TRACE_POINT(22);
         if (!*flag) return;
         // Last CTA of this (batch, KV head): LSE-weighted merge of every split's partial. Warp w owns
         // output row w: its lanes first fetch that row's split LSEs together (one L2 round trip),
@@ -589,6 +665,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
 #pragma unroll
         for (int offset = 16; offset > 0; offset >>= 1)
             lse_max = fmaxf(lse_max, __shfl_xor_sync(0xffffffffu, lse_max, offset));
+        TC_TRACE_POINT(28);
         float total = 0.f;
 #pragma unroll
         for (int i = 0; i < kMaxSplits / 32; ++i) {
@@ -617,10 +694,13 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
                 }
             }
         }
+        TC_TRACE_POINT(29);
         const float inv = total > 0.f ? 1.f / total : 0.f;
         final_o = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         final_lse = total > 0.f ? lse_max + logf(total) : -INFINITY;
-        if (tid == 0) atomicExch(p.tickets + head_slot, 0);
+        // Every split of this head has taken its ticket: a plain store re-arms the counter for the next launch
+        // (an atomic exchange would keep this CTA, and with it the end of the kernel, waiting for its return).
+        if (tid == 0) p.tickets[head_slot] = 0;
     } else {
         final_o = *reinterpret_cast<const float4*>(stage_o + row * kDim + col4 * 4);
         final_lse = stage_lse[row];
@@ -687,7 +767,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
         packed.y = tc::pack_bf16x2(merged.z, merged.w);
         *reinterpret_cast<uint2*>(p.out + out_row * kDim + col4 * 4) = packed;
         if (col4 == 0) p.lse[out_row] = merged_lse;
-        consumer_barrier();  // every thread has read the unit's epoch before it moves on
+        merge_barrier();  // every thread has read the unit's epoch before it moves on
         if (tid == 0) epochs[unit] = epoch;
     } else if (p.partial) {
         *reinterpret_cast<float4*>(p.partial_o + out_row * kDim + col4 * 4) = final_o;
@@ -699,6 +779,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
         *reinterpret_cast<uint2*>(p.out + out_row * kDim + col4 * 4) = packed;
         if (col4 == 0) p.lse[out_row] = final_lse == -INFINITY ? INFINITY : final_lse;
     }
+    TC_TRACE_POINT(19);
 }
 
 // Standalone merge of `parts` partial results (used after the multi-GPU all-gather).
@@ -1157,6 +1238,11 @@ int tc_decode_forward_out_static(int device, void* stream, const void* q, void* 
     return decode_static(device, stream, q, kcache, vcache, knew, vnew, old_lengths, out, lse, batch, capacity,
                          kv_heads, num_splits, mapping, append);
 }
+
+#ifdef TC_TRACE
+// Trace builds only: copies the 1024 x 32 table of time stamps to `host` (synchronises the device).
+int tc_debug_trace(void* host) { return cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace)) == cudaSuccess ? 0 : 1; }
+#endif
 
 int tc_decode_static_status_word(int device, int32_t** word) {
     TC_REQUIRE(word, "null output");

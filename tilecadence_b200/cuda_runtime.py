@@ -90,11 +90,12 @@ def staged_sources(phase):
     return files
 
 
-def _compile(units, include_dirs, files, verbose=False):
+def _compile(units, include_dirs, files, verbose=False, defines=()):
     """Compile ``units`` into one cached shared object; needs nvcc but no GPU.
 
-    The cache key covers the named source files and the flags only, so a library built on a
-    machine without a GPU is found again on the GPU machine from the same sources.
+    The cache key covers the named source files, the flags and the ``defines`` (preprocessor symbols for
+    diagnostic builds) only, so a library built on a machine without a GPU is found again on the GPU
+    machine from the same sources.
     """
     compiler = "unknown"
     nvcc = find_nvcc()
@@ -103,7 +104,7 @@ def _compile(units, include_dirs, files, verbose=False):
     identity = {
         "source_sha256": {name: file_sha256(path) for name, path in sorted(files.items())},
         "target": TARGET,
-        "cuda_flags": list(CUDA_FLAGS),
+        "cuda_flags": list(CUDA_FLAGS) + [f"-D{symbol}" for symbol in defines],
     }
     key = sha256(json.dumps(identity, sort_keys=True).encode()).hexdigest()[:20]
     identity["cuda_compiler"] = compiler
@@ -116,7 +117,7 @@ def _compile(units, include_dirs, files, verbose=False):
                                    f"matches these sources ({library.name})")
             BUILD_DIR.mkdir(parents=True, exist_ok=True)
             temporary = library.with_name(f"{library.stem}.{os.getpid()}.tmp.so")
-            command = [str(nvcc), *CUDA_FLAGS]
+            command = [str(nvcc), *CUDA_FLAGS, *(f"-D{symbol}" for symbol in defines)]
             if verbose:
                 command.append("-Xptxas=-v")
             for directory in include_dirs:
@@ -132,7 +133,7 @@ def _compile(units, include_dirs, files, verbose=False):
     return library, identity
 
 
-def compile_directory(source_dir, verbose=False):
+def compile_directory(source_dir, verbose=False, defines=()):
     """Compile every .cu of a flat emitted directory. Returns ``(library_path, identity)``."""
     source_dir = Path(source_dir).resolve()
     files = {path.name: path for path in sorted(source_dir.iterdir())
@@ -140,7 +141,7 @@ def compile_directory(source_dir, verbose=False):
     units = [path for path in files.values() if path.suffix == ".cu"]
     if not units:
         raise ValueError(f"No generated CUDA translation unit in {source_dir}")
-    return _compile(units, [source_dir], files, verbose)
+    return _compile(units, [source_dir], files, verbose, defines)
 
 
 def compile_tree(verbose=False):
