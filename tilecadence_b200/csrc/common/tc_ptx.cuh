@@ -362,6 +362,8 @@ __device__ __forceinline__ void mma_bf16_16816_rows8(float& d0, float& d1, uint3
         "{%0, %1, %9, %9};"
         : "+f"(d0), "+f"(d1), "=f"(unused2), "=f"(unused3)
         : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.f));
+    (void)unused2;
+    (void)unused3;
 }
 
 // ----------------------------------------------------------------------------- conversions / math

@@ -2,17 +2,19 @@
 //
 // Path replaced: tilecadence/cuda/prefill/prefill.cu:21-43,122-152 (CTA mapping, host checks,
 // launch), long_prefill_rowblock.cuh:117-605 (the row-block kernel: QK^T, online softmax with a
-// gated rescale :68-115, PV, O staged over the CTA's own Q :513-524, both heads' LSE staged in the
-// released terminal K span :539-587) and common.cuh:36-78 (tensor checks).
+// gated rescale :68-115, PV, O staged in shared memory for 16-byte stores :513-524, both heads' LSE staged
+// in the released terminal K span :539-587) and common.cuh:36-78 (tensor checks).
 //
-// One CTA owns a 128-row query tile of the two query heads that share a KV head pair slot, so one
-// K/V tile in shared memory feeds both heads. The two dense contractions run on the 5th-generation
+// A unit of work is a 128-row query tile of the two query heads that share a KV head pair slot, so one
+// K/V tile in shared memory feeds both heads. One persistent CTA per SM works through a list of units
+// dealt from the longest-first order; the loads and the first MMAs of a unit overlap the epilogue of the
+// unit before it. The two dense contractions run on the 5th-generation
 // tensor cores: S = Q_h K^T as a shared x shared tcgen05.mma into one 128-column score buffer in TMEM
 // that the two heads use in strict alternation, O_h += P_h V as a TMEM x shared tcgen05.mma with P_h
 // (BF16) in columns of its own. TMEM: S | P0 P1 | O0 | O1 = 128 + 2*64 + 2*128 = all 512 columns. Roles:
 //   warps 0-3  softmax for head 0 (one query row per thread, TMEM lane = row)
 //   warps 4-7  softmax for head 1
-//   warp  8    TMA producer: Q once, then a 2-stage K ring and a 2-stage V ring (128-byte swizzle)
+//   warp  8    TMA producer: Q of each unit, a 2-stage K ring and a 2-stage V ring (128-byte swizzle)
 //   warp  9    issues every score MMA (one elected thread; the warp also owns TMEM)
 //   warps 10,11 issue PV for head 0 / head 1 (one elected thread each)
 // The third warpgroup gives most of its registers to the softmax warpgroups (setmaxnreg). Score
@@ -21,8 +23,9 @@
 // softmax is bound by the exponential unit (16 results per clock per SM against 8192 MMA flops), so
 // the two warpgroups take turns at it (named barriers). A head may rewrite the first half of its P as
 // soon as the first half of the previous PV has retired. Key tiles go from the diagonal down to 0; the
-// ring index is chosen so that the final tile always uses stage 0: that stage is the "terminal K" donor
-// whose bytes receive the two 512-byte LSE arrays in the epilogue.
+// ring index is chosen so that a unit's final tile always uses stage 0: that stage is the "terminal K" donor
+// whose bytes receive the two 512-byte LSE arrays as soon as the unit's last softmax is done. The BF16 output
+// tile of a head leaves through a 32 KiB staging buffer that the two heads use in turn.
 #include "config.cuh"
 #include "tc_host.cuh"
 #include "tc_ptx.cuh"
@@ -41,7 +44,6 @@ constexpr int kHalfBytes = kTileBytes / 2;    // 64 of the 128 head-dim elements
 constexpr int kQOffset = 0;
 constexpr int kKOffset = 2 * kTileBytes;
 constexpr int kVOffset = kKOffset + kStages * kTileBytes;
-constexpr int kBarrierOffset = kVOffset + kStages * kTileBytes;
 constexpr int kBarrierBytes = 256;
 constexpr int kStagingBytes = 1024;           // dedicated LSE staging when the handoff is disabled
 constexpr int kSoftmaxThreads = 128;
@@ -93,12 +95,18 @@ static_assert(PREFILL_LSE_HEAD0_OFFSET_BYTES + 512 <= PREFILL_LSE_HEAD1_OFFSET_B
                   PREFILL_LSE_HEAD1_OFFSET_BYTES + 512 <= PREFILL_LSE_HEAD0_OFFSET_BYTES,
               "LSE regions must not overlap");
 
+constexpr int kOutStageOffset = kVOffset + kStages * kTileBytes;  // one 128 x 128 BF16 tile, used by the heads in turn
+constexpr int kBarrierOffset = kOutStageOffset + kTileBytes;
 constexpr int shared_bytes(bool handoff) { return 1024 + kBarrierOffset + kBarrierBytes + (handoff ? 0 : kStagingBytes); }
+static_assert(shared_bytes(false) <= 227 * 1024, "the schedule must fit the 227 KiB a CTA can have");
 
 struct Barriers {
-    uint64_t q_full;
+    uint64_t q_full, q_empty;
     uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
     uint64_t s_full[2], s_free[2], p_half[2][2], p_lo_free[2], o_done[2];
+    uint64_t o_free[2];          // the epilogue has read head h's accumulator out of tensor memory
+    uint64_t lse_drained;        // both heads' LSE arrays have left the terminal K stage
+    uint64_t stage_drained[2];   // head h's output tile has left the staging buffer
     uint32_t tmem_base;
     int32_t abort;
     int32_t role[2];  // key-split only: which of the two CTAs of a query tile claimed each head first
@@ -109,6 +117,7 @@ struct PrefillParams {
     float* lse;
     int32_t* status;
     int batch, tokens, q_heads, kv_heads, m_blocks;
+    int total_units;  // work units of the launch: (query tile, batch, KV head, head pair[, key part]), longest first
     float scale, scale_log2;
     // Key-split launches only: per (query tile, head) a claim counter and a ready word (zeroed before the
     // launch), 128 x 128 normalised fp32 O values stored as [32 column groups][128 rows] float4, 128 LSEs.
@@ -127,10 +136,58 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
-// kSplit: two CTAs per query tile, the first takes the key tiles nearest the diagonal (rounded up), the
-// second the rest; whichever finishes a head second merges the other's normalised O and LSE into its own
-// (LSE-weighted) and stores. For launches whose query tiles are too few to fill the GPU, where the longest
-// tile alone would set the run time.
+// Uses of the two ring stages so far, kept in two registers (an indexed array would live in local memory).
+struct StageCounts {
+    uint32_t stage0 = 0, stage1 = 0;
+    __device__ __forceinline__ uint32_t of(int stage) const { return stage == 0 ? stage0 : stage1; }
+    __device__ __forceinline__ void bump(int stage) {
+        if (stage == 0) ++stage0; else ++stage1;
+    }
+};
+static_assert(kStages == 2, "StageCounts holds two stages");
+
+// One unit of work: a 128-row query tile of the two heads of a pair slot and the key tiles it attends to
+// (all of them, or with kSplit one of two parts: part 0 the tiles nearest the diagonal, rounded up).
+struct Unit {
+    int m_block, part, pair, kvh, b, head0, m0, all_tiles, n_tiles, key_block0;
+};
+template <bool kSplit>
+__device__ __forceinline__ Unit unit_at(const PrefillParams& p, int index) {
+    // Longest query tiles first; neighbouring units share a KV head so K/V tiles hit in L2.
+    Unit u;
+    const int per_block = p.batch * p.kv_heads * 2 * (kSplit ? 2 : 1);
+    u.m_block = p.m_blocks - 1 - index / per_block;
+    int rest = index % per_block;
+    u.part = kSplit ? (rest & 1) : 0;
+    if (kSplit) rest >>= 1;
+    u.pair = rest & 1;
+    u.kvh = (rest >> 1) % p.kv_heads;
+    u.b = rest / (2 * p.kv_heads);
+    u.head0 = u.kvh * kGroup + u.pair * 2;
+    u.m0 = u.m_block * kBlockM;
+    // Key tiles m_block, m_block-1, ..., 0; this unit's share is n_tiles of them starting at key_block0.
+    u.all_tiles = u.m_block + 1;
+    const int near_tiles = kSplit ? (u.all_tiles + 1) / 2 : u.all_tiles;
+    u.n_tiles = u.part == 0 ? near_tiles : u.all_tiles - near_tiles;
+    u.key_block0 = u.part == 0 ? u.m_block : u.m_block - near_tiles;
+    return u;
+}
+// Units are dealt to the CTAs of the (persistent) grid in rounds that change direction, so that every CTA gets
+// a similar amount of work from the sorted list. Returns -1 when the round has no unit for this CTA.
+__device__ __forceinline__ int unit_of_round(int round, int total_units) {
+    const int grid = int(gridDim.x), cta = int(blockIdx.x);
+    const int index = round * grid + ((round & 1) ? grid - 1 - cta : cta);
+    return index < total_units ? index : -1;
+}
+
+// Persistent kernel: one CTA per SM works through its units. Barrier phases run on across units (every waiter
+// sees every phase of the barriers it waits on, in order, and keeps its own count), so the TMA producer and the
+// MMA issuers move on to the next unit while the softmax warpgroups are still in the epilogue of the current
+// one: Q of the next unit is loaded as soon as the last score MMA has read the current Q, K/V tiles as soon as
+// ring stages are free, and the first score MMA of the next unit is issued as soon as the score buffer is.
+// kSplit: two units per query tile (see Unit); whichever CTA finishes a head second merges the other's
+// normalised O and LSE into its own (LSE-weighted) and stores. For launches whose query tiles are too few to
+// fill the GPU, where the longest tile alone would set the run time.
 template <bool kHandoff, bool kSplit = false>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
@@ -141,64 +198,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kBarrierOffset);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rounds = (p.total_units + int(gridDim.x) - 1) / int(gridDim.x);
 
-    // Longest query tiles first; neighbouring CTAs share a KV head so K/V tiles hit in L2.
-    const int per_block = p.batch * p.kv_heads * 2 * (kSplit ? 2 : 1);
-    const int m_block = p.m_blocks - 1 - int(blockIdx.x) / per_block;
-    int rest = int(blockIdx.x) % per_block;
-    const int part = kSplit ? (rest & 1) : 0;
-    if (kSplit) rest >>= 1;
-    const int pair = rest & 1;
-    const int kvh = (rest >> 1) % p.kv_heads;
-    const int b = rest / (2 * p.kv_heads);
-    const int head0 = kvh * kGroup + pair * 2;
-    const int m0 = m_block * kBlockM;
-    // Key tiles m_block, m_block-1, ..., 0; this CTA's share is n_tiles of them starting at key_block0.
-    const int all_tiles = m_block + 1;
-    const int near_tiles = kSplit ? (all_tiles + 1) / 2 : all_tiles;
-    const int n_tiles = part == 0 ? near_tiles : all_tiles - near_tiles;
-    const int key_block0 = part == 0 ? m_block : m_block - near_tiles;
-    if (kSplit && n_tiles == 0) return;  // a one-tile row block has nothing to split
-
-    // The TMA producer owns the operand barriers: it initialises them itself and sends for Q and for
-    // the first ring stages at once, so the first loads are in flight while the other warps set up
-    // their barriers and tensor memory. Everything else waits for the CTA barrier below.
-    const uint64_t keep = tc::policy_evict_last(), stream_once = tc::policy_evict_first();
-    auto load_kv = [&](int it) {
-        const int stage = (n_tiles - 1 - it) % kStages;
-        const int n0 = (key_block0 - it) * kBlockN;
-        uint8_t* kdst = smem + kKOffset + stage * kTileBytes;
-        tc::mbar_arrive_expect_tx(&bars->k_full[stage], kTileBytes);
-        tc::tma_load_4d(kdst, &kmap, &bars->k_full[stage], 0, kvh, n0, b, keep);
-        tc::tma_load_4d(kdst + kHalfBytes, &kmap, &bars->k_full[stage], 64, kvh, n0, b, keep);
-        return stage;
-    };
-    auto load_v = [&](int it, int stage) {
-        const int n0 = (key_block0 - it) * kBlockN;
-        uint8_t* vdst = smem + kVOffset + stage * kTileBytes;
-        tc::mbar_arrive_expect_tx(&bars->v_full[stage], kTileBytes);
-        tc::tma_load_4d(vdst, &vmap, &bars->v_full[stage], 0, kvh, n0, b, keep);
-        tc::tma_load_4d(vdst + kHalfBytes, &vmap, &bars->v_full[stage], 64, kvh, n0, b, keep);
-    };
     if (threadIdx.x == kProducerWarp * 32) {
         tc::mbar_init(&bars->q_full, 1);
+        tc::mbar_init(&bars->q_empty, 1);
         for (int s = 0; s < kStages; ++s) {
             tc::mbar_init(&bars->k_full[s], 1);
-            tc::mbar_init(&bars->k_empty[s], 2);  // one arrival per head's MMA issuer
+            tc::mbar_init(&bars->k_empty[s], 2);  // one arrival per head's score MMA
             tc::mbar_init(&bars->v_full[s], 1);
-            tc::mbar_init(&bars->v_empty[s], 2);
+            tc::mbar_init(&bars->v_empty[s], 2);  // one arrival per head's PV issuer
         }
+        tc::mbar_init(&bars->lse_drained, 2);
         tc::mbar_fence_init();
         tc::tma_prefetch_desc(&qmap);
         tc::tma_prefetch_desc(&kmap);
         tc::tma_prefetch_desc(&vmap);
-        tc::mbar_arrive_expect_tx(&bars->q_full, 2 * kTileBytes);
-        for (int h = 0; h < 2; ++h) {
-            uint8_t* dst = smem + kQOffset + h * kTileBytes;
-            tc::tma_load_4d(dst, &qmap, &bars->q_full, 0, head0 + h, m0, b, stream_once);
-            tc::tma_load_4d(dst + kHalfBytes, &qmap, &bars->q_full, 64, head0 + h, m0, b, stream_once);
-        }
-        for (int it = 0; it < kStages && it < n_tiles; ++it) load_v(it, load_kv(it));  // fresh stages: nothing to wait for
     }
     if (threadIdx.x == 0) {
         for (int h = 0; h < 2; ++h) {
@@ -208,6 +223,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             tc::mbar_init(&bars->p_half[h][1], kSoftmaxThreads);
             tc::mbar_init(&bars->o_done[h], 1);
             tc::mbar_init(&bars->p_lo_free[h], 1);
+            tc::mbar_init(&bars->o_free[h], kSoftmaxThreads);
+            tc::mbar_init(&bars->stage_drained[h], 1);
         }
         bars->abort = 0;
         tc::mbar_fence_init();
@@ -229,13 +246,50 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            for (int it = kStages; it < n_tiles; ++it) {
-                const int stage = (n_tiles - 1 - it) % kStages;
-                const uint32_t parity = (uint32_t(it / kStages) & 1) ^ 1;
-                if (!tc::mbar_wait(&bars->k_empty[stage], parity)) { atomicCAS(p.status, 0, 11); break; }
-                load_kv(it);
-                if (!tc::mbar_wait(&bars->v_empty[stage], parity)) { atomicCAS(p.status, 0, 12); break; }
-                load_v(it, stage);
+            const uint64_t keep = tc::policy_evict_last(), stream_once = tc::policy_evict_first();
+            StageCounts k_uses, v_uses;  // loads issued into each ring stage so far
+            uint32_t units_done = 0;
+            bool ok = true;
+            for (int round = 0; ok && round < rounds; ++round) {
+                const int index = unit_of_round(round, p.total_units);
+                if (index < 0) continue;
+                const Unit u = unit_at<kSplit>(p, index);
+                if (u.n_tiles == 0) continue;  // a one-tile row block has nothing to split
+                // Q: the score MMAs of the previous unit must have read the previous Q.
+                if (units_done > 0 && !(ok = tc::mbar_wait(&bars->q_empty, (units_done - 1) & 1))) break;
+                tc::mbar_arrive_expect_tx(&bars->q_full, 2 * kTileBytes);
+                for (int h = 0; h < 2; ++h) {
+                    uint8_t* dst = smem + kQOffset + h * kTileBytes;
+                    tc::tma_load_4d(dst, &qmap, &bars->q_full, 0, u.head0 + h, u.m0, u.b, stream_once);
+                    tc::tma_load_4d(dst + kHalfBytes, &qmap, &bars->q_full, 64, u.head0 + h, u.m0, u.b, stream_once);
+                }
+                bool terminal_checked = units_done == 0;
+                for (int it = 0; it < u.n_tiles; ++it) {
+                    const int stage = (u.n_tiles - 1 - it) % kStages;  // the unit's last tile always lands in stage 0
+                    const int n0 = (u.key_block0 - it) * kBlockN;
+                    if (k_uses.of(stage) > 0 && !(ok = tc::mbar_wait(&bars->k_empty[stage], (k_uses.of(stage) - 1) & 1))) break;
+                    if (stage == 0 && !terminal_checked) {
+                        // Stage 0 was the previous unit's terminal K stage: its LSE arrays must have left it.
+                        if (!(ok = tc::mbar_wait(&bars->lse_drained, (units_done - 1) & 1))) break;
+                        terminal_checked = true;
+                    }
+                    uint8_t* kdst = smem + kKOffset + stage * kTileBytes;
+                    tc::mbar_arrive_expect_tx(&bars->k_full[stage], kTileBytes);
+                    tc::tma_load_4d(kdst, &kmap, &bars->k_full[stage], 0, u.kvh, n0, u.b, keep);
+                    tc::tma_load_4d(kdst + kHalfBytes, &kmap, &bars->k_full[stage], 64, u.kvh, n0, u.b, keep);
+                    k_uses.bump(stage);
+                    if (v_uses.of(stage) > 0 && !(ok = tc::mbar_wait(&bars->v_empty[stage], (v_uses.of(stage) - 1) & 1))) break;
+                    uint8_t* vdst = smem + kVOffset + stage * kTileBytes;
+                    tc::mbar_arrive_expect_tx(&bars->v_full[stage], kTileBytes);
+                    tc::tma_load_4d(vdst, &vmap, &bars->v_full[stage], 0, u.kvh, n0, u.b, keep);
+                    tc::tma_load_4d(vdst + kHalfBytes, &vmap, &bars->v_full[stage], 64, u.kvh, n0, u.b, keep);
+                    v_uses.bump(stage);
+                }
+                ++units_done;
+            }
+            if (!ok) {
+                atomicCAS(p.status, 0, 11);
+                bars->abort = 1;
             }
         }
     } else {
@@ -248,37 +302,48 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         if (lane == 0) {
             constexpr uint32_t idesc_qk = tc::umma_idesc(128, 128, 1, 0, 0);
             constexpr uint32_t idesc_pv = tc::umma_idesc(128, 128, 1, 0, 1);
-            auto stage_of = [&](int it) { return (n_tiles - 1 - it) % kStages; };
-            auto parity_of = [&](int it) { return uint32_t(it / kStages) & 1; };
+            StageCounts uses;  // tiles taken from each ring stage so far (K for warp 9, V for 10 and 11)
+            uint32_t tiles_done = 0, units_done = 0;
             bool ok = true;
             if (warp == kMmaWarp) {
-                // S = Q_h K^T into the shared score buffer: both operands K-major, 8 steps of 16 along D
+                // S = Q_h K^T into the score buffer: both operands K-major, 8 steps of 16 along D
                 // (4 per 64-element half). A score MMA may overwrite the buffer once the other head's
                 // softmax warpgroup has pulled its tile into registers; because P has its own columns it
                 // does not wait for any PV.
                 const uint32_t q_addr = tc::smem_u32(smem + kQOffset);
                 const uint32_t k_addr = tc::smem_u32(smem + kKOffset);
-                ok = tc::mbar_wait(&bars->q_full, 0);
-                for (int it = 0; ok && it < n_tiles; ++it) {
-                    if (!(ok = tc::mbar_wait(&bars->k_full[stage_of(it)], parity_of(it)))) break;
-                    const uint32_t kb = k_addr + stage_of(it) * kTileBytes;
-                    for (int h = 0; h < 2 && ok; ++h) {
-                        if (h == 0) {
-                            if (it > 0) ok = tc::mbar_wait(&bars->s_free[1], uint32_t(it - 1) & 1);
-                        } else {
-                            ok = tc::mbar_wait(&bars->s_free[0], uint32_t(it) & 1);
-                        }
-                        if (!ok) break;
-                        tc::tc_fence_after_sync();
+                for (int round = 0; ok && round < rounds; ++round) {
+                    const int index = unit_of_round(round, p.total_units);
+                    if (index < 0) continue;
+                    const Unit u = unit_at<kSplit>(p, index);
+                    if (u.n_tiles == 0) continue;
+                    if (!(ok = tc::mbar_wait(&bars->q_full, units_done & 1))) break;
+                    for (int it = 0; ok && it < u.n_tiles; ++it) {
+                        const int stage = (u.n_tiles - 1 - it) % kStages;
+                        if (!(ok = tc::mbar_wait(&bars->k_full[stage], uses.of(stage) & 1))) break;
+                        uses.bump(stage);
+                        const uint32_t kb = k_addr + stage * kTileBytes;
+                        for (int h = 0; h < 2 && ok; ++h) {
+                            if (h == 0) {
+                                if (tiles_done > 0) ok = tc::mbar_wait(&bars->s_free[1], (tiles_done - 1) & 1);
+                            } else {
+                                ok = tc::mbar_wait(&bars->s_free[0], tiles_done & 1);
+                            }
+                            if (!ok) break;
+                            tc::tc_fence_after_sync();
 #pragma unroll
-                        for (int ks = 0; ks < 8; ++ks) {
-                            const uint32_t off = uint32_t(ks >> 2) * kHalfBytes + uint32_t(ks & 3) * 32;
-                            tc::umma_ss(tmem + s_column(h), tc::umma_desc_sw128(q_addr + h * kTileBytes + off, 16, 1024),
-                                        tc::umma_desc_sw128(kb + off, 16, 1024), idesc_qk, ks > 0);
+                            for (int ks = 0; ks < 8; ++ks) {
+                                const uint32_t off = uint32_t(ks >> 2) * kHalfBytes + uint32_t(ks & 3) * 32;
+                                tc::umma_ss(tmem + s_column(h), tc::umma_desc_sw128(q_addr + h * kTileBytes + off, 16, 1024),
+                                            tc::umma_desc_sw128(kb + off, 16, 1024), idesc_qk, ks > 0);
+                            }
+                            tc::umma_commit(&bars->s_full[h]);
+                            tc::umma_commit(&bars->k_empty[stage]);  // two arrivals per stage: one per head
                         }
-                        tc::umma_commit(&bars->s_full[h]);
-                        tc::umma_commit(&bars->k_empty[stage_of(it)]);  // two arrivals per stage: one per head
+                        ++tiles_done;
                     }
+                    if (ok) tc::umma_commit(&bars->q_empty);  // every score MMA of this unit has read Q
+                    ++units_done;
                 }
             } else {
                 // O_h += P_h V, one 64-key half at a time: P from TMEM (8 columns per 16 keys), V MN-major
@@ -287,26 +352,39 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 const uint32_t v_addr = tc::smem_u32(smem + kVOffset);
                 const uint32_t p_col = tmem + p_column(h);
                 const uint32_t o_col = tmem + o_column(h);
-                auto issue_pv_half = [&](int it, int half) {
-                    const uint32_t vb = v_addr + stage_of(it) * kTileBytes;
+                for (int round = 0; ok && round < rounds; ++round) {
+                    const int index = unit_of_round(round, p.total_units);
+                    if (index < 0) continue;
+                    const Unit u = unit_at<kSplit>(p, index);
+                    if (u.n_tiles == 0) continue;
+                    for (int it = 0; ok && it < u.n_tiles; ++it) {
+                        const int stage = (u.n_tiles - 1 - it) % kStages;
+                        const uint32_t vb = v_addr + stage * kTileBytes;
+                        auto issue_pv_half = [&](int half) {
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4) {
-                        const int ks = half * 4 + k4;
-                        tc::umma_ts(o_col, p_col + uint32_t(ks) * 8, tc::umma_desc_sw128(vb + ks * 2048, kHalfBytes, 1024),
-                                    idesc_pv, !(it == 0 && ks == 0));
+                            for (int k4 = 0; k4 < 4; ++k4) {
+                                const int ks = half * 4 + k4;
+                                tc::umma_ts(o_col, p_col + uint32_t(ks) * 8, tc::umma_desc_sw128(vb + ks * 2048, kHalfBytes, 1024),
+                                            idesc_pv, !(it == 0 && ks == 0));
+                            }
+                        };
+                        if (!(ok = tc::mbar_wait(&bars->v_full[stage], uses.of(stage) & 1))) break;
+                        uses.bump(stage);
+                        // The first PV of a unit overwrites the accumulator: the previous unit's epilogue must
+                        // have read it out of tensor memory.
+                        if (it == 0 && units_done > 0 && !(ok = tc::mbar_wait(&bars->o_free[h], (units_done - 1) & 1))) break;
+                        if (!(ok = tc::mbar_wait(&bars->p_half[h][0], tiles_done & 1))) break;
+                        tc::tc_fence_after_sync();
+                        issue_pv_half(0);
+                        tc::umma_commit(&bars->p_lo_free[h]);  // P columns of the first 64 keys may be rewritten
+                        if (!(ok = tc::mbar_wait(&bars->p_half[h][1], tiles_done & 1))) break;
+                        tc::tc_fence_after_sync();
+                        issue_pv_half(1);
+                        tc::umma_commit(&bars->o_done[h]);
+                        tc::umma_commit(&bars->v_empty[stage]);
+                        ++tiles_done;
                     }
-                };
-                for (int it = 0; ok && it < n_tiles; ++it) {
-                    if (!(ok = tc::mbar_wait(&bars->v_full[stage_of(it)], parity_of(it)))) break;
-                    if (!(ok = tc::mbar_wait(&bars->p_half[h][0], uint32_t(it) & 1))) break;
-                    tc::tc_fence_after_sync();
-                    issue_pv_half(it, 0);
-                    tc::umma_commit(&bars->p_lo_free[h]);  // P columns of the first 64 keys may be rewritten
-                    if (!(ok = tc::mbar_wait(&bars->p_half[h][1], uint32_t(it) & 1))) break;
-                    tc::tc_fence_after_sync();
-                    issue_pv_half(it, 1);
-                    tc::umma_commit(&bars->o_done[h]);
-                    tc::umma_commit(&bars->v_empty[stage_of(it)]);
+                    ++units_done;
                 }
             }
             if (!ok) {
@@ -324,13 +402,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         const uint32_t s_tmem = tmem + lane_field + s_column(h);
         const uint32_t p_tmem = tmem + lane_field + p_column(h);
         const uint32_t o_tmem = tmem + lane_field + o_column(h);
-        const int head = head0 + h;
         const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
-        float m_used = -INFINITY, l = 0.f;
+        // Tiles of all of this CTA's units: the two heads take turns at the exponential unit from the first tile
+        // of the first unit to the last tile of the last one.
+        uint32_t cta_tiles = 0;
+        for (int round = 0; round < rounds; ++round) {
+            const int index = unit_of_round(round, p.total_units);
+            if (index >= 0) cta_tiles += uint32_t(unit_at<kSplit>(p, index).n_tiles);
+        }
+        uint32_t tiles_done = 0, units_done = 0, terminal_uses = 0;  // terminal_uses: tiles that went through K stage 0
         bool ok = true;
 
-        for (int it = 0; it < n_tiles; ++it) {
-            if (ok) ok = tc::mbar_wait(&bars->s_full[h], uint32_t(it) & 1);  // after a failed wait: keep the barrier pattern, skip waits
+        for (int round = 0; round < rounds; ++round) {
+        const int index = unit_of_round(round, p.total_units);
+        if (index < 0) continue;
+        const Unit u = unit_at<kSplit>(p, index);
+        if (u.n_tiles == 0) continue;
+        const int n_tiles = u.n_tiles, part = u.part, m0 = u.m0, b = u.b;
+        const int head = u.head0 + h;
+        float m_used = -INFINITY, l = 0.f;
+
+        for (int it = 0; it < n_tiles; ++it, ++tiles_done) {
+            if ((n_tiles - 1 - it) % kStages == 0) ++terminal_uses;
+            if (ok) ok = tc::mbar_wait(&bars->s_full[h], tiles_done & 1);  // after a failed wait: keep the barrier pattern, skip waits
             tc::tc_fence_after_sync();
             float s[128];
 #pragma unroll
@@ -390,13 +484,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             // before chunk 0 is rewritten, all of it before chunk 2 is rewritten or O is rescaled. Waiting
             // only for the first half here takes the second half's execution off this head's
             // exp -> PV -> exp chain; the full wait follows before chunk 2, by when it has long finished.
+            // (The first tile of a unit follows an epilogue that has already waited for the previous unit's
+            // last PV.)
             bool pv_done = it == 0;
             if (it > 0) {
                 if (rescale) {
-                    if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1);
+                    if (ok) ok = tc::mbar_wait(&bars->o_done[h], (tiles_done - 1) & 1);
                     pv_done = true;
                 } else {
-                    if (ok) ok = tc::mbar_wait(&bars->p_lo_free[h], uint32_t(it - 1) & 1);
+                    if (ok) ok = tc::mbar_wait(&bars->p_lo_free[h], (tiles_done - 1) & 1);
                 }
                 tc::tc_fence_after_sync();
                 if (rescale) {
@@ -416,7 +512,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             // The exponential unit is the scarcest resource, so the two heads take turns at it: while
             // one warpgroup exponentiates, the other head's P is being consumed by the tensor pipe
             // and its next S tile is produced. Head 0 goes first on every tile.
-            if (h == 1 || it > 0) {
+            if (h == 1 || tiles_done > 0) {
                 // Hardware named barrier: the other warpgroup's 128 threads arrive without blocking when
                 // their exponentials are issued, this warpgroup's 128 threads wait. It wakes faster than
                 // an mbarrier wait; both sides execute it on every path so the counts always match.
@@ -428,7 +524,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 chunk(c, packed);
                 // Hand the exponential unit over when this head's last exponentials are issued: the
                 // other warpgroup needs about a hundred cycles to wake up.
-                if (c == 3 && (h == 0 || it + 1 < n_tiles))
+                if (c == 3 && (h == 0 || tiles_done + 1 < cta_tiles))
                     asm volatile("bar.arrive %0, 256;" ::"r"(3 + (1 - h)) : "memory");
                 if (c == 2) {
                     // Chunks 0 and 1 were stored a whole chunk of arithmetic ago, so this wait is short.
@@ -437,7 +533,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     tc::mbar_arrive(&bars->p_half[h][0]);
                 }
                 if (c == 2 && !pv_done) {
-                    if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1);
+                    if (ok) ok = tc::mbar_wait(&bars->o_done[h], (tiles_done - 1) & 1);
                     tc::tc_fence_after_sync();
                     pv_done = true;
                 }
@@ -449,22 +545,51 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
         }
 
-        // ------------------------------------------------------------------ epilogue
-        if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(n_tiles - 1) & 1);
+        // ------------------------------------------------------------------ epilogue of the unit
+        // (tiles_done now counts this unit's tiles as well.)
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        float row_lse = l > 0.f ? fmaf(m_used, p.scale, logf(l)) : INFINITY;
+        const int rows_here = min(kBlockM, p.tokens - m0);
+        float* lse_out = p.lse + (int64_t(b) * p.q_heads + head) * p.tokens + m0;
+        const bool bulk_lse = rows_here == kBlockM && (p.tokens & 3) == 0;
+        float* lse_stage = reinterpret_cast<float*>(
+            kHandoff ? smem + (h == 0 ? PREFILL_LSE_HEAD0_OFFSET_BYTES : PREFILL_LSE_HEAD1_OFFSET_BYTES)
+                     : smem + kBarrierOffset + kBarrierBytes + h * 512);
+        // The LSE array goes to the planner's region in the released terminal K stage (or to the dedicated
+        // area), is published with one barrier of the head's warpgroup and leaves with one bulk store. Without
+        // key splitting that happens here, before the last PV has even finished, so that the stage is free for the
+        // next unit's keys as early as possible.
+        auto store_lse = [&](bool writes) {
+            // Both heads' last score MMAs have read the terminal stage once its "empty" phase completed.
+            if (ok) ok = tc::mbar_wait(&bars->k_empty[0], (terminal_uses - 1) & 1);
+            if (writes) lse_stage[row] = row_lse;
+            tc::fence_proxy_async_smem();
+            wg_barrier(h);
+            if (row == 0) {
+                if (writes && bulk_lse && !bars->abort) {
+                    tc::bulk_store_1d(lse_out, lse_stage, kBlockM * 4);
+                    tc::bulk_commit();
+                    tc::bulk_wait_read_all();
+                }
+                tc::mbar_arrive(&bars->lse_drained);
+            }
+            if (writes && !bulk_lse && row < rows_here) lse_out[row] = row_lse;
+        };
+        if constexpr (!kSplit) store_lse(true);
+
+        if (ok) ok = tc::mbar_wait(&bars->o_done[h], (tiles_done - 1) & 1);
         if (!ok) {
             atomicCAS(p.status, 0, 14 + h);
             bars->abort = 1;
         }
         tc::tc_fence_after_sync();
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        float row_lse = l > 0.f ? fmaf(m_used, p.scale, logf(l)) : INFINITY;
         float own_weight = inv;        // what this CTA's accumulator is multiplied by in the stored O
         float other_weight = 0.f;      // key-split, second finisher: weight of the other CTA's normalised O
         const float4* other_o = nullptr;
         bool stores = true;
         if constexpr (kSplit) {
-            if (all_tiles >= 2) {
-                const int unit = ((((m_block * p.batch + b) * p.kv_heads + kvh) * 2 + pair) * 2) + h;
+            if (u.all_tiles >= 2) {
+                const int unit = ((((u.m_block * p.batch + b) * p.kv_heads + u.kvh) * 2 + u.pair) * 2) + h;
                 int32_t* claim = p.tickets + 2 * unit;
                 int32_t* ready = claim + 1;
                 float4* slot_o = p.part_o + size_t(unit) * (kBlockM * kDim / 4);
@@ -506,19 +631,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     other_o = slot_o;
                 }
             }
+            store_lse(stores);
+        }
+        // O (BF16) is staged in the output staging buffer in the TMA store layout. The two heads use the buffer in
+        // turn: head 0 of a unit after head 1 of the previous unit, head 1 after head 0 of the same unit.
+        uint8_t* o_stage = smem + kOutStageOffset;
+        if (h == 0) {
+            if (units_done > 0 && ok) ok = tc::mbar_wait(&bars->stage_drained[1], (units_done - 1) & 1);
+        } else {
+            if (ok) ok = tc::mbar_wait(&bars->stage_drained[0], units_done & 1);
         }
         if (stores) {
-        // O (bf16) is staged over this head's own Q tile in the TMA store layout; LSE goes to the
-        // planner's region in the released terminal K stage (or to the dedicated area).
-        uint8_t* o_stage = smem + kQOffset + h * kTileBytes;
-        float* lse_stage = reinterpret_cast<float*>(
-            kHandoff ? smem + (h == 0 ? PREFILL_LSE_HEAD0_OFFSET_BYTES : PREFILL_LSE_HEAD1_OFFSET_BYTES)
-                     : smem + kBarrierOffset + kBarrierBytes + h * 512);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             uint32_t acc[32];
             tc::tmem_ld32(o_tmem + c * 32, acc);
             tc::tmem_wait_ld();
+            if (c == 3) {
+                // The accumulator is in registers: the next unit's first PV may overwrite it.
+                tc::tc_fence_before_sync();
+                tc::mbar_arrive(&bars->o_free[h]);
+            }
             float value[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) value[j] = __uint_as_float(acc[j]) * own_weight;
@@ -546,20 +679,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 *reinterpret_cast<uint4*>(half + ((chunk ^ (row & 7)) << 4)) = word;
             }
         }
-        lse_stage[row] = row_lse;
         tc::fence_proxy_async_smem();
-        wg_barrier(h);  // one barrier publishes the O tile and the LSE array of this head
-        const int rows_here = min(kBlockM, p.tokens - m0);
-        float* lse_out = p.lse + (int64_t(b) * p.q_heads + head) * p.tokens + m0;
-        const bool bulk_lse = rows_here == kBlockM && (p.tokens & 3) == 0;
-        if (row == 0 && !bars->abort) {
-            tc::tma_store_4d(&omap, o_stage, 0, head, m0, b);
-            tc::tma_store_4d(&omap, o_stage + kHalfBytes, 64, head, m0, b);
-            if (bulk_lse) tc::bulk_store_1d(lse_out, lse_stage, kBlockM * 4);
-            tc::bulk_commit();
-            tc::bulk_wait_read_all();  // shared memory must outlive the stores' reads; the writes finish on their own
+        wg_barrier(h);  // the whole tile is staged
+        if (row == 0) {
+            if (!bars->abort) {
+                tc::tma_store_4d(&omap, o_stage, 0, head, m0, b);
+                tc::tma_store_4d(&omap, o_stage + kHalfBytes, 64, head, m0, b);
+                tc::bulk_commit();
+                tc::bulk_wait_read_all();  // shared memory must outlive the stores' reads; the writes finish on their own
+            }
+            tc::mbar_arrive(&bars->stage_drained[h]);
         }
-        if (!bulk_lse && row < rows_here) lse_out[row] = row_lse;
+        } else {
+            // (key split, first finisher) Nothing is staged, but the phases of both barriers advance all the same.
+            tc::tc_fence_before_sync();
+            tc::mbar_arrive(&bars->o_free[h]);
+            if (row == 0) tc::mbar_arrive(&bars->stage_drained[h]);
+        }
+        ++units_done;
         }
     }
 
@@ -628,7 +765,7 @@ bool split_pays_off(const tc::DeviceInfo& info, int64_t batch, int64_t tokens, i
 
 template <bool kHandoff, bool kSplit>
 int launch(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& omap,
-           const PrefillParams& p, cudaStream_t stream) {
+           const PrefillParams& p, int sms, cudaStream_t stream) {
     auto kernel = &prefill_kernel<kHandoff, kSplit>;
     constexpr int shared = shared_bytes(kHandoff);
     static thread_local int configured_device = -1;
@@ -638,7 +775,8 @@ int launch(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& 
         TC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared));
         configured_device = device;
     }
-    const unsigned grid = unsigned(p.m_blocks) * p.batch * p.kv_heads * 2 * (kSplit ? 2 : 1);
+    // One persistent CTA per SM (the schedule's shared memory and tensor memory leave room for one only).
+    const unsigned grid = unsigned(p.total_units < sms ? p.total_units : sms);
     kernel<<<grid, kThreads, shared, stream>>>(qmap, kmap, vmap, omap, p);
     TC_CUDA(cudaGetLastError());
     return TC_OK;
@@ -747,6 +885,7 @@ int prefill_common(int device, void* stream, const void* q, const int64_t q_stri
     p.q_heads = int(q_heads);
     p.kv_heads = int(kv_heads);
     p.m_blocks = int((tokens + kBlockM - 1) / kBlockM);
+    p.total_units = p.m_blocks * p.batch * p.kv_heads * 2;
     p.scale = float(scale);
     p.scale_log2 = float(scale) * float(M_LOG2E);
     TC_REQUIRE(std::isfinite(p.scale_log2) && p.scale > 0.f, "attention scale is not a positive finite FP32 value");
@@ -762,11 +901,12 @@ int prefill_common(int device, void* stream, const void* q, const int64_t q_stri
         p.part_o = reinterpret_cast<float4*>(base + split.o_offset);
         p.part_lse = reinterpret_cast<float*>(base + split.lse_offset);
         TC_CUDA(cudaMemsetAsync(base, 0, size_t(split.ticket_bytes), cuda_stream));
-        return mapping == 1 ? launch<true, true>(qmap, kmap, vmap, omap, p, cuda_stream)
-                            : launch<false, true>(qmap, kmap, vmap, omap, p, cuda_stream);
+        p.total_units *= 2;
+        return mapping == 1 ? launch<true, true>(qmap, kmap, vmap, omap, p, info.sms, cuda_stream)
+                            : launch<false, true>(qmap, kmap, vmap, omap, p, info.sms, cuda_stream);
     }
-    return mapping == 1 ? launch<true, false>(qmap, kmap, vmap, omap, p, cuda_stream)
-                        : launch<false, false>(qmap, kmap, vmap, omap, p, cuda_stream);
+    return mapping == 1 ? launch<true, false>(qmap, kmap, vmap, omap, p, info.sms, cuda_stream)
+                        : launch<false, false>(qmap, kmap, vmap, omap, p, info.sms, cuda_stream);
 }
 
 }  // namespace
