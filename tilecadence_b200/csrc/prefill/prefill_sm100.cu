@@ -95,18 +95,22 @@ static_assert(PREFILL_LSE_HEAD0_OFFSET_BYTES + 512 <= PREFILL_LSE_HEAD1_OFFSET_B
                   PREFILL_LSE_HEAD1_OFFSET_BYTES + 512 <= PREFILL_LSE_HEAD0_OFFSET_BYTES,
               "LSE regions must not overlap");
 
-constexpr int kOutStageOffset = kVOffset + kStages * kTileBytes;  // one 128 x 128 BF16 tile, used by the heads in turn
-constexpr int kBarrierOffset = kOutStageOffset + kTileBytes;
+// Three Q buffers in rotation (Q tile number 2 * unit + head goes to buffer number % 3), so that head 0's tile of
+// the next unit is loaded a whole unit ahead and head 1's as soon as head 0 of the current unit is done with
+// its own. Buffers 0 and 1 sit in front of the K ring, buffer 2 behind the V ring.
+constexpr int kQBuffers = 3;
+constexpr int kQ2Offset = kVOffset + kStages * kTileBytes;
+constexpr int kBarrierOffset = kQ2Offset + kTileBytes;
+__host__ __device__ constexpr int q_buffer_offset(int buffer) { return buffer < 2 ? kQOffset + buffer * kTileBytes : kQ2Offset; }
 constexpr int shared_bytes(bool handoff) { return 1024 + kBarrierOffset + kBarrierBytes + (handoff ? 0 : kStagingBytes); }
 static_assert(shared_bytes(false) <= 227 * 1024, "the schedule must fit the 227 KiB a CTA can have");
 
 struct Barriers {
-    uint64_t q_full, q_empty;
+    uint64_t q_full[kQBuffers], q_empty[kQBuffers];
     uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
     uint64_t s_full[2], s_free[2], p_half[2][2], p_lo_free[2], o_done[2];
     uint64_t o_free[2];          // the epilogue has read head h's accumulator out of tensor memory
     uint64_t lse_drained;        // both heads' LSE arrays have left the terminal K stage
-    uint64_t stage_drained[2];   // head h's output tile has left the staging buffer
     uint32_t tmem_base;
     int32_t abort;
     int32_t role[2];  // key-split only: which of the two CTAs of a query tile claimed each head first
@@ -114,6 +118,7 @@ struct Barriers {
 static_assert(sizeof(Barriers) <= kBarrierBytes, "barrier block");
 
 struct PrefillParams {
+    __nv_bfloat16* out;  // [B, T, Hq, 128] contiguous
     float* lse;
     int32_t* status;
     int batch, tokens, q_heads, kv_heads, m_blocks;
@@ -145,6 +150,14 @@ struct StageCounts {
     }
 };
 static_assert(kStages == 2, "StageCounts holds two stages");
+struct BufferCounts {
+    uint32_t buffer0 = 0, buffer1 = 0, buffer2 = 0;
+    __device__ __forceinline__ uint32_t of(int buffer) const { return buffer == 0 ? buffer0 : (buffer == 1 ? buffer1 : buffer2); }
+    __device__ __forceinline__ void bump(int buffer) {
+        if (buffer == 0) ++buffer0; else if (buffer == 1) ++buffer1; else ++buffer2;
+    }
+};
+static_assert(kQBuffers == 3, "BufferCounts holds three buffers");
 
 // One unit of work: a 128-row query tile of the two heads of a pair slot and the key tiles it attends to
 // (all of them, or with kSplit one of two parts: part 0 the tiles nearest the diagonal, rounded up).
@@ -180,6 +193,35 @@ __device__ __forceinline__ int unit_of_round(int round, int total_units) {
     return index < total_units ? index : -1;
 }
 
+// Advances `round` to this CTA's next unit that has work and returns it in `unit`; false when the list is done.
+// (With kSplit the second part of a one-tile row block is empty: every role skips it the same way.)
+template <bool kSplit>
+__device__ __forceinline__ bool next_unit(const PrefillParams& p, int rounds, int& round, Unit& unit) {
+    while (round < rounds) {
+        const int index = unit_of_round(round++, p.total_units);
+        if (index < 0) continue;
+        unit = unit_at<kSplit>(p, index);
+        if (unit.n_tiles > 0) return true;
+    }
+    return false;
+}
+
+// Build switch TC_TRACE (off in every shipped library): one thread of each role appends (tag, %globaltimer) records
+// to a per-CTA, per-role log that tc_debug_prefill_trace copies out; see tilecadence_b200/trace_prefill.py.
+// Roles: 0 TMA producer, 1 score-MMA issuer, 2/3 PV issuers, 4/5 softmax warpgroups (row 0).
+// Tags: 1 Q tile issued, 2 first K/V tile of a unit issued, 3 last tile of a unit issued; 10 first / 11 last score
+// MMA of a unit issued; 20 first / 21 last PV of a unit issued; 30 first score tile of a unit arrived, 31 key loop
+// done, 32 LSE array left, 33 last PV done, 34 output rows stored.
+#ifdef TC_TRACE
+constexpr int kTraceRoles = 6, kTraceEvents = 256;
+__device__ unsigned long long g_prefill_trace[148][kTraceRoles][kTraceEvents];
+#define TC_TRACE_DECLARE(role) unsigned long long* trace_log = blockIdx.x < 148 ? g_prefill_trace[blockIdx.x][role] : nullptr; int trace_count = 0
+#define TC_TRACE_EVENT(tag) do { if (trace_log && trace_count < kTraceEvents) trace_log[trace_count++] = (tc::global_timer_ns() << 8) | (unsigned long long)(tag); } while (0)
+#else
+#define TC_TRACE_DECLARE(role) do { } while (0)
+#define TC_TRACE_EVENT(tag) do { } while (0)
+#endif
+
 // Persistent kernel: one CTA per SM works through its units. Barrier phases run on across units (every waiter
 // sees every phase of the barriers it waits on, in order, and keeps its own count), so the TMA producer and the
 // MMA issuers move on to the next unit while the softmax warpgroups are still in the epilogue of the current
@@ -191,8 +233,7 @@ __device__ __forceinline__ int unit_of_round(int round, int total_units) {
 template <bool kHandoff, bool kSplit = false>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
-               const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap,
-               const PrefillParams p) {
+               const __grid_constant__ CUtensorMap vmap, const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kBarrierOffset);
@@ -201,8 +242,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     const int rounds = (p.total_units + int(gridDim.x) - 1) / int(gridDim.x);
 
     if (threadIdx.x == kProducerWarp * 32) {
-        tc::mbar_init(&bars->q_full, 1);
-        tc::mbar_init(&bars->q_empty, 1);
+        for (int buffer = 0; buffer < kQBuffers; ++buffer) {
+            tc::mbar_init(&bars->q_full[buffer], 1);
+            tc::mbar_init(&bars->q_empty[buffer], 1);
+        }
         for (int s = 0; s < kStages; ++s) {
             tc::mbar_init(&bars->k_full[s], 1);
             tc::mbar_init(&bars->k_empty[s], 2);  // one arrival per head's score MMA
@@ -224,7 +267,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             tc::mbar_init(&bars->o_done[h], 1);
             tc::mbar_init(&bars->p_lo_free[h], 1);
             tc::mbar_init(&bars->o_free[h], kSoftmaxThreads);
-            tc::mbar_init(&bars->stage_drained[h], 1);
         }
         bars->abort = 0;
         tc::mbar_fence_init();
@@ -245,34 +287,42 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kDataRegisters));
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
+        // Loads are issued in the order in which what they overwrite comes free: the first K/V tile of a unit
+        // into the ring stage that the previous unit's last-but-one tile has left, then head 1's Q tile of this
+        // unit (its buffer held head 0's tile of the previous unit), then head 0's Q tile of the NEXT unit, then
+        // the remaining K/V tiles. The ring stage a unit starts in is the one its predecessor did not end in, so
+        // that the predecessor's terminal K stage, which holds its LSE arrays for a while, is the second to be
+        // reloaded.
         if (lane == 0) {
             const uint64_t keep = tc::policy_evict_last(), stream_once = tc::policy_evict_first();
             StageCounts k_uses, v_uses;  // loads issued into each ring stage so far
-            uint32_t units_done = 0;
+            BufferCounts q_uses;         // loads issued into each Q buffer so far
             bool ok = true;
-            for (int round = 0; ok && round < rounds; ++round) {
-                const int index = unit_of_round(round, p.total_units);
-                if (index < 0) continue;
-                const Unit u = unit_at<kSplit>(p, index);
-                if (u.n_tiles == 0) continue;  // a one-tile row block has nothing to split
-                // Q: the score MMAs of the previous unit must have read the previous Q.
-                if (units_done > 0 && !(ok = tc::mbar_wait(&bars->q_empty, (units_done - 1) & 1))) break;
-                tc::mbar_arrive_expect_tx(&bars->q_full, 2 * kTileBytes);
-                for (int h = 0; h < 2; ++h) {
-                    uint8_t* dst = smem + kQOffset + h * kTileBytes;
-                    tc::tma_load_4d(dst, &qmap, &bars->q_full, 0, u.head0 + h, u.m0, u.b, stream_once);
-                    tc::tma_load_4d(dst + kHalfBytes, &qmap, &bars->q_full, 64, u.head0 + h, u.m0, u.b, stream_once);
-                }
-                bool terminal_checked = units_done == 0;
-                for (int it = 0; it < u.n_tiles; ++it) {
-                    const int stage = (u.n_tiles - 1 - it) % kStages;  // the unit's last tile always lands in stage 0
+            TC_TRACE_DECLARE(0);
+            auto load_q = [&](const Unit& u, int ordinal, int h) {
+                const int buffer = (2 * ordinal + h) % kQBuffers;
+                if (q_uses.of(buffer) > 0 && !tc::mbar_wait(&bars->q_empty[buffer], (q_uses.of(buffer) - 1) & 1)) return false;
+                uint8_t* dst = smem + q_buffer_offset(buffer);
+                tc::mbar_arrive_expect_tx(&bars->q_full[buffer], kTileBytes);
+                tc::tma_load_4d(dst, &qmap, &bars->q_full[buffer], 0, u.head0 + h, u.m0, u.b, stream_once);
+                tc::tma_load_4d(dst + kHalfBytes, &qmap, &bars->q_full[buffer], 64, u.head0 + h, u.m0, u.b, stream_once);
+                q_uses.bump(buffer);
+                TC_TRACE_EVENT(1);
+                return true;
+            };
+            Unit u, next;
+            int round = 0, ordinal = 0, first_stage = 0;
+            bool have = next_unit<kSplit>(p, rounds, round, u);
+            if (have) ok = load_q(u, 0, 0) && load_q(u, 0, 1);
+            while (ok && have) {
+                int look = round;
+                const bool have_next = next_unit<kSplit>(p, rounds, look, next);
+                for (int it = 0; ok && it < u.n_tiles; ++it) {
+                    const int stage = (first_stage + it) & 1;
                     const int n0 = (u.key_block0 - it) * kBlockN;
+                    // The second tile goes where the previous unit ended: its LSE arrays must have left.
+                    if (it == 1 && ordinal > 0 && !(ok = tc::mbar_wait(&bars->lse_drained, (ordinal - 1) & 1))) break;
                     if (k_uses.of(stage) > 0 && !(ok = tc::mbar_wait(&bars->k_empty[stage], (k_uses.of(stage) - 1) & 1))) break;
-                    if (stage == 0 && !terminal_checked) {
-                        // Stage 0 was the previous unit's terminal K stage: its LSE arrays must have left it.
-                        if (!(ok = tc::mbar_wait(&bars->lse_drained, (units_done - 1) & 1))) break;
-                        terminal_checked = true;
-                    }
                     uint8_t* kdst = smem + kKOffset + stage * kTileBytes;
                     tc::mbar_arrive_expect_tx(&bars->k_full[stage], kTileBytes);
                     tc::tma_load_4d(kdst, &kmap, &bars->k_full[stage], 0, u.kvh, n0, u.b, keep);
@@ -284,8 +334,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     tc::tma_load_4d(vdst, &vmap, &bars->v_full[stage], 0, u.kvh, n0, u.b, keep);
                     tc::tma_load_4d(vdst + kHalfBytes, &vmap, &bars->v_full[stage], 64, u.kvh, n0, u.b, keep);
                     v_uses.bump(stage);
+                    if (it == 0) TC_TRACE_EVENT(2);
+                    if (it + 1 == u.n_tiles) TC_TRACE_EVENT(3);
+                    if (it == 0) {
+                        if (ordinal > 0) ok = load_q(u, ordinal, 1);
+                        if (ok && have_next) ok = load_q(next, ordinal + 1, 0);
+                    }
                 }
-                ++units_done;
+                // A one-tile unit never reloads its predecessor's terminal stage: take that phase here, so that
+                // every phase of the barrier is seen in order.
+                if (ok && u.n_tiles == 1 && ordinal > 0) ok = tc::mbar_wait(&bars->lse_drained, (ordinal - 1) & 1);
+                first_stage = 1 - ((first_stage + u.n_tiles - 1) & 1);
+                ++ordinal;
+                u = next;
+                round = look;
+                have = have_next;
             }
             if (!ok) {
                 atomicCAS(p.status, 0, 11);
@@ -303,27 +366,30 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             constexpr uint32_t idesc_qk = tc::umma_idesc(128, 128, 1, 0, 0);
             constexpr uint32_t idesc_pv = tc::umma_idesc(128, 128, 1, 0, 1);
             StageCounts uses;  // tiles taken from each ring stage so far (K for warp 9, V for 10 and 11)
-            uint32_t tiles_done = 0, units_done = 0;
+            uint32_t tiles_done = 0;
+            int ordinal = 0, first_stage = 0, round = 0;
+            Unit u;
             bool ok = true;
             if (warp == kMmaWarp) {
                 // S = Q_h K^T into the score buffer: both operands K-major, 8 steps of 16 along D
                 // (4 per 64-element half). A score MMA may overwrite the buffer once the other head's
                 // softmax warpgroup has pulled its tile into registers; because P has its own columns it
                 // does not wait for any PV.
-                const uint32_t q_addr = tc::smem_u32(smem + kQOffset);
+                BufferCounts q_uses;  // Q tiles taken from each buffer so far
+                TC_TRACE_DECLARE(1);
                 const uint32_t k_addr = tc::smem_u32(smem + kKOffset);
-                for (int round = 0; ok && round < rounds; ++round) {
-                    const int index = unit_of_round(round, p.total_units);
-                    if (index < 0) continue;
-                    const Unit u = unit_at<kSplit>(p, index);
-                    if (u.n_tiles == 0) continue;
-                    if (!(ok = tc::mbar_wait(&bars->q_full, units_done & 1))) break;
+                while (ok && next_unit<kSplit>(p, rounds, round, u)) {
                     for (int it = 0; ok && it < u.n_tiles; ++it) {
-                        const int stage = (u.n_tiles - 1 - it) % kStages;
+                        const int stage = (first_stage + it) & 1;
                         if (!(ok = tc::mbar_wait(&bars->k_full[stage], uses.of(stage) & 1))) break;
                         uses.bump(stage);
                         const uint32_t kb = k_addr + stage * kTileBytes;
                         for (int h = 0; h < 2 && ok; ++h) {
+                            const int buffer = (2 * ordinal + h) % kQBuffers;
+                            if (it == 0) {
+                                if (!(ok = tc::mbar_wait(&bars->q_full[buffer], q_uses.of(buffer) & 1))) break;
+                                q_uses.bump(buffer);
+                            }
                             if (h == 0) {
                                 if (tiles_done > 0) ok = tc::mbar_wait(&bars->s_free[1], (tiles_done - 1) & 1);
                             } else {
@@ -331,19 +397,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                             }
                             if (!ok) break;
                             tc::tc_fence_after_sync();
+                            const uint32_t qb = tc::smem_u32(smem + q_buffer_offset(buffer));
 #pragma unroll
                             for (int ks = 0; ks < 8; ++ks) {
                                 const uint32_t off = uint32_t(ks >> 2) * kHalfBytes + uint32_t(ks & 3) * 32;
-                                tc::umma_ss(tmem + s_column(h), tc::umma_desc_sw128(q_addr + h * kTileBytes + off, 16, 1024),
+                                tc::umma_ss(tmem + s_column(h), tc::umma_desc_sw128(qb + off, 16, 1024),
                                             tc::umma_desc_sw128(kb + off, 16, 1024), idesc_qk, ks > 0);
                             }
                             tc::umma_commit(&bars->s_full[h]);
                             tc::umma_commit(&bars->k_empty[stage]);  // two arrivals per stage: one per head
+                            if (it + 1 == u.n_tiles) tc::umma_commit(&bars->q_empty[buffer]);  // this head's Q tile is read
+                            if (it == 0 && h == 0) TC_TRACE_EVENT(10);
+                            if (it + 1 == u.n_tiles && h == 1) TC_TRACE_EVENT(11);
                         }
                         ++tiles_done;
                     }
-                    if (ok) tc::umma_commit(&bars->q_empty);  // every score MMA of this unit has read Q
-                    ++units_done;
+                    first_stage = 1 - ((first_stage + u.n_tiles - 1) & 1);
+                    ++ordinal;
                 }
             } else {
                 // O_h += P_h V, one 64-key half at a time: P from TMEM (8 columns per 16 keys), V MN-major
@@ -352,13 +422,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 const uint32_t v_addr = tc::smem_u32(smem + kVOffset);
                 const uint32_t p_col = tmem + p_column(h);
                 const uint32_t o_col = tmem + o_column(h);
-                for (int round = 0; ok && round < rounds; ++round) {
-                    const int index = unit_of_round(round, p.total_units);
-                    if (index < 0) continue;
-                    const Unit u = unit_at<kSplit>(p, index);
-                    if (u.n_tiles == 0) continue;
+                TC_TRACE_DECLARE(2 + h);
+                while (ok && next_unit<kSplit>(p, rounds, round, u)) {
                     for (int it = 0; ok && it < u.n_tiles; ++it) {
-                        const int stage = (u.n_tiles - 1 - it) % kStages;
+                        const int stage = (first_stage + it) & 1;
                         const uint32_t vb = v_addr + stage * kTileBytes;
                         auto issue_pv_half = [&](int half) {
 #pragma unroll
@@ -372,7 +439,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                         uses.bump(stage);
                         // The first PV of a unit overwrites the accumulator: the previous unit's epilogue must
                         // have read it out of tensor memory.
-                        if (it == 0 && units_done > 0 && !(ok = tc::mbar_wait(&bars->o_free[h], (units_done - 1) & 1))) break;
+                        if (it == 0 && ordinal > 0 && !(ok = tc::mbar_wait(&bars->o_free[h], (ordinal - 1) & 1))) break;
                         if (!(ok = tc::mbar_wait(&bars->p_half[h][0], tiles_done & 1))) break;
                         tc::tc_fence_after_sync();
                         issue_pv_half(0);
@@ -382,9 +449,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                         issue_pv_half(1);
                         tc::umma_commit(&bars->o_done[h]);
                         tc::umma_commit(&bars->v_empty[stage]);
+                        if (it == 0) TC_TRACE_EVENT(20);
+                        if (it + 1 == u.n_tiles) TC_TRACE_EVENT(21);
                         ++tiles_done;
                     }
-                    ++units_done;
+                    first_stage = 1 - ((first_stage + u.n_tiles - 1) & 1);
+                    ++ordinal;
                 }
             }
             if (!ok) {
@@ -406,25 +476,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         // Tiles of all of this CTA's units: the two heads take turns at the exponential unit from the first tile
         // of the first unit to the last tile of the last one.
         uint32_t cta_tiles = 0;
-        for (int round = 0; round < rounds; ++round) {
-            const int index = unit_of_round(round, p.total_units);
-            if (index >= 0) cta_tiles += uint32_t(unit_at<kSplit>(p, index).n_tiles);
-        }
-        uint32_t tiles_done = 0, units_done = 0, terminal_uses = 0;  // terminal_uses: tiles that went through K stage 0
+        Unit u;
+        for (int round = 0; next_unit<kSplit>(p, rounds, round, u);) cta_tiles += uint32_t(u.n_tiles);
+        uint32_t tiles_done = 0;
+        StageCounts k_uses;  // tiles that went through each K ring stage so far
+        int first_stage = 0;
         bool ok = true;
+#ifdef TC_TRACE
+        unsigned long long* trace_log = (row == 0 && blockIdx.x < 148) ? g_prefill_trace[blockIdx.x][4 + h] : nullptr;
+        int trace_count = 0;
+#endif
 
-        for (int round = 0; round < rounds; ++round) {
-        const int index = unit_of_round(round, p.total_units);
-        if (index < 0) continue;
-        const Unit u = unit_at<kSplit>(p, index);
-        if (u.n_tiles == 0) continue;
+        for (int round = 0; next_unit<kSplit>(p, rounds, round, u);) {
         const int n_tiles = u.n_tiles, part = u.part, m0 = u.m0, b = u.b;
         const int head = u.head0 + h;
+        const int terminal = (first_stage + n_tiles - 1) & 1;  // the ring stage this unit's last score MMA reads
         float m_used = -INFINITY, l = 0.f;
 
         for (int it = 0; it < n_tiles; ++it, ++tiles_done) {
-            if ((n_tiles - 1 - it) % kStages == 0) ++terminal_uses;
+            k_uses.bump((first_stage + it) & 1);
             if (ok) ok = tc::mbar_wait(&bars->s_full[h], tiles_done & 1);  // after a failed wait: keep the barrier pattern, skip waits
+            if (it == 0) TC_TRACE_EVENT(30);
             tc::tc_fence_after_sync();
             float s[128];
 #pragma unroll
@@ -547,13 +619,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
 
         // ------------------------------------------------------------------ epilogue of the unit
         // (tiles_done now counts this unit's tiles as well.)
+        TC_TRACE_EVENT(31);
         const float inv = l > 0.f ? 1.f / l : 0.f;
         float row_lse = l > 0.f ? fmaf(m_used, p.scale, logf(l)) : INFINITY;
         const int rows_here = min(kBlockM, p.tokens - m0);
         float* lse_out = p.lse + (int64_t(b) * p.q_heads + head) * p.tokens + m0;
         const bool bulk_lse = rows_here == kBlockM && (p.tokens & 3) == 0;
+        // The planner's offsets are those of a terminal stage at PREFILL_TERMINAL_K_OFFSET_BYTES (ring stage 0);
+        // when this unit ends in stage 1 the same regions lie one stage further on.
         float* lse_stage = reinterpret_cast<float*>(
-            kHandoff ? smem + (h == 0 ? PREFILL_LSE_HEAD0_OFFSET_BYTES : PREFILL_LSE_HEAD1_OFFSET_BYTES)
+            kHandoff ? smem + terminal * kTileBytes + (h == 0 ? PREFILL_LSE_HEAD0_OFFSET_BYTES : PREFILL_LSE_HEAD1_OFFSET_BYTES)
                      : smem + kBarrierOffset + kBarrierBytes + h * 512);
         // The LSE array goes to the planner's region in the released terminal K stage (or to the dedicated
         // area), is published with one barrier of the head's warpgroup and leaves with one bulk store. Without
@@ -561,7 +636,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         // next unit's keys as early as possible.
         auto store_lse = [&](bool writes) {
             // Both heads' last score MMAs have read the terminal stage once its "empty" phase completed.
-            if (ok) ok = tc::mbar_wait(&bars->k_empty[0], (terminal_uses - 1) & 1);
+            if (ok) ok = tc::mbar_wait(&bars->k_empty[terminal], (k_uses.of(terminal) - 1) & 1);
             if (writes) lse_stage[row] = row_lse;
             tc::fence_proxy_async_smem();
             wg_barrier(h);
@@ -576,8 +651,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             if (writes && !bulk_lse && row < rows_here) lse_out[row] = row_lse;
         };
         if constexpr (!kSplit) store_lse(true);
+        TC_TRACE_EVENT(32);
 
         if (ok) ok = tc::mbar_wait(&bars->o_done[h], (tiles_done - 1) & 1);
+        TC_TRACE_EVENT(33);
         if (!ok) {
             atomicCAS(p.status, 0, 14 + h);
             bars->abort = 1;
@@ -633,14 +710,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             }
             store_lse(stores);
         }
-        // O (BF16) is staged in the output staging buffer in the TMA store layout. The two heads use the buffer in
-        // turn: head 0 of a unit after head 1 of the previous unit, head 1 after head 0 of the same unit.
-        uint8_t* o_stage = smem + kOutStageOffset;
-        if (h == 0) {
-            if (units_done > 0 && ok) ok = tc::mbar_wait(&bars->stage_drained[1], (units_done - 1) & 1);
-        } else {
-            if (ok) ok = tc::mbar_wait(&bars->stage_drained[0], units_done & 1);
-        }
+        // O (BF16) goes from the accumulator to global memory through registers: every thread owns one query
+        // row, 256 contiguous bytes of the output, written as sixteen 16-byte stores. No shared memory is staged,
+        // so nothing of this unit stands in the way of the next unit's loads.
+        __nv_bfloat16* out_row = p.out + ((int64_t(b) * p.tokens + m0 + row) * p.q_heads + head) * kDim;
         if (stores) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -667,36 +740,25 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     }
                 }
             }
-            uint8_t* half = o_stage + (c >> 1) * kHalfBytes + row * 128;
+            if (row < rows_here && !bars->abort) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint4 word;
-                word.x = tc::pack_bf16x2(value[i * 8 + 0], value[i * 8 + 1]);
-                word.y = tc::pack_bf16x2(value[i * 8 + 2], value[i * 8 + 3]);
-                word.z = tc::pack_bf16x2(value[i * 8 + 4], value[i * 8 + 5]);
-                word.w = tc::pack_bf16x2(value[i * 8 + 6], value[i * 8 + 7]);
-                const int chunk = (c & 1) * 4 + i;
-                *reinterpret_cast<uint4*>(half + ((chunk ^ (row & 7)) << 4)) = word;
+                for (int i = 0; i < 4; ++i) {
+                    uint4 word;
+                    word.x = tc::pack_bf16x2(value[i * 8 + 0], value[i * 8 + 1]);
+                    word.y = tc::pack_bf16x2(value[i * 8 + 2], value[i * 8 + 3]);
+                    word.z = tc::pack_bf16x2(value[i * 8 + 4], value[i * 8 + 5]);
+                    word.w = tc::pack_bf16x2(value[i * 8 + 6], value[i * 8 + 7]);
+                    reinterpret_cast<uint4*>(out_row + c * 32)[i] = word;
+                }
             }
-        }
-        tc::fence_proxy_async_smem();
-        wg_barrier(h);  // the whole tile is staged
-        if (row == 0) {
-            if (!bars->abort) {
-                tc::tma_store_4d(&omap, o_stage, 0, head, m0, b);
-                tc::tma_store_4d(&omap, o_stage + kHalfBytes, 64, head, m0, b);
-                tc::bulk_commit();
-                tc::bulk_wait_read_all();  // shared memory must outlive the stores' reads; the writes finish on their own
-            }
-            tc::mbar_arrive(&bars->stage_drained[h]);
         }
         } else {
-            // (key split, first finisher) Nothing is staged, but the phases of both barriers advance all the same.
+            // (key split, first finisher) Nothing is stored, but the barrier's phase advances all the same.
             tc::tc_fence_before_sync();
             tc::mbar_arrive(&bars->o_free[h]);
-            if (row == 0) tc::mbar_arrive(&bars->stage_drained[h]);
         }
-        ++units_done;
+        TC_TRACE_EVENT(34);
+        first_stage = 1 - terminal;
         }
     }
 
@@ -764,8 +826,8 @@ bool split_pays_off(const tc::DeviceInfo& info, int64_t batch, int64_t tokens, i
 }
 
 template <bool kHandoff, bool kSplit>
-int launch(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& omap,
-           const PrefillParams& p, int sms, cudaStream_t stream) {
+int launch(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap, const PrefillParams& p, int sms,
+           cudaStream_t stream) {
     auto kernel = &prefill_kernel<kHandoff, kSplit>;
     constexpr int shared = shared_bytes(kHandoff);
     static thread_local int configured_device = -1;
@@ -777,7 +839,7 @@ int launch(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& 
     }
     // One persistent CTA per SM (the schedule's shared memory and tensor memory leave room for one only).
     const unsigned grid = unsigned(p.total_units < sms ? p.total_units : sms);
-    kernel<<<grid, kThreads, shared, stream>>>(qmap, kmap, vmap, omap, p);
+    kernel<<<grid, kThreads, shared, stream>>>(qmap, kmap, vmap, p);
     TC_CUDA(cudaGetLastError());
     return TC_OK;
 }
@@ -791,6 +853,18 @@ int prefill_common(int device, void* stream, const void* q, const int64_t q_stri
 }  // namespace
 
 extern "C" {
+
+#ifdef TC_TRACE
+// Trace builds only: copies the role logs of all CTAs to `host` (synchronises the device).
+int tc_debug_prefill_trace(void* host) {
+    return cudaMemcpyFromSymbol(host, g_prefill_trace, sizeof(g_prefill_trace)) == cudaSuccess ? 0 : 1;
+}
+int tc_debug_prefill_trace_clear(void) {
+    void* address = nullptr;
+    if (cudaGetSymbolAddress(&address, g_prefill_trace) != cudaSuccess) return 1;
+    return cudaMemset(address, 0, sizeof(g_prefill_trace)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 int tc_prefill_workspace_spec(int device, int64_t batch, int64_t tokens, int64_t q_heads, int64_t num_splits,
                               int64_t mapping, int causal, int64_t spec[3]) {
@@ -871,13 +945,13 @@ int prefill_common(int device, void* stream, const void* q, const int64_t q_stri
     TC_CUDA(guard.status);
     tc::DeviceScratch scratch;
     if ((status = tc::device_scratch(device, &scratch)) != TC_OK) return status;
-    CUtensorMap qmap, kmap, vmap, omap;
+    CUtensorMap qmap, kmap, vmap;
     if ((status = tc::make_rows_map(&qmap, q, false, q_heads, tokens, batch, q_strides[2], q_strides[1], q_strides[0], kBlockM, 2)) != TC_OK) return status;
     if ((status = tc::make_rows_map(&kmap, k, false, kv_heads, tokens, batch, k_strides[2], k_strides[1], k_strides[0], kBlockN, 2)) != TC_OK) return status;
     if ((status = tc::make_rows_map(&vmap, v, false, kv_heads, tokens, batch, v_strides[2], v_strides[1], v_strides[0], kBlockN, 2)) != TC_OK) return status;
-    if ((status = tc::make_rows_map(&omap, out, false, q_heads, tokens, batch, kDim, q_heads * kDim, tokens * q_heads * kDim, kBlockM, 2)) != TC_OK) return status;
 
     PrefillParams p{};
+    p.out = static_cast<__nv_bfloat16*>(out);
     p.lse = lse;
     p.status = scratch.status;
     p.batch = int(batch);
@@ -902,11 +976,11 @@ int prefill_common(int device, void* stream, const void* q, const int64_t q_stri
         p.part_lse = reinterpret_cast<float*>(base + split.lse_offset);
         TC_CUDA(cudaMemsetAsync(base, 0, size_t(split.ticket_bytes), cuda_stream));
         p.total_units *= 2;
-        return mapping == 1 ? launch<true, true>(qmap, kmap, vmap, omap, p, info.sms, cuda_stream)
-                            : launch<false, true>(qmap, kmap, vmap, omap, p, info.sms, cuda_stream);
+        return mapping == 1 ? launch<true, true>(qmap, kmap, vmap, p, info.sms, cuda_stream)
+                            : launch<false, true>(qmap, kmap, vmap, p, info.sms, cuda_stream);
     }
-    return mapping == 1 ? launch<true, false>(qmap, kmap, vmap, omap, p, info.sms, cuda_stream)
-                        : launch<false, false>(qmap, kmap, vmap, omap, p, info.sms, cuda_stream);
+    return mapping == 1 ? launch<true, false>(qmap, kmap, vmap, p, info.sms, cuda_stream)
+                        : launch<false, false>(qmap, kmap, vmap, p, info.sms, cuda_stream);
 }
 
 }  // namespace
