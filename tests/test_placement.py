@@ -123,6 +123,12 @@ def test_prefill_tensor_memory_map_is_the_kernels_layout():
     assert {k: v["offset_columns"] for k, v in solved["regions"].items()} == {
         "score_head0": 0, "score_head1": 0, "probability_head0": 128, "probability_head1": 192,
         "output_head0": 256, "output_head1": 384}
+    # the measured alternative: the heads' pipelines are not synchronised, so nothing of one head shares columns
+    # with anything of the other, and a head's probabilities sit over its own retired score buffer
+    private = solve_tmem(TMEM_MAPS["prefill_private_scores"])
+    assert {k: v["offset_columns"] for k, v in private["regions"].items()} == {
+        "score_head0": 0, "score_head1": 128, "probability_head0": 0, "probability_head1": 128,
+        "output_head0": 256, "output_head1": 384}
     assert solved["high_water_columns"] == 512 and solved["allocation_columns"] == 512
     assert solved["schema"] == "b200-tmem-placement-v1" and solved["status"] == "OPTIMAL"
 
@@ -138,7 +144,7 @@ def test_candidate_tensor_memory_maps_fit_and_reuse_retired_score_buffers():
         assert total > 512 >= solved["high_water_columns"]  # only possible because dead tiles give up their columns
     # a probability tile sits in the columns of its own retired score buffer
     private = {k: v["offset_columns"] for k, v in solve_tmem(TMEM_MAPS["prefill_private_scores"])["regions"].items()}
-    assert private["probability_head0"] == private["score_head0"]
+    assert private["probability_head0"] == private["score_head0"] and private["probability_head1"] == private["score_head1"]
 
 
 def test_tensor_memory_replay_rejects_overlap_misalignment_and_overflow():

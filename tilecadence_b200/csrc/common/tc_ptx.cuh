@@ -36,6 +36,13 @@ __device__ __forceinline__ void mbar_fence_init() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival for a whole warp: the lanes meet, then lane 0 arrives (with release semantics, so what the other lanes
+// did before the meeting is covered). For barriers initialised with one count per warp: 32 times fewer operations on
+// the shared-memory pipe than an arrival per thread.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
@@ -78,6 +85,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t start = global_timer_ns();
     for (uint32_t poll = 1;; ++poll) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((poll & 15u) == 0 && global_timer_ns() - start > TC_WAIT_LIMIT_NS) return false;
+    }
+}
+
+// The same bounded wait for a warp that has nothing else to do for a long time: it sleeps between polls, so that
+// it does not take issue slots from the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    for (uint32_t poll = 1;; ++poll) {
+        __nanosleep(128);
         if (mbar_try_wait(bar, parity)) return true;
         if ((poll & 15u) == 0 && global_timer_ns() - start > TC_WAIT_LIMIT_NS) return false;
     }
@@ -317,6 +336,17 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -356,14 +386,12 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 // non-zero, so only their two accumulator registers are carried; the lower half is fed zeros and dropped.
 __device__ __forceinline__ void mma_bf16_16816_rows8(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0,
                                                      uint32_t b1) {
-    float unused2, unused3;
+    [[maybe_unused]] float unused2, unused3;
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %5}, {%7, %8}, "
         "{%0, %1, %9, %9};"
         : "+f"(d0), "+f"(d1), "=f"(unused2), "=f"(unused3)
         : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.f));
-    (void)unused2;
-    (void)unused3;
 }
 
 // ----------------------------------------------------------------------------- conversions / math

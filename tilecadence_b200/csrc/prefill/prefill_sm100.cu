@@ -95,22 +95,18 @@ static_assert(PREFILL_LSE_HEAD0_OFFSET_BYTES + 512 <= PREFILL_LSE_HEAD1_OFFSET_B
                   PREFILL_LSE_HEAD1_OFFSET_BYTES + 512 <= PREFILL_LSE_HEAD0_OFFSET_BYTES,
               "LSE regions must not overlap");
 
-// Three Q buffers in rotation (Q tile number 2 * unit + head goes to buffer number % 3), so that head 0's tile of
-// the next unit is loaded a whole unit ahead and head 1's as soon as head 0 of the current unit is done with
-// its own. Buffers 0 and 1 sit in front of the K ring, buffer 2 behind the V ring.
-constexpr int kQBuffers = 3;
-constexpr int kQ2Offset = kVOffset + kStages * kTileBytes;
-constexpr int kBarrierOffset = kQ2Offset + kTileBytes;
-__host__ __device__ constexpr int q_buffer_offset(int buffer) { return buffer < 2 ? kQOffset + buffer * kTileBytes : kQ2Offset; }
+constexpr int kOutStageOffset = kVOffset + kStages * kTileBytes;  // one 128 x 128 BF16 tile, used by the heads in turn
+constexpr int kBarrierOffset = kOutStageOffset + kTileBytes;
 constexpr int shared_bytes(bool handoff) { return 1024 + kBarrierOffset + kBarrierBytes + (handoff ? 0 : kStagingBytes); }
 static_assert(shared_bytes(false) <= 227 * 1024, "the schedule must fit the 227 KiB a CTA can have");
 
 struct Barriers {
-    uint64_t q_full[kQBuffers], q_empty[kQBuffers];
+    uint64_t q_full, q_empty;
     uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
     uint64_t s_full[2], s_free[2], p_half[2][2], p_lo_free[2], o_done[2];
     uint64_t o_free[2];          // the epilogue has read head h's accumulator out of tensor memory
     uint64_t lse_drained;        // both heads' LSE arrays have left the terminal K stage
+    uint64_t stage_drained[2];   // head h's output tile has left the staging buffer
     uint32_t tmem_base;
     int32_t abort;
     int32_t role[2];  // key-split only: which of the two CTAs of a query tile claimed each head first
@@ -118,7 +114,6 @@ struct Barriers {
 static_assert(sizeof(Barriers) <= kBarrierBytes, "barrier block");
 
 struct PrefillParams {
-    __nv_bfloat16* out;  // [B, T, Hq, 128] contiguous
     float* lse;
     int32_t* status;
     int batch, tokens, q_heads, kv_heads, m_blocks;
@@ -150,14 +145,6 @@ struct StageCounts {
     }
 };
 static_assert(kStages == 2, "StageCounts holds two stages");
-struct BufferCounts {
-    uint32_t buffer0 = 0, buffer1 = 0, buffer2 = 0;
-    __device__ __forceinline__ uint32_t of(int buffer) const { return buffer == 0 ? buffer0 : (buffer == 1 ? buffer1 : buffer2); }
-    __device__ __forceinline__ void bump(int buffer) {
-        if (buffer == 0) ++buffer0; else if (buffer == 1) ++buffer1; else ++buffer2;
-    }
-};
-static_assert(kQBuffers == 3, "BufferCounts holds three buffers");
 
 // One unit of work: a 128-row query tile of the two heads of a pair slot and the key tiles it attends to
 // (all of them, or with kSplit one of two parts: part 0 the tiles nearest the diagonal, rounded up).
@@ -193,25 +180,12 @@ __device__ __forceinline__ int unit_of_round(int round, int total_units) {
     return index < total_units ? index : -1;
 }
 
-// Advances `round` to this CTA's next unit that has work and returns it in `unit`; false when the list is done.
-// (With kSplit the second part of a one-tile row block is empty: every role skips it the same way.)
-template <bool kSplit>
-__device__ __forceinline__ bool next_unit(const PrefillParams& p, int rounds, int& round, Unit& unit) {
-    while (round < rounds) {
-        const int index = unit_of_round(round++, p.total_units);
-        if (index < 0) continue;
-        unit = unit_at<kSplit>(p, index);
-        if (unit.n_tiles > 0) return true;
-    }
-    return false;
-}
-
 // Build switch TC_TRACE (off in every shipped library): one thread of each role appends (tag, %globaltimer) records
 // to a per-CTA, per-role log that tc_debug_prefill_trace copies out; see tilecadence_b200/trace_prefill.py.
 // Roles: 0 TMA producer, 1 score-MMA issuer, 2/3 PV issuers, 4/5 softmax warpgroups (row 0).
-// Tags: 1 Q tile issued, 2 first K/V tile of a unit issued, 3 last tile of a unit issued; 10 first / 11 last score
+// Tags: 1 Q tiles issued, 2 first K/V tile of a unit issued, 3 last tile of a unit issued; 10 first / 11 last score
 // MMA of a unit issued; 20 first / 21 last PV of a unit issued; 30 first score tile of a unit arrived, 31 key loop
-// done, 32 LSE array left, 33 last PV done, 34 output rows stored.
+// done, 32 LSE array left, 33 last PV done, 34 output tile left.
 #ifdef TC_TRACE
 constexpr int kTraceRoles = 6, kTraceEvents = 256;
 __device__ unsigned long long g_prefill_trace[148][kTraceRoles][kTraceEvents];
@@ -233,7 +207,8 @@ __device__ unsigned long long g_prefill_trace[148][kTraceRoles][kTraceEvents];
 template <bool kHandoff, bool kSplit = false>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
-               const __grid_constant__ CUtensorMap vmap, const PrefillParams p) {
+               const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap,
+               const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kBarrierOffset);
@@ -241,11 +216,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rounds = (p.total_units + int(gridDim.x) - 1) / int(gridDim.x);
 
+    int preissued_tiles = -1;  // producer thread: tiles of the first unit already sent for (-1: nor its Q)
     if (threadIdx.x == kProducerWarp * 32) {
-        for (int buffer = 0; buffer < kQBuffers; ++buffer) {
-            tc::mbar_init(&bars->q_full[buffer], 1);
-            tc::mbar_init(&bars->q_empty[buffer], 1);
-        }
+        tc::mbar_init(&bars->q_full, 1);
+        tc::mbar_init(&bars->q_empty, 1);
         for (int s = 0; s < kStages; ++s) {
             tc::mbar_init(&bars->k_full[s], 1);
             tc::mbar_init(&bars->k_empty[s], 2);  // one arrival per head's score MMA
@@ -257,6 +231,32 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         tc::tma_prefetch_desc(&qmap);
         tc::tma_prefetch_desc(&kmap);
         tc::tma_prefetch_desc(&vmap);
+        // The operand barriers are this thread's own, and the stages are fresh: Q and the first ring stages of the
+        // CTA's first unit are sent for at once, so that they fly while the other warps set up their barriers and
+        // tensor memory. Everything else waits for the CTA barrier below.
+        const Unit first = unit_at<kSplit>(p, unit_of_round(0, p.total_units));
+        if (first.n_tiles > 0) {
+            const uint64_t keep = tc::policy_evict_last(), stream_once = tc::policy_evict_first();
+            tc::mbar_arrive_expect_tx(&bars->q_full, 2 * kTileBytes);
+            for (int h = 0; h < 2; ++h) {
+                uint8_t* dst = smem + kQOffset + h * kTileBytes;
+                tc::tma_load_4d(dst, &qmap, &bars->q_full, 0, first.head0 + h, first.m0, first.b, stream_once);
+                tc::tma_load_4d(dst + kHalfBytes, &qmap, &bars->q_full, 64, first.head0 + h, first.m0, first.b, stream_once);
+            }
+            preissued_tiles = first.n_tiles < kStages ? first.n_tiles : kStages;
+            for (int it = 0; it < preissued_tiles; ++it) {
+                const int stage = (first.n_tiles - 1 - it) % kStages;
+                const int n0 = (first.key_block0 - it) * kBlockN;
+                uint8_t* kdst = smem + kKOffset + stage * kTileBytes;
+                tc::mbar_arrive_expect_tx(&bars->k_full[stage], kTileBytes);
+                tc::tma_load_4d(kdst, &kmap, &bars->k_full[stage], 0, first.kvh, n0, first.b, keep);
+                tc::tma_load_4d(kdst + kHalfBytes, &kmap, &bars->k_full[stage], 64, first.kvh, n0, first.b, keep);
+                uint8_t* vdst = smem + kVOffset + stage * kTileBytes;
+                tc::mbar_arrive_expect_tx(&bars->v_full[stage], kTileBytes);
+                tc::tma_load_4d(vdst, &vmap, &bars->v_full[stage], 0, first.kvh, n0, first.b, keep);
+                tc::tma_load_4d(vdst + kHalfBytes, &vmap, &bars->v_full[stage], 64, first.kvh, n0, first.b, keep);
+            }
+        }
     }
     if (threadIdx.x == 0) {
         for (int h = 0; h < 2; ++h) {
@@ -267,6 +267,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             tc::mbar_init(&bars->o_done[h], 1);
             tc::mbar_init(&bars->p_lo_free[h], 1);
             tc::mbar_init(&bars->o_free[h], kSoftmaxThreads);
+            tc::mbar_init(&bars->stage_drained[h], 1);
         }
         bars->abort = 0;
         tc::mbar_fence_init();
@@ -287,42 +288,46 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kDataRegisters));
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
-        // Loads are issued in the order in which what they overwrite comes free: the first K/V tile of a unit
-        // into the ring stage that the previous unit's last-but-one tile has left, then head 1's Q tile of this
-        // unit (its buffer held head 0's tile of the previous unit), then head 0's Q tile of the NEXT unit, then
-        // the remaining K/V tiles. The ring stage a unit starts in is the one its predecessor did not end in, so
-        // that the predecessor's terminal K stage, which holds its LSE arrays for a while, is the second to be
-        // reloaded.
         if (lane == 0) {
             const uint64_t keep = tc::policy_evict_last(), stream_once = tc::policy_evict_first();
             StageCounts k_uses, v_uses;  // loads issued into each ring stage so far
-            BufferCounts q_uses;         // loads issued into each Q buffer so far
+            uint32_t units_done = 0;
             bool ok = true;
             TC_TRACE_DECLARE(0);
-            auto load_q = [&](const Unit& u, int ordinal, int h) {
-                const int buffer = (2 * ordinal + h) % kQBuffers;
-                if (q_uses.of(buffer) > 0 && !tc::mbar_wait(&bars->q_empty[buffer], (q_uses.of(buffer) - 1) & 1)) return false;
-                uint8_t* dst = smem + q_buffer_offset(buffer);
-                tc::mbar_arrive_expect_tx(&bars->q_full[buffer], kTileBytes);
-                tc::tma_load_4d(dst, &qmap, &bars->q_full[buffer], 0, u.head0 + h, u.m0, u.b, stream_once);
-                tc::tma_load_4d(dst + kHalfBytes, &qmap, &bars->q_full[buffer], 64, u.head0 + h, u.m0, u.b, stream_once);
-                q_uses.bump(buffer);
+            for (int round = 0; ok && round < rounds; ++round) {
+                const int index = unit_of_round(round, p.total_units);
+                if (index < 0) continue;
+                const Unit u = unit_at<kSplit>(p, index);
+                if (u.n_tiles == 0) continue;  // a one-tile row block has nothing to split
+                int first_tile = 0;
+                if (units_done == 0 && preissued_tiles >= 0) {
+                    // The CTA's first unit: Q and the first ring stages were sent for before the CTA barrier.
+                    first_tile = preissued_tiles;
+                    for (int it = 0; it < preissued_tiles; ++it) {
+                        k_uses.bump((u.n_tiles - 1 - it) % kStages);
+                        v_uses.bump((u.n_tiles - 1 - it) % kStages);
+                    }
+                } else {
+                    // Q: the score MMAs of the previous unit must have read the previous Q.
+                    if (units_done > 0 && !(ok = tc::mbar_wait(&bars->q_empty, (units_done - 1) & 1))) break;
+                    tc::mbar_arrive_expect_tx(&bars->q_full, 2 * kTileBytes);
+                    for (int h = 0; h < 2; ++h) {
+                        uint8_t* dst = smem + kQOffset + h * kTileBytes;
+                        tc::tma_load_4d(dst, &qmap, &bars->q_full, 0, u.head0 + h, u.m0, u.b, stream_once);
+                        tc::tma_load_4d(dst + kHalfBytes, &qmap, &bars->q_full, 64, u.head0 + h, u.m0, u.b, stream_once);
+                    }
+                }
                 TC_TRACE_EVENT(1);
-                return true;
-            };
-            Unit u, next;
-            int round = 0, ordinal = 0, first_stage = 0;
-            bool have = next_unit<kSplit>(p, rounds, round, u);
-            if (have) ok = load_q(u, 0, 0) && load_q(u, 0, 1);
-            while (ok && have) {
-                int look = round;
-                const bool have_next = next_unit<kSplit>(p, rounds, look, next);
-                for (int it = 0; ok && it < u.n_tiles; ++it) {
-                    const int stage = (first_stage + it) & 1;
+                bool terminal_checked = units_done == 0;
+                for (int it = first_tile; it < u.n_tiles; ++it) {
+                    const int stage = (u.n_tiles - 1 - it) % kStages;  // the unit's last tile always lands in stage 0
                     const int n0 = (u.key_block0 - it) * kBlockN;
-                    // The second tile goes where the previous unit ended: its LSE arrays must have left.
-                    if (it == 1 && ordinal > 0 && !(ok = tc::mbar_wait(&bars->lse_drained, (ordinal - 1) & 1))) break;
                     if (k_uses.of(stage) > 0 && !(ok = tc::mbar_wait(&bars->k_empty[stage], (k_uses.of(stage) - 1) & 1))) break;
+                    if (stage == 0 && !terminal_checked) {
+                        // Stage 0 was the previous unit's terminal K stage: its LSE arrays must have left it.
+                        if (!(ok = tc::mbar_wait(&bars->lse_drained, (units_done - 1) & 1))) break;
+                        terminal_checked = true;
+                    }
                     uint8_t* kdst = smem + kKOffset + stage * kTileBytes;
                     tc::mbar_arrive_expect_tx(&bars->k_full[stage], kTileBytes);
                     tc::tma_load_4d(kdst, &kmap, &bars->k_full[stage], 0, u.kvh, n0, u.b, keep);
@@ -336,19 +341,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     v_uses.bump(stage);
                     if (it == 0) TC_TRACE_EVENT(2);
                     if (it + 1 == u.n_tiles) TC_TRACE_EVENT(3);
-                    if (it == 0) {
-                        if (ordinal > 0) ok = load_q(u, ordinal, 1);
-                        if (ok && have_next) ok = load_q(next, ordinal + 1, 0);
-                    }
                 }
-                // A one-tile unit never reloads its predecessor's terminal stage: take that phase here, so that
-                // every phase of the barrier is seen in order.
-                if (ok && u.n_tiles == 1 && ordinal > 0) ok = tc::mbar_wait(&bars->lse_drained, (ordinal - 1) & 1);
-                first_stage = 1 - ((first_stage + u.n_tiles - 1) & 1);
-                ++ordinal;
-                u = next;
-                round = look;
-                have = have_next;
+                ++units_done;
             }
             if (!ok) {
                 atomicCAS(p.status, 0, 11);
@@ -366,30 +360,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             constexpr uint32_t idesc_qk = tc::umma_idesc(128, 128, 1, 0, 0);
             constexpr uint32_t idesc_pv = tc::umma_idesc(128, 128, 1, 0, 1);
             StageCounts uses;  // tiles taken from each ring stage so far (K for warp 9, V for 10 and 11)
-            uint32_t tiles_done = 0;
-            int ordinal = 0, first_stage = 0, round = 0;
-            Unit u;
+            uint32_t tiles_done = 0, units_done = 0;
             bool ok = true;
+            TC_TRACE_DECLARE(warp - kMmaWarp + 1);
             if (warp == kMmaWarp) {
                 // S = Q_h K^T into the score buffer: both operands K-major, 8 steps of 16 along D
                 // (4 per 64-element half). A score MMA may overwrite the buffer once the other head's
                 // softmax warpgroup has pulled its tile into registers; because P has its own columns it
                 // does not wait for any PV.
-                BufferCounts q_uses;  // Q tiles taken from each buffer so far
-                TC_TRACE_DECLARE(1);
+                const uint32_t q_addr = tc::smem_u32(smem + kQOffset);
                 const uint32_t k_addr = tc::smem_u32(smem + kKOffset);
-                while (ok && next_unit<kSplit>(p, rounds, round, u)) {
+                for (int round = 0; ok && round < rounds; ++round) {
+                    const int index = unit_of_round(round, p.total_units);
+                    if (index < 0) continue;
+                    const Unit u = unit_at<kSplit>(p, index);
+                    if (u.n_tiles == 0) continue;
+                    if (!(ok = tc::mbar_wait(&bars->q_full, units_done & 1))) break;
                     for (int it = 0; ok && it < u.n_tiles; ++it) {
-                        const int stage = (first_stage + it) & 1;
+                        const int stage = (u.n_tiles - 1 - it) % kStages;
                         if (!(ok = tc::mbar_wait(&bars->k_full[stage], uses.of(stage) & 1))) break;
                         uses.bump(stage);
                         const uint32_t kb = k_addr + stage * kTileBytes;
                         for (int h = 0; h < 2 && ok; ++h) {
-                            const int buffer = (2 * ordinal + h) % kQBuffers;
-                            if (it == 0) {
-                                if (!(ok = tc::mbar_wait(&bars->q_full[buffer], q_uses.of(buffer) & 1))) break;
-                                q_uses.bump(buffer);
-                            }
                             if (h == 0) {
                                 if (tiles_done > 0) ok = tc::mbar_wait(&bars->s_free[1], (tiles_done - 1) & 1);
                             } else {
@@ -397,23 +389,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                             }
                             if (!ok) break;
                             tc::tc_fence_after_sync();
-                            const uint32_t qb = tc::smem_u32(smem + q_buffer_offset(buffer));
 #pragma unroll
                             for (int ks = 0; ks < 8; ++ks) {
                                 const uint32_t off = uint32_t(ks >> 2) * kHalfBytes + uint32_t(ks & 3) * 32;
-                                tc::umma_ss(tmem + s_column(h), tc::umma_desc_sw128(qb + off, 16, 1024),
+                                tc::umma_ss(tmem + s_column(h), tc::umma_desc_sw128(q_addr + h * kTileBytes + off, 16, 1024),
                                             tc::umma_desc_sw128(kb + off, 16, 1024), idesc_qk, ks > 0);
                             }
                             tc::umma_commit(&bars->s_full[h]);
                             tc::umma_commit(&bars->k_empty[stage]);  // two arrivals per stage: one per head
-                            if (it + 1 == u.n_tiles) tc::umma_commit(&bars->q_empty[buffer]);  // this head's Q tile is read
                             if (it == 0 && h == 0) TC_TRACE_EVENT(10);
                             if (it + 1 == u.n_tiles && h == 1) TC_TRACE_EVENT(11);
                         }
                         ++tiles_done;
                     }
-                    first_stage = 1 - ((first_stage + u.n_tiles - 1) & 1);
-                    ++ordinal;
+                    if (ok) tc::umma_commit(&bars->q_empty);  // every score MMA of this unit has read Q
+                    ++units_done;
                 }
             } else {
                 // O_h += P_h V, one 64-key half at a time: P from TMEM (8 columns per 16 keys), V MN-major
@@ -422,10 +412,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                 const uint32_t v_addr = tc::smem_u32(smem + kVOffset);
                 const uint32_t p_col = tmem + p_column(h);
                 const uint32_t o_col = tmem + o_column(h);
-                TC_TRACE_DECLARE(2 + h);
-                while (ok && next_unit<kSplit>(p, rounds, round, u)) {
+                for (int round = 0; ok && round < rounds; ++round) {
+                    const int index = unit_of_round(round, p.total_units);
+                    if (index < 0) continue;
+                    const Unit u = unit_at<kSplit>(p, index);
+                    if (u.n_tiles == 0) continue;
                     for (int it = 0; ok && it < u.n_tiles; ++it) {
-                        const int stage = (first_stage + it) & 1;
+                        const int stage = (u.n_tiles - 1 - it) % kStages;
                         const uint32_t vb = v_addr + stage * kTileBytes;
                         auto issue_pv_half = [&](int half) {
 #pragma unroll
@@ -439,7 +432,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                         uses.bump(stage);
                         // The first PV of a unit overwrites the accumulator: the previous unit's epilogue must
                         // have read it out of tensor memory.
-                        if (it == 0 && ordinal > 0 && !(ok = tc::mbar_wait(&bars->o_free[h], (ordinal - 1) & 1))) break;
+                        if (it == 0 && units_done > 0 && !(ok = tc::mbar_wait(&bars->o_free[h], (units_done - 1) & 1))) break;
                         if (!(ok = tc::mbar_wait(&bars->p_half[h][0], tiles_done & 1))) break;
                         tc::tc_fence_after_sync();
                         issue_pv_half(0);
@@ -453,8 +446,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                         if (it + 1 == u.n_tiles) TC_TRACE_EVENT(21);
                         ++tiles_done;
                     }
-                    first_stage = 1 - ((first_stage + u.n_tiles - 1) & 1);
-                    ++ordinal;
+                    ++units_done;
                 }
             }
             if (!ok) {
@@ -476,25 +468,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         // Tiles of all of this CTA's units: the two heads take turns at the exponential unit from the first tile
         // of the first unit to the last tile of the last one.
         uint32_t cta_tiles = 0;
-        Unit u;
-        for (int round = 0; next_unit<kSplit>(p, rounds, round, u);) cta_tiles += uint32_t(u.n_tiles);
-        uint32_t tiles_done = 0;
-        StageCounts k_uses;  // tiles that went through each K ring stage so far
-        int first_stage = 0;
+        for (int round = 0; round < rounds; ++round) {
+            const int index = unit_of_round(round, p.total_units);
+            if (index >= 0) cta_tiles += uint32_t(unit_at<kSplit>(p, index).n_tiles);
+        }
+        uint32_t tiles_done = 0, units_done = 0, terminal_uses = 0;  // terminal_uses: tiles that went through K stage 0
         bool ok = true;
 #ifdef TC_TRACE
         unsigned long long* trace_log = (row == 0 && blockIdx.x < 148) ? g_prefill_trace[blockIdx.x][4 + h] : nullptr;
         int trace_count = 0;
 #endif
 
-        for (int round = 0; next_unit<kSplit>(p, rounds, round, u);) {
+        for (int round = 0; round < rounds; ++round) {
+        const int index = unit_of_round(round, p.total_units);
+        if (index < 0) continue;
+        const Unit u = unit_at<kSplit>(p, index);
+        if (u.n_tiles == 0) continue;
         const int n_tiles = u.n_tiles, part = u.part, m0 = u.m0, b = u.b;
         const int head = u.head0 + h;
-        const int terminal = (first_stage + n_tiles - 1) & 1;  // the ring stage this unit's last score MMA reads
         float m_used = -INFINITY, l = 0.f;
 
         for (int it = 0; it < n_tiles; ++it, ++tiles_done) {
-            k_uses.bump((first_stage + it) & 1);
+            if ((n_tiles - 1 - it) % kStages == 0) ++terminal_uses;
             if (ok) ok = tc::mbar_wait(&bars->s_full[h], tiles_done & 1);  // after a failed wait: keep the barrier pattern, skip waits
             if (it == 0) TC_TRACE_EVENT(30);
             tc::tc_fence_after_sync();
@@ -625,10 +620,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         const int rows_here = min(kBlockM, p.tokens - m0);
         float* lse_out = p.lse + (int64_t(b) * p.q_heads + head) * p.tokens + m0;
         const bool bulk_lse = rows_here == kBlockM && (p.tokens & 3) == 0;
-        // The planner's offsets are those of a terminal stage at PREFILL_TERMINAL_K_OFFSET_BYTES (ring stage 0);
-        // when this unit ends in stage 1 the same regions lie one stage further on.
         float* lse_stage = reinterpret_cast<float*>(
-            kHandoff ? smem + terminal * kTileBytes + (h == 0 ? PREFILL_LSE_HEAD0_OFFSET_BYTES : PREFILL_LSE_HEAD1_OFFSET_BYTES)
+            kHandoff ? smem + (h == 0 ? PREFILL_LSE_HEAD0_OFFSET_BYTES : PREFILL_LSE_HEAD1_OFFSET_BYTES)
                      : smem + kBarrierOffset + kBarrierBytes + h * 512);
         // The LSE array goes to the planner's region in the released terminal K stage (or to the dedicated
         // area), is published with one barrier of the head's warpgroup and leaves with one bulk store. Without
@@ -636,7 +629,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
         // next unit's keys as early as possible.
         auto store_lse = [&](bool writes) {
             // Both heads' last score MMAs have read the terminal stage once its "empty" phase completed.
-            if (ok) ok = tc::mbar_wait(&bars->k_empty[terminal], (k_uses.of(terminal) - 1) & 1);
+            if (ok) ok = tc::mbar_wait(&bars->k_empty[0], (terminal_uses - 1) & 1);
             if (writes) lse_stage[row] = row_lse;
             tc::fence_proxy_async_smem();
             wg_barrier(h);
@@ -710,10 +703,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
             }
             store_lse(stores);
         }
-        // O (BF16) goes from the accumulator to global memory through registers: every thread owns one query
-        // row, 256 contiguous bytes of the output, written as sixteen 16-byte stores. No shared memory is staged,
-        // so nothing of this unit stands in the way of the next unit's loads.
-        __nv_bfloat16* out_row = p.out + ((int64_t(b) * p.tokens + m0 + row) * p.q_heads + head) * kDim;
+        // O (BF16) is staged in the output staging buffer in the TMA store layout. The two heads use the buffer in
+        // turn: head 0 of a unit after head 1 of the previous unit, head 1 after head 0 of the same unit.
+        uint8_t* o_stage = smem + kOutStageOffset;
+        if (h == 0) {
+            if (units_done > 0 && ok) ok = tc::mbar_wait(&bars->stage_drained[1], (units_done - 1) & 1);
+        } else {
+            if (ok) ok = tc::mbar_wait(&bars->stage_drained[0], units_done & 1);
+        }
         if (stores) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -740,25 +737,500 @@ prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__
                     }
                 }
             }
-            if (row < rows_here && !bars->abort) {
+            uint8_t* half = o_stage + (c >> 1) * kHalfBytes + row * 128;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint4 word;
-                    word.x = tc::pack_bf16x2(value[i * 8 + 0], value[i * 8 + 1]);
-                    word.y = tc::pack_bf16x2(value[i * 8 + 2], value[i * 8 + 3]);
-                    word.z = tc::pack_bf16x2(value[i * 8 + 4], value[i * 8 + 5]);
-                    word.w = tc::pack_bf16x2(value[i * 8 + 6], value[i * 8 + 7]);
-                    reinterpret_cast<uint4*>(out_row + c * 32)[i] = word;
+            for (int i = 0; i < 4; ++i) {
+                uint4 word;
+                word.x = tc::pack_bf16x2(value[i * 8 + 0], value[i * 8 + 1]);
+                word.y = tc::pack_bf16x2(value[i * 8 + 2], value[i * 8 + 3]);
+                word.z = tc::pack_bf16x2(value[i * 8 + 4], value[i * 8 + 5]);
+                word.w = tc::pack_bf16x2(value[i * 8 + 6], value[i * 8 + 7]);
+                const int chunk = (c & 1) * 4 + i;
+                *reinterpret_cast<uint4*>(half + ((chunk ^ (row & 7)) << 4)) = word;
+            }
+        }
+        tc::fence_proxy_async_smem();
+        wg_barrier(h);  // the whole tile is staged
+        if (row == 0) {
+            if (!bars->abort) {
+                tc::tma_store_4d(&omap, o_stage, 0, head, m0, b);
+                tc::tma_store_4d(&omap, o_stage + kHalfBytes, 64, head, m0, b);
+                tc::bulk_commit();
+                tc::bulk_wait_read_all();  // shared memory must outlive the stores' reads; the writes finish on their own
+            }
+            tc::mbar_arrive(&bars->stage_drained[h]);
+        }
+        } else {
+            // (key split, first finisher) Nothing is staged, but the phases of both barriers advance all the same.
+            tc::tc_fence_before_sync();
+            tc::mbar_arrive(&bars->o_free[h]);
+            if (row == 0) tc::mbar_arrive(&bars->stage_drained[h]);
+        }
+        TC_TRACE_EVENT(34);
+        ++units_done;
+        }
+    }
+
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc::tc_fence_after_sync();
+        tc::tmem_dealloc(tmem, kTmemColumns);
+    }
+}
+
+// =============================================================================== one CTA per unit
+// The schedule for long units (more than 32 key tiles): the grid holds one CTA per unit and the hardware deals
+// them to the SMs as they come free, longest first. The CTA's own Q tile doubles as the staging area of its output
+// tile, so the arena ends behind the V ring.
+constexpr int kRowblockBarrierOffset = kVOffset + kStages * kTileBytes;
+constexpr int rowblock_shared_bytes(bool handoff) {
+    return 1024 + kRowblockBarrierOffset + kBarrierBytes + (handoff ? 0 : kStagingBytes);
+}
+
+struct RowblockBarriers {
+    uint64_t q_full;
+    uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+    uint64_t s_full[2], s_free[2], p_half[2][2], p_lo_free[2], o_done[2];
+    uint32_t tmem_base;
+    int32_t abort;
+    int32_t role[2];  // key-split only: which of the two CTAs of a query tile claimed each head first
+};
+static_assert(sizeof(RowblockBarriers) <= kBarrierBytes, "barrier block");
+
+// kSplit: two CTAs per query tile, the first takes the key tiles nearest the diagonal (rounded up), the
+// second the rest; whichever finishes a head second merges the other's normalised O and LSE into its own
+// (LSE-weighted) and stores. For launches whose query tiles are too few to fill the GPU, where the longest
+// tile alone would set the run time.
+template <bool kHandoff, bool kSplit = false>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_rowblock_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+               const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap omap,
+               const PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    RowblockBarriers* bars = reinterpret_cast<RowblockBarriers*>(smem + kRowblockBarrierOffset);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // Longest query tiles first; neighbouring CTAs share a KV head so K/V tiles hit in L2.
+    const int per_block = p.batch * p.kv_heads * 2 * (kSplit ? 2 : 1);
+    const int m_block = p.m_blocks - 1 - int(blockIdx.x) / per_block;
+    int rest = int(blockIdx.x) % per_block;
+    const int part = kSplit ? (rest & 1) : 0;
+    if (kSplit) rest >>= 1;
+    const int pair = rest & 1;
+    const int kvh = (rest >> 1) % p.kv_heads;
+    const int b = rest / (2 * p.kv_heads);
+    const int head0 = kvh * kGroup + pair * 2;
+    const int m0 = m_block * kBlockM;
+    // Key tiles m_block, m_block-1, ..., 0; this CTA's share is n_tiles of them starting at key_block0.
+    const int all_tiles = m_block + 1;
+    const int near_tiles = kSplit ? (all_tiles + 1) / 2 : all_tiles;
+    const int n_tiles = part == 0 ? near_tiles : all_tiles - near_tiles;
+    const int key_block0 = part == 0 ? m_block : m_block - near_tiles;
+    if (kSplit && n_tiles == 0) return;  // a one-tile row block has nothing to split
+
+    // The TMA producer owns the operand barriers: it initialises them itself and sends for Q and for
+    // the first ring stages at once, so the first loads are in flight while the other warps set up
+    // their barriers and tensor memory. Everything else waits for the CTA barrier below.
+    const uint64_t keep = tc::policy_evict_last(), stream_once = tc::policy_evict_first();
+    auto load_kv = [&](int it) {
+        const int stage = (n_tiles - 1 - it) % kStages;
+        const int n0 = (key_block0 - it) * kBlockN;
+        uint8_t* kdst = smem + kKOffset + stage * kTileBytes;
+        tc::mbar_arrive_expect_tx(&bars->k_full[stage], kTileBytes);
+        tc::tma_load_4d(kdst, &kmap, &bars->k_full[stage], 0, kvh, n0, b, keep);
+        tc::tma_load_4d(kdst + kHalfBytes, &kmap, &bars->k_full[stage], 64, kvh, n0, b, keep);
+        return stage;
+    };
+    auto load_v = [&](int it, int stage) {
+        const int n0 = (key_block0 - it) * kBlockN;
+        uint8_t* vdst = smem + kVOffset + stage * kTileBytes;
+        tc::mbar_arrive_expect_tx(&bars->v_full[stage], kTileBytes);
+        tc::tma_load_4d(vdst, &vmap, &bars->v_full[stage], 0, kvh, n0, b, keep);
+        tc::tma_load_4d(vdst + kHalfBytes, &vmap, &bars->v_full[stage], 64, kvh, n0, b, keep);
+    };
+    if (threadIdx.x == kProducerWarp * 32) {
+        tc::mbar_init(&bars->q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            tc::mbar_init(&bars->k_full[s], 1);
+            tc::mbar_init(&bars->k_empty[s], 2);  // one arrival per head's MMA issuer
+            tc::mbar_init(&bars->v_full[s], 1);
+            tc::mbar_init(&bars->v_empty[s], 2);
+        }
+        tc::mbar_fence_init();
+        tc::tma_prefetch_desc(&qmap);
+        tc::tma_prefetch_desc(&kmap);
+        tc::tma_prefetch_desc(&vmap);
+        tc::mbar_arrive_expect_tx(&bars->q_full, 2 * kTileBytes);
+        for (int h = 0; h < 2; ++h) {
+            uint8_t* dst = smem + kQOffset + h * kTileBytes;
+            tc::tma_load_4d(dst, &qmap, &bars->q_full, 0, head0 + h, m0, b, stream_once);
+            tc::tma_load_4d(dst + kHalfBytes, &qmap, &bars->q_full, 64, head0 + h, m0, b, stream_once);
+        }
+        for (int it = 0; it < kStages && it < n_tiles; ++it) load_v(it, load_kv(it));  // fresh stages: nothing to wait for
+    }
+    if (threadIdx.x == 0) {
+        for (int h = 0; h < 2; ++h) {
+            tc::mbar_init(&bars->s_full[h], 1);
+            tc::mbar_init(&bars->s_free[h], kSoftmaxThreads);
+            tc::mbar_init(&bars->p_half[h][0], kSoftmaxThreads);
+            tc::mbar_init(&bars->p_half[h][1], kSoftmaxThreads);
+            tc::mbar_init(&bars->o_done[h], 1);
+            tc::mbar_init(&bars->p_lo_free[h], 1);
+        }
+        bars->abort = 0;
+        tc::mbar_fence_init();
+    }
+    if (warp == kMmaWarp) {
+        tc::tmem_alloc(&bars->tmem_base, kTmemColumns);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem = bars->tmem_base;
+
+    // The third warpgroup only moves data and issues MMAs: it hands most of its registers to the
+    // two softmax warpgroups, which keep a whole 128-column score row per thread. Each role's code
+    // sits under its own setmaxnreg so that the register allocator sees the right budget.
+    if (warp >= 2 * (kSoftmaxThreads / 32)) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kDataRegisters));
+    if (warp == kProducerWarp) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int it = kStages; it < n_tiles; ++it) {
+                const int stage = (n_tiles - 1 - it) % kStages;
+                const uint32_t parity = (uint32_t(it / kStages) & 1) ^ 1;
+                if (!tc::mbar_wait(&bars->k_empty[stage], parity)) { atomicCAS(p.status, 0, 11); break; }
+                load_kv(it);
+                if (!tc::mbar_wait(&bars->v_empty[stage], parity)) { atomicCAS(p.status, 0, 12); break; }
+                load_v(it, stage);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ MMA issuers
+        // Warp 9 issues every score MMA (the shared score buffer is used 0,1,0,1,... so their order is
+        // fixed anyway); warps 10 and 11 issue PV for head 0 and head 1. Each role is one elected thread.
+        // Issue blocks at the tensor pipe's rate and every barrier check costs such a lone thread
+        // 100-170 cycles, so a thread that is busy issuing one kind of MMA must not be the one that has
+        // to notice that the other kind has become ready.
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = tc::umma_idesc(128, 128, 1, 0, 0);
+            constexpr uint32_t idesc_pv = tc::umma_idesc(128, 128, 1, 0, 1);
+            auto stage_of = [&](int it) { return (n_tiles - 1 - it) % kStages; };
+            auto parity_of = [&](int it) { return uint32_t(it / kStages) & 1; };
+            bool ok = true;
+            if (warp == kMmaWarp) {
+                // S = Q_h K^T into the shared score buffer: both operands K-major, 8 steps of 16 along D
+                // (4 per 64-element half). A score MMA may overwrite the buffer once the other head's
+                // softmax warpgroup has pulled its tile into registers; because P has its own columns it
+                // does not wait for any PV.
+                const uint32_t q_addr = tc::smem_u32(smem + kQOffset);
+                const uint32_t k_addr = tc::smem_u32(smem + kKOffset);
+                ok = tc::mbar_wait(&bars->q_full, 0);
+                for (int it = 0; ok && it < n_tiles; ++it) {
+                    if (!(ok = tc::mbar_wait(&bars->k_full[stage_of(it)], parity_of(it)))) break;
+                    const uint32_t kb = k_addr + stage_of(it) * kTileBytes;
+                    for (int h = 0; h < 2 && ok; ++h) {
+                        if (h == 0) {
+                            if (it > 0) ok = tc::mbar_wait(&bars->s_free[1], uint32_t(it - 1) & 1);
+                        } else {
+                            ok = tc::mbar_wait(&bars->s_free[0], uint32_t(it) & 1);
+                        }
+                        if (!ok) break;
+                        tc::tc_fence_after_sync();
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks) {
+                            const uint32_t off = uint32_t(ks >> 2) * kHalfBytes + uint32_t(ks & 3) * 32;
+                            tc::umma_ss(tmem + s_column(h), tc::umma_desc_sw128(q_addr + h * kTileBytes + off, 16, 1024),
+                                        tc::umma_desc_sw128(kb + off, 16, 1024), idesc_qk, ks > 0);
+                        }
+                        tc::umma_commit(&bars->s_full[h]);
+                        tc::umma_commit(&bars->k_empty[stage_of(it)]);  // two arrivals per stage: one per head
+                    }
+                }
+            } else {
+                // O_h += P_h V, one 64-key half at a time: P from TMEM (8 columns per 16 keys), V MN-major
+                // (row = key, 128 bytes per 64 d; the d halves 16 KiB apart, 8-key groups 1 KiB).
+                const int h = warp - (kMmaWarp + 1);
+                const uint32_t v_addr = tc::smem_u32(smem + kVOffset);
+                const uint32_t p_col = tmem + p_column(h);
+                const uint32_t o_col = tmem + o_column(h);
+                auto issue_pv_half = [&](int it, int half) {
+                    const uint32_t vb = v_addr + stage_of(it) * kTileBytes;
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const int ks = half * 4 + k4;
+                        tc::umma_ts(o_col, p_col + uint32_t(ks) * 8, tc::umma_desc_sw128(vb + ks * 2048, kHalfBytes, 1024),
+                                    idesc_pv, !(it == 0 && ks == 0));
+                    }
+                };
+                for (int it = 0; ok && it < n_tiles; ++it) {
+                    if (!(ok = tc::mbar_wait(&bars->v_full[stage_of(it)], parity_of(it)))) break;
+                    if (!(ok = tc::mbar_wait(&bars->p_half[h][0], uint32_t(it) & 1))) break;
+                    tc::tc_fence_after_sync();
+                    issue_pv_half(it, 0);
+                    tc::umma_commit(&bars->p_lo_free[h]);  // P columns of the first 64 keys may be rewritten
+                    if (!(ok = tc::mbar_wait(&bars->p_half[h][1], uint32_t(it) & 1))) break;
+                    tc::tc_fence_after_sync();
+                    issue_pv_half(it, 1);
+                    tc::umma_commit(&bars->o_done[h]);
+                    tc::umma_commit(&bars->v_empty[stage_of(it)]);
+                }
+            }
+            if (!ok) {
+                atomicCAS(p.status, 0, 13);
+                bars->abort = 1;
+            }
+        }
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegisters));
+        // ------------------------------------------------------------------ softmax warpgroups
+        const int h = warp >> 2;                        // head slot
+        const int row = threadIdx.x & (kSoftmaxThreads - 1);
+        const uint32_t lane_field = uint32_t((warp & 3) * 32) << 16;
+        const uint32_t s_tmem = tmem + lane_field + s_column(h);
+        const uint32_t p_tmem = tmem + lane_field + p_column(h);
+        const uint32_t o_tmem = tmem + lane_field + o_column(h);
+        const int head = head0 + h;
+        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+
+        for (int it = 0; it < n_tiles; ++it) {
+            if (ok) ok = tc::mbar_wait(&bars->s_full[h], uint32_t(it) & 1);  // after a failed wait: keep the barrier pattern, skip waits
+            tc::tc_fence_after_sync();
+            float s[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tc::tmem_ld32(s_tmem + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+            tc::tmem_wait_ld();
+            tc::tc_fence_before_sync();
+            tc::mbar_arrive(&bars->s_free[h]);  // the score buffer may be overwritten by the other head
+            if (it == 0 && part == 0) {
+                // Diagonal tile: key column j is visible to query row i only if j <= i.
+#pragma unroll
+                for (int j = 0; j < 128; ++j) s[j] = j > row ? -INFINITY : s[j];
+            }
+            float mx[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) mx[q] = max3(s[q * 32], s[q * 32 + 1], s[q * 32 + 2]);
+#pragma unroll
+            for (int j = 3; j + 1 < 32; j += 2) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) mx[q] = max3(mx[q], s[q * 32 + j], s[q * 32 + j + 1]);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) mx[q] = fmaxf(mx[q], s[q * 32 + 31]);
+            const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            // Gated rescale: O and l are only brought to a new reference maximum when the row maximum
+            // grew by more than 2^kRescaleThreshold, and only if some row of the warp needs it (the
+            // TMEM accesses are warp-collective). The decision needs only the maxima; the rescale itself
+            // waits for the previous tile's PV further down.
+            float alpha = 1.f;
+            bool rescale = false;
+            if (it == 0) {
+                m_used = tile_max;  // finite: column `row` of the diagonal tile is always visible, other tiles fully
+            } else {
+                const float m_new = fmaxf(m_used, tile_max);
+                const bool grow = (m_new - m_used) * p.scale_log2 > kRescaleThreshold;
+                rescale = __any_sync(0xffffffffu, grow);
+                if (rescale) {
+                    const float m_target = grow ? m_new : m_used;
+                    alpha = tc::fast_exp2((m_used - m_target) * p.scale_log2);
+                    m_used = m_target;
+                }
+            }
+            const float neg_bias = -m_used * p.scale_log2;
+            const float2 bias2 = make_float2(neg_bias, neg_bias);
+            float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            // One chunk = 32 keys: x = s*scale - bias on packed pairs (fma.rn.f32x2), 2^x on the
+            // exponential unit, packed row sums, BF16 pack for this head's P columns.
+            auto chunk = [&](int c, uint32_t (&packed)[16]) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    const float2 x = __ffma2_rn(make_float2(s[c * 32 + j], s[c * 32 + j + 1]), scale2, bias2);
+                    const float2 e = make_float2(tc::fast_exp2(x.x), tc::fast_exp2(x.y));
+                    sum2[(j >> 1) & 1] = __fadd2_rn(sum2[(j >> 1) & 1], e);
+                    packed[j >> 1] = tc::pack_bf16x2(e.x, e.y);
+                }
+            };
+            // PV of the previous tile reads P: its first half (keys 0-63, P chunks 0 and 1) must be done
+            // before chunk 0 is rewritten, all of it before chunk 2 is rewritten or O is rescaled. Waiting
+            // only for the first half here takes the second half's execution off this head's
+            // exp -> PV -> exp chain; the full wait follows before chunk 2, by when it has long finished.
+            bool pv_done = it == 0;
+            if (it > 0) {
+                if (rescale) {
+                    if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1);
+                    pv_done = true;
+                } else {
+                    if (ok) ok = tc::mbar_wait(&bars->p_lo_free[h], uint32_t(it - 1) & 1);
+                }
+                tc::tc_fence_after_sync();
+                if (rescale) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t acc[32];
+                        tc::tmem_ld32(o_tmem + c * 32, acc);
+                        tc::tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) * alpha);
+                        tc::tmem_st32(o_tmem + c * 32, acc);
+                    }
+                    tc::tmem_wait_st();
+                    l *= alpha;
+                }
+            }
+            // The exponential unit is the scarcest resource, so the two heads take turns at it: while
+            // one warpgroup exponentiates, the other head's P is being consumed by the tensor pipe
+            // and its next S tile is produced. Head 0 goes first on every tile.
+            if (h == 1 || it > 0) {
+                // Hardware named barrier: the other warpgroup's 128 threads arrive without blocking when
+                // their exponentials are issued, this warpgroup's 128 threads wait. It wakes faster than
+                // an mbarrier wait; both sides execute it on every path so the counts always match.
+                asm volatile("bar.sync %0, 256;" ::"r"(3 + h) : "memory");
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t packed[16];
+                chunk(c, packed);
+                // Hand the exponential unit over when this head's last exponentials are issued: the
+                // other warpgroup needs about a hundred cycles to wake up.
+                if (c == 3 && (h == 0 || it + 1 < n_tiles))
+                    asm volatile("bar.arrive %0, 256;" ::"r"(3 + (1 - h)) : "memory");
+                if (c == 2) {
+                    // Chunks 0 and 1 were stored a whole chunk of arithmetic ago, so this wait is short.
+                    tc::tmem_wait_st();
+                    tc::tc_fence_before_sync();
+                    tc::mbar_arrive(&bars->p_half[h][0]);
+                }
+                if (c == 2 && !pv_done) {
+                    if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(it - 1) & 1);
+                    tc::tc_fence_after_sync();
+                    pv_done = true;
+                }
+                tc::tmem_st16(p_tmem + c * 16, packed);
+            }
+            tc::tmem_wait_st();
+            tc::tc_fence_before_sync();
+            tc::mbar_arrive(&bars->p_half[h][1]);
+            l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
+        }
+
+        // ------------------------------------------------------------------ epilogue
+        if (ok) ok = tc::mbar_wait(&bars->o_done[h], uint32_t(n_tiles - 1) & 1);
+        if (!ok) {
+            atomicCAS(p.status, 0, 14 + h);
+            bars->abort = 1;
+        }
+        tc::tc_fence_after_sync();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        float row_lse = l > 0.f ? fmaf(m_used, p.scale, logf(l)) : INFINITY;
+        float own_weight = inv;        // what this CTA's accumulator is multiplied by in the stored O
+        float other_weight = 0.f;      // key-split, second finisher: weight of the other CTA's normalised O
+        const float4* other_o = nullptr;
+        bool stores = true;
+        if constexpr (kSplit) {
+            if (all_tiles >= 2) {
+                const int unit = ((((m_block * p.batch + b) * p.kv_heads + kvh) * 2 + pair) * 2) + h;
+                int32_t* claim = p.tickets + 2 * unit;
+                int32_t* ready = claim + 1;
+                float4* slot_o = p.part_o + size_t(unit) * (kBlockM * kDim / 4);
+                float* slot_lse = p.part_lse + size_t(unit) * kBlockM;
+                if (row == 0) bars->role[h] = atomicAdd(claim, 1);
+                wg_barrier(h);
+                if (bars->role[h] == 0) {
+                    // First to finish this head: publish normalised O (coalesced: a warp's rows are
+                    // consecutive float4s of one column group) and LSE, then raise the ready word.
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t acc[32];
+                        tc::tmem_ld32(o_tmem + c * 32, acc);
+                        tc::tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            slot_o[(c * 8 + i) * kBlockM + row] =
+                                make_float4(__uint_as_float(acc[i * 4 + 0]) * inv, __uint_as_float(acc[i * 4 + 1]) * inv,
+                                            __uint_as_float(acc[i * 4 + 2]) * inv, __uint_as_float(acc[i * 4 + 3]) * inv);
+                    }
+                    slot_lse[row] = row_lse;
+                    __threadfence();
+                    wg_barrier(h);
+                    if (row == 0) tc::store_release_gpu(ready, 1);
+                    stores = false;
+                } else {
+                    // Second: the first is past its key loop (it claimed), so this wait is short.
+                    if (row == 0 && !tc::wait_word_gpu(ready, 1)) {
+                        atomicCAS(p.status, 0, 16 + h);
+                        bars->abort = 1;
+                    }
+                    wg_barrier(h);
+                    const float other_lse = __ldcg(slot_lse + row);
+                    const float top = fmaxf(row_lse, other_lse);
+                    const float merged = top + logf(expf(row_lse - top) + expf(other_lse - top));
+                    own_weight = inv * expf(row_lse - merged);
+                    other_weight = expf(other_lse - merged);
+                    row_lse = merged;
+                    other_o = slot_o;
                 }
             }
         }
-        } else {
-            // (key split, first finisher) Nothing is stored, but the barrier's phase advances all the same.
-            tc::tc_fence_before_sync();
-            tc::mbar_arrive(&bars->o_free[h]);
+        if (stores) {
+        // O (bf16) is staged over this head's own Q tile in the TMA store layout; LSE goes to the
+        // planner's region in the released terminal K stage (or to the dedicated area).
+        uint8_t* o_stage = smem + kQOffset + h * kTileBytes;
+        float* lse_stage = reinterpret_cast<float*>(
+            kHandoff ? smem + (h == 0 ? PREFILL_LSE_HEAD0_OFFSET_BYTES : PREFILL_LSE_HEAD1_OFFSET_BYTES)
+                     : smem + kRowblockBarrierOffset + kBarrierBytes + h * 512);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint32_t acc[32];
+            tc::tmem_ld32(o_tmem + c * 32, acc);
+            tc::tmem_wait_ld();
+            float value[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) value[j] = __uint_as_float(acc[j]) * own_weight;
+            if constexpr (kSplit) {
+                if (other_o != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 other = __ldcg(other_o + (c * 8 + i) * kBlockM + row);
+                        value[i * 4 + 0] = fmaf(other.x, other_weight, value[i * 4 + 0]);
+                        value[i * 4 + 1] = fmaf(other.y, other_weight, value[i * 4 + 1]);
+                        value[i * 4 + 2] = fmaf(other.z, other_weight, value[i * 4 + 2]);
+                        value[i * 4 + 3] = fmaf(other.w, other_weight, value[i * 4 + 3]);
+                    }
+                }
+            }
+            uint8_t* half = o_stage + (c >> 1) * kHalfBytes + row * 128;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint4 word;
+                word.x = tc::pack_bf16x2(value[i * 8 + 0], value[i * 8 + 1]);
+                word.y = tc::pack_bf16x2(value[i * 8 + 2], value[i * 8 + 3]);
+                word.z = tc::pack_bf16x2(value[i * 8 + 4], value[i * 8 + 5]);
+                word.w = tc::pack_bf16x2(value[i * 8 + 6], value[i * 8 + 7]);
+                const int chunk = (c & 1) * 4 + i;
+                *reinterpret_cast<uint4*>(half + ((chunk ^ (row & 7)) << 4)) = word;
+            }
         }
-        TC_TRACE_EVENT(34);
-        first_stage = 1 - terminal;
+        lse_stage[row] = row_lse;
+        tc::fence_proxy_async_smem();
+        wg_barrier(h);  // one barrier publishes the O tile and the LSE array of this head
+        const int rows_here = min(kBlockM, p.tokens - m0);
+        float* lse_out = p.lse + (int64_t(b) * p.q_heads + head) * p.tokens + m0;
+        const bool bulk_lse = rows_here == kBlockM && (p.tokens & 3) == 0;
+        if (row == 0 && !bars->abort) {
+            tc::tma_store_4d(&omap, o_stage, 0, head, m0, b);
+            tc::tma_store_4d(&omap, o_stage + kHalfBytes, 64, head, m0, b);
+            if (bulk_lse) tc::bulk_store_1d(lse_out, lse_stage, kBlockM * 4);
+            tc::bulk_commit();
+            tc::bulk_wait_read_all();  // shared memory must outlive the stores' reads; the writes finish on their own
+        }
+        if (!bulk_lse && row < rows_here) lse_out[row] = row_lse;
         }
     }
 
@@ -825,21 +1297,33 @@ bool split_pays_off(const tc::DeviceInfo& info, int64_t batch, int64_t tokens, i
     return m_blocks >= 16 && m_blocks * int64_t(info.sms) * 4 > tile_pairs * 5;
 }
 
+// Short units (up to 32 key tiles, i.e. 4096 tokens) go to one persistent CTA per SM, which saves a CTA's start-up
+// per unit: 13 % at batch 4 x 2048 tokens, 3 % at batch 1 x 2048. Long units go to the schedule with one CTA per
+// unit: the hardware's own dealing balances the SMs better than the fixed deal, and a change of unit inside a
+// persistent CTA costs about as much as a new CTA (measured: the persistent schedule 4-8 % slower at 8192 tokens).
+bool persistent_schedule(const PrefillParams& p) { return p.m_blocks <= 32; }
+
 template <bool kHandoff, bool kSplit>
-int launch(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap, const PrefillParams& p, int sms,
-           cudaStream_t stream) {
-    auto kernel = &prefill_kernel<kHandoff, kSplit>;
-    constexpr int shared = shared_bytes(kHandoff);
+int launch(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap, const CUtensorMap& omap,
+           const PrefillParams& p, int sms, cudaStream_t stream) {
     static thread_local int configured_device = -1;
     int device = 0;
     TC_CUDA(cudaGetDevice(&device));
     if (configured_device != device) {
-        TC_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared));
+        TC_CUDA(cudaFuncSetAttribute(&prefill_kernel<kHandoff, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     shared_bytes(kHandoff)));
+        TC_CUDA(cudaFuncSetAttribute(&prefill_rowblock_kernel<kHandoff, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     rowblock_shared_bytes(kHandoff)));
         configured_device = device;
     }
-    // One persistent CTA per SM (the schedule's shared memory and tensor memory leave room for one only).
-    const unsigned grid = unsigned(p.total_units < sms ? p.total_units : sms);
-    kernel<<<grid, kThreads, shared, stream>>>(qmap, kmap, vmap, p);
+    // Either way the shared memory and the tensor memory of a CTA leave room for one CTA per SM.
+    if (persistent_schedule(p)) {
+        const unsigned grid = unsigned(p.total_units > sms ? sms : p.total_units);
+        prefill_kernel<kHandoff, kSplit><<<grid, kThreads, shared_bytes(kHandoff), stream>>>(qmap, kmap, vmap, omap, p);
+    } else {
+        prefill_rowblock_kernel<kHandoff, kSplit>
+            <<<unsigned(p.total_units), kThreads, rowblock_shared_bytes(kHandoff), stream>>>(qmap, kmap, vmap, omap, p);
+    }
     TC_CUDA(cudaGetLastError());
     return TC_OK;
 }
@@ -855,7 +1339,7 @@ int prefill_common(int device, void* stream, const void* q, const int64_t q_stri
 extern "C" {
 
 #ifdef TC_TRACE
-// Trace builds only: copies the role logs of all CTAs to `host` (synchronises the device).
+// Trace builds only: copy out / clear the role logs of all CTAs (both synchronise the device).
 int tc_debug_prefill_trace(void* host) {
     return cudaMemcpyFromSymbol(host, g_prefill_trace, sizeof(g_prefill_trace)) == cudaSuccess ? 0 : 1;
 }
@@ -945,13 +1429,13 @@ int prefill_common(int device, void* stream, const void* q, const int64_t q_stri
     TC_CUDA(guard.status);
     tc::DeviceScratch scratch;
     if ((status = tc::device_scratch(device, &scratch)) != TC_OK) return status;
-    CUtensorMap qmap, kmap, vmap;
+    CUtensorMap qmap, kmap, vmap, omap;
     if ((status = tc::make_rows_map(&qmap, q, false, q_heads, tokens, batch, q_strides[2], q_strides[1], q_strides[0], kBlockM, 2)) != TC_OK) return status;
     if ((status = tc::make_rows_map(&kmap, k, false, kv_heads, tokens, batch, k_strides[2], k_strides[1], k_strides[0], kBlockN, 2)) != TC_OK) return status;
     if ((status = tc::make_rows_map(&vmap, v, false, kv_heads, tokens, batch, v_strides[2], v_strides[1], v_strides[0], kBlockN, 2)) != TC_OK) return status;
+    if ((status = tc::make_rows_map(&omap, out, false, q_heads, tokens, batch, kDim, q_heads * kDim, tokens * q_heads * kDim, kBlockM, 2)) != TC_OK) return status;
 
     PrefillParams p{};
-    p.out = static_cast<__nv_bfloat16*>(out);
     p.lse = lse;
     p.status = scratch.status;
     p.batch = int(batch);
@@ -976,11 +1460,11 @@ int prefill_common(int device, void* stream, const void* q, const int64_t q_stri
         p.part_lse = reinterpret_cast<float*>(base + split.lse_offset);
         TC_CUDA(cudaMemsetAsync(base, 0, size_t(split.ticket_bytes), cuda_stream));
         p.total_units *= 2;
-        return mapping == 1 ? launch<true, true>(qmap, kmap, vmap, p, info.sms, cuda_stream)
-                            : launch<false, true>(qmap, kmap, vmap, p, info.sms, cuda_stream);
+        return mapping == 1 ? launch<true, true>(qmap, kmap, vmap, omap, p, info.sms, cuda_stream)
+                            : launch<false, true>(qmap, kmap, vmap, omap, p, info.sms, cuda_stream);
     }
-    return mapping == 1 ? launch<true, false>(qmap, kmap, vmap, p, info.sms, cuda_stream)
-                        : launch<false, false>(qmap, kmap, vmap, p, info.sms, cuda_stream);
+    return mapping == 1 ? launch<true, false>(qmap, kmap, vmap, omap, p, info.sms, cuda_stream)
+                        : launch<false, false>(qmap, kmap, vmap, omap, p, info.sms, cuda_stream);
 }
 
 }  // namespace
@@ -1000,8 +1484,13 @@ int tc_prefill_resources(int device, const int64_t q_strides[3], const int64_t k
     const int64_t tiles = (tokens + kBlockM - 1) / kBlockM;
     const int64_t header[12] = {1, tokens, q_heads, kGroup, 1, batch * (q_heads / 2) * tiles, 0, 0, 0, kBlockM, kBlockN, 1};
     for (int i = 0; i < 12; ++i) values[i] = header[i];
-    status = mapping == 1 ? tc::kernel_resources(&prefill_kernel<true>, kThreads, shared_bytes(true), values + 12)
-                          : tc::kernel_resources(&prefill_kernel<false>, kThreads, shared_bytes(false), values + 12);
+    if (tiles <= 32)
+        status = mapping == 1 ? tc::kernel_resources(&prefill_kernel<true>, kThreads, shared_bytes(true), values + 12)
+                              : tc::kernel_resources(&prefill_kernel<false>, kThreads, shared_bytes(false), values + 12);
+    else
+        status = mapping == 1
+                     ? tc::kernel_resources(&prefill_rowblock_kernel<true>, kThreads, rowblock_shared_bytes(true), values + 12)
+                     : tc::kernel_resources(&prefill_rowblock_kernel<false>, kThreads, rowblock_shared_bytes(false), values + 12);
     if (status != TC_OK) return status;
     for (int i = 20; i < 28; ++i) values[i] = 0;
     const int64_t layout[18] = {0, tokens, tokens, q_heads, q_heads / kGroup, 1, MODEL_FAMILY_CODE,

@@ -173,13 +173,17 @@ TMEM_MIN_ALLOCATION = 32    # tcgen05.alloc hands out a power of two of at least
 class TmemRegion:
     """A tile in tensor memory: ``columns`` 32-bit columns (all 128 lanes) at a multiple of
     ``alignment_columns``, alive during steps [start, end) of the map's timeline. With a cyclic timeline
-    ``end`` may exceed the period: the region then stays alive into the next round of the loop."""
+    ``end`` may exceed the period: the region then stays alive into the next round of the loop. ``pipeline``
+    names the software pipeline the tile belongs to when a kernel runs several that do not wait for each other
+    (the two heads of the prefill kernel): steps of different pipelines cannot be compared, so their tiles
+    never share columns."""
 
     name: str
     columns: int
     alignment_columns: int
     start: int
     end: int
+    pipeline: str = ""  # tiles of different (named) pipelines run unsynchronised: they are always alive together
 
 
 @dataclass(frozen=True)
@@ -194,6 +198,8 @@ class TmemMap:
     capacity_columns: int = TMEM_COLUMNS
 
     def alive_together(self, first: TmemRegion, second: TmemRegion) -> bool:
+        if first.pipeline and second.pipeline and first.pipeline != second.pipeline:
+            return True
         shifts = (-len(self.timeline), 0, len(self.timeline)) if self.cyclic else (0,)
         return any(first.start < second.end + shift and second.start + shift < first.end for shift in shifts)
 
@@ -207,24 +213,29 @@ class TmemMap:
 #: after the pull and read by the PV MMA until the head's next pull, and the output accumulators live through
 #: the whole loop: neither can share with anything. The solved map is S (shared) | P0 P1 | O0 O1 = all 512
 #: columns.
-_PREFILL_STEPS = ("score_and_pull_head0", "score_and_pull_head1")
 TMEM_MAPS = {
     "prefill": TmemMap(
-        name="prefill_two_heads_per_cta",
+        name="prefill_two_heads_shared_score",
         regions=(TmemRegion("score_head0", 128, 32, start=0, end=1), TmemRegion("score_head1", 128, 32, start=1, end=2),
                  TmemRegion("probability_head0", 64, 16, start=0, end=2),
                  TmemRegion("probability_head1", 64, 16, start=0, end=2),
                  TmemRegion("output_head0", 128, 32, start=0, end=2), TmemRegion("output_head1", 128, 32, start=0, end=2)),
-        timeline=_PREFILL_STEPS),
-    # Candidate layouts that the planner can price without a kernel being written for them.
-    # Two private score buffers with P stored over the first half of its own retired score buffer: the score
-    # MMA of a head's next tile then has to wait for that head's PV, but never for the other head's pull.
+        timeline=("score_and_pull_head0", "score_and_pull_head1")),
+    # Candidate layouts that the planner can price without a kernel being kept for them.
+    # Every head a pipeline of its own (one MMA issuer per head, nobody waits for the other head): a head's
+    # probabilities are stored over its own retired score buffer, S0/P0 | S1/P1 | O0 | O1. Built and measured:
+    # correct, but the head's chain exp -> PV -> next score MMA -> pull is then serial, and one key tile of both
+    # heads took 4150 cycles against 3320 with the shared score buffer, whose score MMA runs under the other
+    # head's exponentials.
     "prefill_private_scores": TmemMap(
-        name="prefill_private_score_buffers",
-        regions=(TmemRegion("score_head0", 128, 32, start=0, end=1), TmemRegion("probability_head0", 64, 16, start=1, end=4),
-                 TmemRegion("score_head1", 128, 32, start=2, end=3), TmemRegion("probability_head1", 64, 16, start=3, end=6),
-                 TmemRegion("output_head0", 128, 32, start=0, end=4), TmemRegion("output_head1", 128, 32, start=0, end=4)),
-        timeline=("score_head0", "exp_head0", "score_head1", "exp_head1")),
+        name="prefill_two_heads_private_scores",
+        regions=(TmemRegion("score_head0", 128, 32, start=0, end=1, pipeline="head0"),
+                 TmemRegion("score_head1", 128, 32, start=0, end=1, pipeline="head1"),
+                 TmemRegion("probability_head0", 64, 16, start=1, end=3, pipeline="head0"),
+                 TmemRegion("probability_head1", 64, 16, start=1, end=3, pipeline="head1"),
+                 TmemRegion("output_head0", 128, 32, start=0, end=3, pipeline="head0"),
+                 TmemRegion("output_head1", 128, 32, start=0, end=3, pipeline="head1")),
+        timeline=("score_and_pull", "exponentiate", "pv")),
     # One head per CTA, three score/probability buffers in rotation and one output accumulator.
     "prefill_one_head": TmemMap(
         name="prefill_one_head_three_buffers",
