@@ -1,11 +1,12 @@
 """Time line of one prefill launch, measured inside the kernel.
 
-    python -m tilecadence_b200.trace_prefill [--build-only] [--tokens 8192] [--batch 1] [--cta 0]
+    python -m tilecadence_b200.trace_prefill [--build-only] [--tokens 8192] [--batch 1] [--heads 32] [--cta 0]
 
 Builds the prefill kernel with the ``TC_TRACE`` switch (one thread of each role logs (tag, ``%globaltimer``)
 records; roles and tags are listed in ``csrc/prefill/prefill_sm100.cu``), runs one launch and prints, for one
-CTA, every record of every role in microseconds since that CTA's first record, unit by unit. The trace build is
-a library of its own in the build cache; the shipped library never contains the switch.
+CTA, every record of every role in microseconds since that CTA's first record, unit by unit; ``--cta -1`` prints
+one line per CTA instead (its units, first and last record relative to the launch's first). The trace build is a
+library of its own in the build cache; the shipped library never contains the switch.
 """
 from __future__ import annotations
 
@@ -56,6 +57,17 @@ def run(device="cuda:0", batch=1, tokens=8192, cta=0, q_heads=32):
     library.handle.tc_debug_prefill_trace.argtypes = [ctypes.c_void_p]
     if library.handle.tc_debug_prefill_trace(table.ctypes.data) != 0:
         raise RuntimeError("tc_debug_prefill_trace failed")
+    everything = table[table != 0] >> np.uint64(8)
+    first, last = int(everything.min()), int(everything.max())
+    if cta < 0:
+        print(f"batch {batch}, {tokens} tokens, {q_heads} query heads; whole launch {(last - first) / 1e3:.1f} us; per CTA: "
+              "units, first record, last record (us since the launch's first record)")
+        for index in range(table.shape[0]):
+            stamps = table[index][table[index] != 0] >> np.uint64(8)
+            if stamps.size:
+                units = int(((table[index, 0] & np.uint64(0xFF)) == 1).sum())
+                print(f"  CTA {index:3d}: {units:3d} units {(int(stamps.min()) - first) / 1e3:8.2f} {(int(stamps.max()) - first) / 1e3:8.2f}")
+        return
     records = []
     for role, name in enumerate(ROLES):
         for word in table[cta, role]:
@@ -64,8 +76,7 @@ def run(device="cuda:0", batch=1, tokens=8192, cta=0, q_heads=32):
                 records.append((word >> 8, name, TAGS.get(word & 0xFF, str(word & 0xFF))))
     records.sort()
     start = records[0][0]
-    everything = table[table != 0] >> np.uint64(8)
-    print(f"batch {batch}, {tokens} tokens, {q_heads} query heads; whole launch {(int(everything.max()) - int(everything.min())) / 1e3:.1f} us; "
+    print(f"batch {batch}, {tokens} tokens, {q_heads} query heads; whole launch {(last - first) / 1e3:.1f} us; "
           f"CTA {cta}, microseconds since its first record")
     for stamp, name, tag in records:
         print(f"  {(stamp - start) / 1e3:9.2f}  {name:10s} {tag}")
