@@ -444,6 +444,39 @@ def run_ours(args, rank, world, local_rank):
     del whole
     torch.cuda.empty_cache()
 
+    # ------------------------------------------------------------------ shorter sequences (N = 1 only)
+    # 2048-token batches run the persistent schedule of the prefill kernel; the headline runs one CTA per unit.
+    prefill_shapes = None
+    if world == 1:
+        prefill_shapes = []
+        full_ops = cuda_runtime.ops_for(library, "prefill")
+        for sbatch, stokens in ((4, 2048), (1, 2048)):
+            generator = torch.Generator(device=device).manual_seed(PREFILL["seed"] + stokens + sbatch)
+            count = max(2, int(300e6 // (sbatch * stokens * HQ * DIM * 2 * 2.6)))  # rotate through more than L2 holds
+            shape_sets = []
+            for _ in range(count):
+                sq = torch.randn((sbatch, stokens, HQ, DIM), generator=generator, device=device, dtype=torch.bfloat16)
+                sk, sv = (torch.randn((sbatch, stokens, HKV, DIM), generator=generator, device=device,
+                                      dtype=torch.bfloat16) for _ in range(2))
+                shape_sets.append((sq, sk, sv, torch.empty_like(sq),
+                                   torch.empty((sbatch, HQ, stokens), device=device, dtype=torch.float32)))
+            shape_graphs = [graph_of(lambda t=t: full_ops.forward_out(t[0], t[1], t[2], t[3], t[4], empty, empty, 0, 1,
+                                                                      SCALE, True)) for t in shape_sets]
+            shape_turn = [0]
+
+            def shape_step():
+                shape_graphs[shape_turn[0] % count].replay()
+                shape_turn[0] += 1
+
+            shape_ms = timed(shape_step, max(args.steps, 20), max(args.warmup, 3)) / max(args.steps, 20)
+            launches += max(args.steps, 20)
+            tflops = prefill_flops(sbatch, stokens) / (shape_ms * 1e-3) / 1e12
+            prefill_shapes.append({"workload": f"causal GQA prefill B{sbatch} S{stokens} Hq{HQ} Hkv{HKV} D{DIM}, graph replay over "
+                                               f"{count} rotating buffer sets", "us_per_step": shape_ms * 1e3,
+                                   "tflops": tflops, "frac_of_burst": tflops / peaks["bf16"]})
+            del shape_graphs, shape_sets
+            torch.cuda.empty_cache()
+
     # ------------------------------------------------------------------ decode
     def verify_sharded(driver, cache, dq, dkn, dvn, old, dout, dlse, shard_start, route):
         """One more step of a sharded route, outside any timed region, compared (a) bit for bit with the
@@ -786,6 +819,8 @@ def run_ours(args, rank, world, local_rank):
         }
         if prefill_replicas:
             line["prefill_replicas"] = prefill_replicas
+        if prefill_shapes is not None:
+            line["prefill_shapes"] = prefill_shapes
         if checks:
             line["checks"] = checks
         if cpu_baseline:
