@@ -36,13 +36,6 @@ __device__ __forceinline__ void mbar_fence_init() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// One arrival for a whole warp: the lanes meet, then lane 0 arrives (with release semantics, so what the other lanes
-// did before the meeting is covered). For barriers initialised with one count per warp: 32 times fewer operations on
-// the shared-memory pipe than an arrival per thread.
-__device__ __forceinline__ void warp_arrive(uint64_t* bar) {
-    __syncwarp();
-    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
-}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
@@ -85,18 +78,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t start = global_timer_ns();
     for (uint32_t poll = 1;; ++poll) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((poll & 15u) == 0 && global_timer_ns() - start > TC_WAIT_LIMIT_NS) return false;
-    }
-}
-
-// The same bounded wait for a warp that has nothing else to do for a long time: it sleeps between polls, so that
-// it does not take issue slots from the warps that share its scheduler.
-__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t start = global_timer_ns();
-    for (uint32_t poll = 1;; ++poll) {
-        __nanosleep(128);
         if (mbar_try_wait(bar, parity)) return true;
         if ((poll & 15u) == 0 && global_timer_ns() - start > TC_WAIT_LIMIT_NS) return false;
     }
@@ -335,17 +316,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
-}
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
 }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
     asm volatile(

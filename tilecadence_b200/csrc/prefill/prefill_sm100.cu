@@ -6,9 +6,11 @@
 // in the released terminal K span :539-587) and common.cuh:36-78 (tensor checks).
 //
 // A unit of work is a 128-row query tile of the two query heads that share a KV head pair slot, so one
-// K/V tile in shared memory feeds both heads. One persistent CTA per SM works through a list of units
-// dealt from the longest-first order; the loads and the first MMAs of a unit overlap the epilogue of the
-// unit before it. The two dense contractions run on the 5th-generation
+// K/V tile in shared memory feeds both heads. Two schedules of the same pipeline: for sequences of up to
+// 4096 tokens one persistent CTA per SM works through a list of units dealt from the longest-first order,
+// the loads and the first MMAs of a unit overlapping the epilogue of the unit before it (prefill_kernel);
+// for longer ones the grid holds one CTA per unit, longest first (prefill_rowblock_kernel). What follows
+// describes the persistent form. The two dense contractions run on the 5th-generation
 // tensor cores: S = Q_h K^T as a shared x shared tcgen05.mma into one 128-column score buffer in TMEM
 // that the two heads use in strict alternation, O_h += P_h V as a TMEM x shared tcgen05.mma with P_h
 // (BF16) in columns of its own. TMEM: S | P0 P1 | O0 | O1 = 128 + 2*64 + 2*128 = all 512 columns. Roles:
