@@ -95,6 +95,10 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p)
         tc::mbar_fence_init();
         tc::tma_prefetch_desc(&wmap);
         for (int it = 0; it < kStages && it < n_tiles; ++it) load_tile(it);
+        // The rest of this CTA's weight slice is asked into L2 behind the ring: the stream from HBM then runs
+        // through the preceding kernel's tail instead of stopping when the ring is full, and after the wait the
+        // ring refills from L2.
+        for (int it = kStages; it < n_tiles; ++it) tc::tma_prefetch_2d(&wmap, (tile_begin + it) * kTileK, head * kRows);
     }
     tc::grid_dependency_wait();
     tc::grid_launch_dependents();
@@ -110,6 +114,29 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p)
         }
     }
     __syncthreads();
+
+    // Rank 0 finishes the head with one warp per token: what that needs from global memory (norm weights, the
+    // token's position and its rotary table rows: two dependent loads) is sent for now and arrives during the
+    // weight loop instead of after the cluster barrier.
+    const bool is_q = head < p.q_heads, is_k = !is_q && head < p.q_heads + p.kv_heads;
+    const __nv_bfloat16* norm = is_q ? p.q_norm : (is_k ? p.k_norm : nullptr);
+    const bool rotates = p.rope_cos && (is_q || is_k);
+    float norm_weight[4] = {1.f, 1.f, 1.f, 1.f}, rope_c[2] = {1.f, 1.f}, rope_s[2] = {0.f, 0.f};
+    if (rank == 0 && warp < p.tokens) {
+        if (norm) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) norm_weight[j] = __bfloat162float(norm[lane + 32 * j]);
+        }
+        if (rotates) {
+            int position = p.positions[warp];
+            position = position < 0 ? 0 : (position >= p.rope_positions ? p.rope_positions - 1 : position);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                rope_c[j] = p.rope_cos[int64_t(position) * 64 + lane + 32 * j];
+                rope_s[j] = p.rope_sin[int64_t(position) * 64 + lane + 32 * j];
+            }
+        }
+    }
 
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     bool failed = false;
@@ -180,8 +207,6 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p)
     float v[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) v[j] = sums[(lane + 32 * j) * kMaxTokens + token];
-    const bool is_q = head < p.q_heads, is_k = !is_q && head < p.q_heads + p.kv_heads;
-    const __nv_bfloat16* norm = is_q ? p.q_norm : (is_k ? p.k_norm : nullptr);
     if (norm) {
         // RMS norm as Qwen3 applies it per head: x * rsqrt(mean(x^2) + eps) rounded to BF16, times the
         // BF16 weight, rounded to BF16.
@@ -191,19 +216,15 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p)
         const float inv = rsqrtf(square * (1.f / kRows) + p.eps);
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-            v[j] = round_bf16(round_bf16(v[j] * inv) * __bfloat162float(norm[lane + 32 * j]));
+            v[j] = round_bf16(round_bf16(v[j] * inv) * norm_weight[j]);
     } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j) v[j] = round_bf16(v[j]);
     }
-    if (p.rope_cos && (is_q || is_k)) {
-        int position = p.positions[token];
-        position = position < 0 ? 0 : (position >= p.rope_positions ? p.rope_positions - 1 : position);
-        const float* c = p.rope_cos + int64_t(position) * 64;
-        const float* s = p.rope_sin + int64_t(position) * 64;
+    if (rotates) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            const float cs = c[lane + 32 * j], sn = s[lane + 32 * j];
+            const float cs = rope_c[j], sn = rope_s[j];
             const float lo = __fsub_rn(__fmul_rn(v[j], cs), __fmul_rn(v[j + 2], sn));
             const float hi = __fadd_rn(__fmul_rn(v[j + 2], cs), __fmul_rn(v[j], sn));
             v[j] = lo;
