@@ -59,6 +59,18 @@ __host__ __device__ constexpr int shared_bytes(int k_local) { return 1024 + barr
 
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+// Build switch TC_TRACE (off in every shipped library): thread 0 and the producer lane of every CTA record
+// %globaltimer at the points below into a device table that tc_debug_project_trace copies out; see
+// tilecadence_b200/trace_project.py.
+//   0 entry  1 ring and L2 prefetch issued  2 stream dependency resolved  3 token slab ready  4 tile 0 arrived
+//   5 first refilled tile arrived  6 weight loop done  7 cluster barrier passed  8 head stored (rank 0)
+#ifdef TC_TRACE
+__device__ unsigned long long g_project_trace[256][16];
+#define TC_TRACE_POINT(slot) do { if (trace_row) trace_row[slot] = tc::global_timer_ns(); } while (0)
+#else
+#define TC_TRACE_POINT(slot) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(kThreads, 2)
 qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -66,6 +78,11 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rank = int(tc::cluster_cta_rank());
     const int head = blockIdx.y;
+#ifdef TC_TRACE
+    unsigned long long* trace_row = (threadIdx.x == 0 || threadIdx.x == kWarps * 32)
+                                        ? g_project_trace[(blockIdx.y * gridDim.x + blockIdx.x) & 255] : nullptr;
+#endif
+    if (threadIdx.x == 0) TC_TRACE_POINT(0);
 
     const int tiles_total = p.hidden / kTileK;
     const int tile_begin = rank * tiles_total / p.splits, tile_end = (rank + 1) * tiles_total / p.splits;
@@ -99,8 +116,10 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p)
         // through the preceding kernel's tail instead of stopping when the ring is full, and after the wait the
         // ring refills from L2.
         for (int it = kStages; it < n_tiles; ++it) tc::tma_prefetch_2d(&wmap, (tile_begin + it) * kTileK, head * kRows);
+        TC_TRACE_POINT(1);
     }
     tc::grid_dependency_wait();
+    if (threadIdx.x == 0) TC_TRACE_POINT(2);
     tc::grid_launch_dependents();
     // Token slab: this CTA's slice of every token's hidden vector, zero rows for absent tokens.
     {
@@ -114,6 +133,7 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p)
         }
     }
     __syncthreads();
+    if (threadIdx.x == 0) TC_TRACE_POINT(3);
 
     // Rank 0 finishes the head with one warp per token: what that needs from global memory (norm weights, the
     // token's position and its rotary table rows: two dependent loads) is sent for now and arrives during the
@@ -163,6 +183,8 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p)
                 failed = true;
                 break;
             }
+            if (threadIdx.x == 0 && it == 0) TC_TRACE_POINT(4);
+            if (threadIdx.x == 0 && it == kStages) TC_TRACE_POINT(5);
             const uint32_t tile = tc::smem_u32(smem + stage * kTileBytes);
 #pragma unroll
             for (int ks = 0; ks < kTileK / 16; ++ks) {
@@ -176,6 +198,7 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p)
             if (lane == 0) tc::mbar_arrive(&empty[stage]);
         }
         if (failed) atomicCAS(p.status, 0, 22);
+        if (threadIdx.x == 0) TC_TRACE_POINT(6);
         // Partial sums of rows g, g + 8 (of this warp's 16) for tokens 2t, 2t + 1.
         const int g = lane >> 2, t = lane & 3;
         const int row0 = warp * 16 + g;
@@ -192,6 +215,7 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p)
     // ranks > 0 are in rank 0's shared memory afterwards.
     __syncwarp();
     tc::cluster_sync();
+    if (threadIdx.x == 0) TC_TRACE_POINT(7);
     if (rank != 0 || warp == kWarps) return;
 
     // ---------------------------------------------------------------------- finish the head (rank 0)
@@ -236,6 +260,7 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p)
                                 : p.v_out + (int64_t(token) * p.kv_heads + (head - p.q_heads - p.kv_heads)) * kRows;
 #pragma unroll
     for (int j = 0; j < 4; ++j) out[lane + 32 * j] = __float2bfloat16_rn(v[j]);
+    if (threadIdx.x == 0) TC_TRACE_POINT(8);
 }
 
 int encode_weight_map(CUtensorMap* map, const void* weights, int64_t rows, int64_t hidden) {
@@ -256,6 +281,13 @@ int encode_weight_map(CUtensorMap* map, const void* weights, int64_t rows, int64
 }  // namespace
 
 extern "C" {
+
+#ifdef TC_TRACE
+// Trace builds only: copies the 256 x 16 table of time stamps to `host` (synchronises the device).
+int tc_debug_project_trace(void* host) {
+    return cudaMemcpyFromSymbol(host, g_project_trace, sizeof(g_project_trace)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 int tc_qkv_rope_forward_out(int device, void* stream, const void* x, const void* w_qkv, const void* q_norm_weight,
                             const void* k_norm_weight, const float* rope_cos, const float* rope_sin,
