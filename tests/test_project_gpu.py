@@ -133,6 +133,37 @@ def test_decode_may_stream_the_cache_while_the_projection_finishes(project, libr
         assert torch.equal(a.view(torch.int16), b.view(torch.int16))
 
 
+def test_a_chain_of_projections_released_early_gives_the_same_bits(project, library, gpu_device):
+    """Thirty projections back to back on one stream, each with its own weights and token slab and its own
+    outputs: with TC_PROJECT_RELEASE_EARLY a launch's weight stream starts while the launch two places before
+    it is still running; every output must equal the plain chain's bit for bit."""
+    tokens, layers = 4, 30
+    device = gpu_device
+    cos, sin = (t.to(device) for t in oracle.rope_tables(4096))
+    positions = torch.tensor([5, 77, 1024, 4095], dtype=torch.int32, device=device)
+    slabs, weights = [], []
+    for layer in range(layers):
+        x, w, _, _ = make_inputs(500 + layer, tokens, 2560)
+        slabs.append(x.to(device))
+        weights.append(w.to(device))
+    ones = torch.ones(128, device=device, dtype=torch.bfloat16)
+    results = {}
+    for early in (False, True):
+        outs = [[torch.full((tokens, 1, h, 128), float("nan"), device=device, dtype=torch.bfloat16) for h in (32, 8, 8)]
+                for _ in range(layers)]
+        torch.cuda.synchronize()
+        for layer in range(layers):
+            project.forward_out(slabs[layer], weights[layer], positions, *outs[layer], q_norm_weight=ones,
+                                k_norm_weight=ones, rope_cos=cos, rope_sin=sin, release_early=early)
+        torch.cuda.synchronize()
+        assert library.device_status(device.index) == 0
+        results[early] = [[t.cpu() for t in triple] for triple in outs]
+    for plain, released in zip(results[False], results[True]):
+        for a, b in zip(plain, released):
+            assert not torch.isnan(a.float()).any()
+            assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
 def test_argument_checks(project, gpu_device):
     x, w, _, _ = make_inputs(1, 2, 128)
     outs = [torch.empty((2, 1, h, 128), device=gpu_device, dtype=torch.bfloat16) for h in (32, 8, 8)]

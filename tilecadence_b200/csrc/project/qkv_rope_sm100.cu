@@ -45,6 +45,7 @@ struct ProjectParams {
     __nv_bfloat16* v_out;
     int32_t* status;
     int tokens, hidden, q_heads, kv_heads, splits, rope_positions;
+    int release_early;              // TC_PROJECT_RELEASE_EARLY: dependents may be scheduled before this launch's own wait
     float eps;
 };
 
@@ -118,9 +119,14 @@ qkv_rope_kernel(const __grid_constant__ CUtensorMap wmap, const ProjectParams p)
         for (int it = kStages; it < n_tiles; ++it) tc::tma_prefetch_2d(&wmap, (tile_begin + it) * kTileK, head * kRows);
         TC_TRACE_POINT(1);
     }
+    // By default the launch that follows is released once this one has seen its own dependency resolve, so that it
+    // overlaps this launch only. With the caller's promise that the follower's independent part is also safe beside
+    // the kernel BEFORE this one, it is released at once: its CTAs then take the SM slots as that kernel's CTAs leave
+    // them, a few microseconds earlier, and its weight stream starts that much sooner.
+    if (p.release_early) tc::grid_launch_dependents();
     tc::grid_dependency_wait();
     if (threadIdx.x == 0) TC_TRACE_POINT(2);
-    tc::grid_launch_dependents();
+    if (!p.release_early) tc::grid_launch_dependents();
     // Token slab: this CTA's slice of every token's hidden vector, zero rows for absent tokens.
     {
         const int chunks = n_tiles * kTileK / 8;  // 16-byte chunks per token
@@ -294,10 +300,21 @@ int tc_qkv_rope_forward_out(int device, void* stream, const void* x, const void*
                             int64_t rope_positions, const int32_t* positions, void* q_out, void* knew_out,
                             void* vnew_out, int64_t tokens, int64_t hidden, int64_t q_heads, int64_t kv_heads,
                             double rms_eps) {
+    return tc_qkv_rope_forward_out_flags(device, stream, x, w_qkv, q_norm_weight, k_norm_weight, rope_cos, rope_sin,
+                                         rope_positions, positions, q_out, knew_out, vnew_out, tokens, hidden, q_heads,
+                                         kv_heads, rms_eps, 0);
+}
+
+int tc_qkv_rope_forward_out_flags(int device, void* stream, const void* x, const void* w_qkv, const void* q_norm_weight,
+                                  const void* k_norm_weight, const float* rope_cos, const float* rope_sin,
+                                  int64_t rope_positions, const int32_t* positions, void* q_out, void* knew_out,
+                                  void* vnew_out, int64_t tokens, int64_t hidden, int64_t q_heads, int64_t kv_heads,
+                                  double rms_eps, int flags) {
     tc::DeviceInfo info;
     int status = tc::require_sm100(device, &info);
     if (status != TC_OK) return status;
     TC_REQUIRE(x && w_qkv && q_out && knew_out && vnew_out, "null tensor pointer");
+    TC_REQUIRE((flags & ~TC_PROJECT_RELEASE_EARLY) == 0, "unknown projection flag");
     TC_REQUIRE(tokens >= 1 && tokens <= kMaxTokens, "the projection handles 1 to 8 tokens (one per sequence) per call");
     TC_REQUIRE(hidden >= kTileK && hidden <= kMaxHidden && hidden % kTileK == 0, "hidden must be a multiple of 64 up to 16384");
     TC_REQUIRE(q_heads >= 1 && kv_heads >= 1 && q_heads + 2 * kv_heads <= 4096, "head counts out of range");
@@ -341,6 +358,7 @@ int tc_qkv_rope_forward_out(int device, void* stream, const void* x, const void*
     p.splits = int(splits);
     p.rope_positions = int(rope_positions);
     p.eps = float(rms_eps);
+    p.release_early = (flags & TC_PROJECT_RELEASE_EARLY) != 0;
 
     static thread_local int configured_device = -1, configured_shared = 0;
     if (configured_device != device || configured_shared < shared) {

@@ -197,6 +197,9 @@ class Library:
         "tc_qkv_rope_forward_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 6, ctypes.c_int64, *[ctypes.c_void_p] * 4,
             *[ctypes.c_int64] * 4, ctypes.c_double)),
+        "tc_qkv_rope_forward_out_flags": (ctypes.c_int, (
+            ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 6, ctypes.c_int64, *[ctypes.c_void_p] * 4,
+            *[ctypes.c_int64] * 4, ctypes.c_double, ctypes.c_int)),
         "tc_decode_rope_forward_out": (ctypes.c_int, (
             ctypes.c_int, ctypes.c_void_p, *[ctypes.c_void_p] * 8, ctypes.c_void_p, ctypes.c_int64,
             ctypes.c_void_p, ctypes.c_int64, *[ctypes.c_int64] * 5, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
@@ -404,6 +407,8 @@ class PrefillOps:
 #: TC_DECODE_PREFIX_STABLE in the header.
 DECODE_CACHE_STABLE = 1
 DECODE_PREFIX_STABLE = 2
+#: ``flags`` bit of ``tc_qkv_rope_forward_out_flags`` (TC_PROJECT_RELEASE_EARLY in the header).
+PROJECT_RELEASE_EARLY = 1
 
 
 def _decode_flags(cache_stable):
@@ -713,7 +718,10 @@ class ProjectOps:
         self.library, self.q_heads, self.kv_heads = library, q_heads, kv_heads
 
     def forward_out(self, x, w_qkv, positions, q_out, knew_out, vnew_out, q_norm_weight=None, k_norm_weight=None,
-                    rope_cos=None, rope_sin=None, rms_eps=1e-6):
+                    rope_cos=None, rope_sin=None, rms_eps=1e-6, *, release_early=False):
+        """``release_early=True`` (``TC_PROJECT_RELEASE_EARLY``) lets the kernel launched after this one start its
+        independent part while the kernel launched before this one is still running; the caller promises that this
+        is safe (it always is when the follower is another projection)."""
         import torch
 
         tokens, hidden = x.shape
@@ -739,11 +747,15 @@ class ProjectOps:
                      and tuple(positions.shape) == (tokens,) and positions.is_contiguous(),
                      "positions must be contiguous int32[tokens]")
         optional = lambda tensor: _pointer(tensor) if tensor is not None else None
-        self.library.call(
-            "tc_qkv_rope_forward_out", x.device.index, _stream(x), _pointer(x), _pointer(w_qkv),
+        arguments = (
+            x.device.index, _stream(x), _pointer(x), _pointer(w_qkv),
             optional(q_norm_weight), optional(k_norm_weight), optional(rope_cos), optional(rope_sin),
             rope_cos.size(0) if rope_cos is not None else 0, optional(positions), _pointer(q_out), _pointer(knew_out),
             _pointer(vnew_out), tokens, hidden, self.q_heads, self.kv_heads, float(rms_eps))
+        if release_early:
+            self.library.call("tc_qkv_rope_forward_out_flags", *arguments, PROJECT_RELEASE_EARLY)
+        else:
+            self.library.call("tc_qkv_rope_forward_out", *arguments)
 
 
 def ops_for(library, phase=None, q_heads=32):
