@@ -43,6 +43,19 @@ def test_phase_libraries_export_only_their_phase(tmp_path):
         phase_library.call("tc_prefill_workspace_spec")
 
 
+@pytest.mark.parametrize("module,symbol", [("trace_decode", "tc_debug_trace"),
+                                           ("trace_prefill", "tc_debug_prefill_trace"),
+                                           ("trace_project", "tc_debug_project_trace")])
+def test_time_line_builds_are_libraries_of_their_own(library, module, symbol):
+    """The TC_TRACE switch makes a separate library that exports the table reader; the shipped one never does."""
+    import importlib
+
+    path = importlib.import_module(f"tilecadence_b200.{module}").build()
+    assert Path(path) != Path(library.path)
+    assert hasattr(ctypes.CDLL(str(path)), symbol)
+    assert not hasattr(ctypes.CDLL(str(library.path)), symbol)
+
+
 def test_calls_fail_loudly_without_a_b200(library):
     """No CPU fallback: on a machine without an sm_100 device the entry points return an error."""
     import torch
