@@ -15,7 +15,7 @@ reference's saved Qwen3 projections). A step is one forward over that batch.
                  time. ``prefill_replicas`` (N > 1) is the other experiment, one whole batch per rank.
 * ``e2e``        the same metric through the operator API with HOST buffers: every step copies its
                  (slice of) Q/K/V from pinned host memory and reads O and LSE back; copies and kernels of
-                 neighbouring steps overlap on three streams.
+                 neighbouring steps overlap on four streams (two uploads, compute, download).
 * ``roofline``   the prefill kernel against the measured dense BF16 peak.
 * ``decode``     split-KV decode with fused append: config 4 (batch 1, 8192 of 32768 rows valid) and
                  config 5 (batch 4, 32768 rows attended; KV sequence sharded over the ranks when N > 1 and
@@ -346,7 +346,8 @@ def run_ours(args, rank, world, local_rank):
     host_out = [torch.empty(buffers[0]["out"].shape, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     host_lse = [torch.empty(buffers[0]["lse"].shape, dtype=torch.float32).pin_memory() for _ in range(2)]
     slots = [{name: torch.empty_like(tensor) for name, tensor in buffers[0].items()} for _ in range(2)]
-    copy_in, compute, copy_out = (torch.cuda.Stream(device) for _ in range(3))
+    # Two upload streams (Q on one, K and V on the other): two copy engines keep the link a little fuller than one.
+    copy_in, copy_in_kv, compute, copy_out = (torch.cuda.Stream(device) for _ in range(4))
 
     def e2e_run(steps):
         loaded = [None, None]
@@ -355,17 +356,22 @@ def run_ours(args, rank, world, local_rank):
         barrier()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record(copy_in)
+        copy_in_kv.wait_event(start)
         for index in range(steps):
             slot = slots[index % 2]
-            with torch.cuda.stream(copy_in):
-                if computed[index % 2] is not None:
-                    copy_in.wait_event(computed[index % 2])  # the kernel that read this slot is done
-                for name, source in zip("qkv", host):
-                    slot[name].copy_(source, non_blocking=True)
-                loaded[index % 2] = torch.cuda.Event()
-                loaded[index % 2].record(copy_in)
+            uploads = []
+            for stream, names in ((copy_in, "q"), (copy_in_kv, "kv")):
+                with torch.cuda.stream(stream):
+                    if computed[index % 2] is not None:
+                        stream.wait_event(computed[index % 2])  # the kernel that read this slot is done
+                    for name in names:
+                        slot[name].copy_(host["qkv".index(name)], non_blocking=True)
+                    uploads.append(torch.cuda.Event())
+                    uploads[-1].record(stream)
+            loaded[index % 2] = uploads
             with torch.cuda.stream(compute):
-                compute.wait_event(loaded[index % 2])
+                for event in loaded[index % 2]:
+                    compute.wait_event(event)
                 if drained[index % 2] is not None:
                     compute.wait_event(drained[index % 2])  # the previous result left this slot
                 prefill_call(slot)
