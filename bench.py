@@ -746,8 +746,9 @@ def run_ours(args, rank, world, local_rank):
     # ------------------------------------------------------------------ projection -> decode, as a layer runs them
     def layer_chain_case(sets=8, graph_steps=16):
         """One token's projection followed by the config-4 decode step on that layer's cache, `graph_steps`
-        layers back to back in a captured graph; once with the plain decode entry and once with the
-        cache-stable promise, under which the decode kernel streams K/V while the projection finishes."""
+        layers back to back in a captured graph; once with the plain decode entry, once with the cache-stable
+        promise, under which the decode kernel streams K/V while the projection finishes, and once with the
+        projection's early release on top."""
         nonlocal launches
         project_ops = cuda_runtime.ops_for(library, "project")
         hidden, rows = 2560, (HQ + 2 * HKV) * DIM
@@ -768,13 +769,18 @@ def run_ours(args, rank, world, local_rank):
         result = {"workload": "per layer: fused QKV projection (1 token, hidden 2560) then config4 decode step on that "
                               f"layer's cache; {sets} rotating weight and cache sets (larger than L2), {graph_steps} "
                               "layers per captured graph"}
-        for key, promise in (("us_per_layer", False), ("us_per_layer_cache_stable", True)):
+        # Third arm: the projection also releases its follower early (TC_PROJECT_RELEASE_EARLY), so the decode step of
+        # a layer streams its cache beside the decode step of the layer before it as well; in a model that step works
+        # on another layer's cache, so the cache-stable promise holds for both predecessors (here: another cache set).
+        for key, promise, early in (("us_per_layer", False, False), ("us_per_layer_cache_stable", True, False),
+                                    ("us_per_layer_cache_stable_release_early", True, True)):
             steps = [decode_ops.bind_forward_out(q, kc, vc, knew, vnew, old, out, lse, *workspace, 0, 1, True,
                                                  cache_stable=promise) for kc, vc in caches]
 
             def chain():
                 for layer in range(graph_steps):
-                    project_ops.forward_out(x, weights[layer % sets], old, q, knew, vnew, rope_cos=cos, rope_sin=sin)
+                    project_ops.forward_out(x, weights[layer % sets], old, q, knew, vnew, rope_cos=cos, rope_sin=sin,
+                                            release_early=early)
                     steps[layer % sets]()
 
             chain()
@@ -790,6 +796,7 @@ def run_ours(args, rank, world, local_rank):
         moved = rows * hidden * 2 + decode_bytes(1, valid + 1)
         result["bytes_per_layer"] = moved
         result["hbm_gbs_cache_stable"] = moved / (result["us_per_layer_cache_stable"] * 1e-6) / 1e9
+        result["hbm_gbs_cache_stable_release_early"] = moved / (result["us_per_layer_cache_stable_release_early"] * 1e-6) / 1e9
         return result
 
     try:

@@ -110,7 +110,7 @@ def test_decode_may_stream_the_cache_while_the_projection_finishes(project, libr
         weights.append(w.to(device))
     prefix_k, prefix_v = oracle.seeded_normal(77, (tokens, capacity, 8, 128), (tokens, capacity, 8, 128))
     results = {}
-    for promise in (False, True):
+    for promise, early in ((False, False), (True, False), (True, True)):
         caches = [(prefix_k.to(device), prefix_v.to(device)) for _ in range(layers)]
         q, knew, vnew = (torch.empty((tokens, 1, h, 128), device=device, dtype=torch.bfloat16) for h in (32, 8, 8))
         outs = torch.full((layers, tokens, 1, 32, 128), float("nan"), device=device, dtype=torch.bfloat16)
@@ -119,18 +119,22 @@ def test_decode_may_stream_the_cache_while_the_projection_finishes(project, libr
         ws = [torch.empty(n, device=device, dtype=torch.float32) for n in spec[1:3]]
         torch.cuda.synchronize()
         for layer in range(layers):
-            project.forward_out(slabs[layer], weights[layer], old, q, knew, vnew, rope_cos=cos, rope_sin=sin)
+            project.forward_out(slabs[layer], weights[layer], old, q, knew, vnew, rope_cos=cos, rope_sin=sin,
+                                release_early=early)
             decode.forward_out(q, *caches[layer], knew, vnew, old, outs[layer], lses[layer], *ws, 0, 1, True,
                                cache_stable=promise)
         torch.cuda.synchronize()
         assert library.device_status(device.index) == 0
-        results[promise] = (outs.cpu(), lses.cpu(), [k[:, capacity - 2].cpu() for k, _ in caches])
-    plain, early = results[False], results[True]
+        results[promise, early] = (outs.cpu(), lses.cpu(), [k[:, capacity - 2].cpu() for k, _ in caches])
+    plain = results[False, False]
     assert not torch.isnan(plain[0].float()).any()
-    assert torch.equal(plain[0].view(torch.int16), early[0].view(torch.int16))
-    assert torch.equal(plain[1].view(torch.int32), early[1].view(torch.int32))
-    for a, b in zip(plain[2], early[2]):
-        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    # (every layer has a cache of its own here, so with the projection's early release the decode step of a layer
+    # also streams beside the decode step of the layer before it without breaking its promise)
+    for overlapped in (results[True, False], results[True, True]):
+        assert torch.equal(plain[0].view(torch.int16), overlapped[0].view(torch.int16))
+        assert torch.equal(plain[1].view(torch.int32), overlapped[1].view(torch.int32))
+        for a, b in zip(plain[2], overlapped[2]):
+            assert torch.equal(a.view(torch.int16), b.view(torch.int16))
 
 
 def test_a_chain_of_projections_released_early_gives_the_same_bits(project, library, gpu_device):
