@@ -154,6 +154,32 @@ def test_config2_full_size(ops, gpu_device):
     oracle.check_outputs(got_o, got_lse, want_o, want_lse)
 
 
+def test_full_size_properties_causality_and_linearity_in_v(ops, gpu_device):
+    """Two properties that need no oracle pass, at config-2 size. Causality: replacing every key and value row
+    from 5000 on changes no bit of the outputs of the rows before it (a query tile's CTA runs the same
+    instructions on the same data whatever else is in the launch). Linearity: the probabilities do not
+    depend on V, so O(V1 + V2) = O(V1) + O(V2) up to the BF16 roundings of the three outputs."""
+    tokens, cut = 8192, 5000
+    q, k, v = oracle.seeded_normal(21, (1, tokens, 32, 128), (1, tokens, 8, 128), (1, tokens, 8, 128))
+    base_o, base_lse = run_prefill(ops, gpu_device, q, k, v)
+    k2, v2 = k.clone(), v.clone()
+    other_k, other_v = oracle.seeded_normal(22, (1, tokens - cut, 8, 128), (1, tokens - cut, 8, 128))
+    k2[:, cut:], v2[:, cut:] = other_k, other_v
+    changed_o, changed_lse = run_prefill(ops, gpu_device, q, k2, v2)
+    assert torch.equal(bits(base_o[:, :cut]), bits(changed_o[:, :cut]))
+    assert torch.equal(bits(base_lse[:, :, :cut], torch.int32), bits(changed_lse[:, :, :cut], torch.int32))
+    assert not torch.equal(bits(base_o[:, cut:]), bits(changed_o[:, cut:]))
+    _, _, w = oracle.seeded_normal(23, (1, 1, 1, 1), (1, 1, 1, 1), (1, tokens, 8, 128))
+    total = (v.float() + w.float()).to(torch.bfloat16)       # what the kernel sees as V1 + V2 ...
+    second = (total.float() - v.float()).to(torch.bfloat16)  # ... and the V2 that goes with it
+    sum_o, sum_lse = run_prefill(ops, gpu_device, q, k, total)
+    second_o, second_lse = run_prefill(ops, gpu_device, q, k, second)
+    assert torch.equal(bits(sum_lse, torch.int32), bits(base_lse, torch.int32))
+    assert torch.equal(bits(second_lse, torch.int32), bits(base_lse, torch.int32))
+    error = (sum_o.float() - (base_o.float() + second_o.float())).abs().max().item()
+    assert error <= 2 ** -6 * max(1.0, sum_o.float().abs().max().item())
+
+
 def test_long_sequence_rows_against_oracle(ops, gpu_device):
     """32768 tokens, batch 1: every row's LSE is finite and a sample of rows matches the oracle."""
     tokens = 32768
