@@ -170,6 +170,26 @@ def test_config5_full_size(ops, gpu_device):
     assert (out.cpu().float() - got_o.float()).abs().max().item() <= 2e-2
 
 
+def test_full_size_properties_key_order_and_repeatability(ops, gpu_device):
+    """Two properties at config-5 size that need no oracle pass. A step repeated on a copy of the same cache
+    gives the same bits (no run-to-run race in the split merge). Attention does not depend on the order of
+    the cached keys: the same rows in reversed order (values reversed with them) give the same O and LSE up
+    to rounding, although every split then sees other rows."""
+    batch, capacity, length = 4, 32768, 32767
+    q, kcache, vcache, knew, vnew = make_case(31, batch, capacity)
+    old = torch.full((batch,), length, dtype=torch.int32)
+    first_o, first_lse, k_after, _, _ = run_step(ops, gpu_device, q, kcache, vcache, knew, vnew, old)
+    again_o, again_lse, _, _, _ = run_step(ops, gpu_device, q, kcache, vcache, knew, vnew, old)
+    assert torch.equal(bits(first_o), bits(again_o)) and torch.equal(first_lse.view(torch.int32), again_lse.view(torch.int32))
+    assert torch.equal(bits(k_after[:, length]), bits(knew[:, 0]))
+    reversed_k, reversed_v = kcache.clone(), vcache.clone()
+    reversed_k[:, :length] = kcache[:, :length].flip(1)
+    reversed_v[:, :length] = vcache[:, :length].flip(1)
+    other_o, other_lse, _, _, _ = run_step(ops, gpu_device, q, reversed_k, reversed_v, knew, vnew, old)
+    assert (other_o.float() - first_o.float()).abs().max().item() <= 2 ** -8
+    assert torch.allclose(other_lse, first_lse, rtol=1e-5, atol=1e-5)
+
+
 def test_sharded_partials_and_combine(ops, gpu_device):
     """KV-sequence shards produce partials whose LSE-weighted merge equals the unsharded step."""
     batch, capacity, shards = 4, 2048, 4
