@@ -56,6 +56,8 @@ def bits(tensor):
     (1, 65, [64]),                # append lands in the last, one-row tile at the end of capacity
     (4, 1024, [1023, 0, 511, 64]),  # ragged batch, one sequence filling the cache
     (1, 4096, [2500]),
+    (1, 16384, [8193]),           # lengths the reference studies: one row past a tile boundary
+    (2, 16384, [12289, 192]),
 ])
 def test_decode_matches_oracle(ops, gpu_device, batch, capacity, lengths):
     q, kcache, vcache, knew, vnew = make_case(100 + capacity, batch, capacity, fill=lengths)

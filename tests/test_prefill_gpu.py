@@ -198,6 +198,26 @@ def test_long_sequence_rows_against_oracle(ops, gpu_device):
             oracle.check_outputs(got_o[0, rows, g * 4:(g + 1) * 4], got_lse[0, g * 4:(g + 1) * 4, rows], want_o, want_lse)
 
 
+@pytest.mark.parametrize("tokens", [8193, 12289, 4225])
+def test_ragged_long_sequences(ops, gpu_device, tokens):
+    """Lengths the reference studies that are no multiple of the tile (8193, 12289) and one just above the
+    switch between the two schedules: the last query tile holds a single row or 65 rows. Sampled row blocks,
+    the ragged end among them, against the oracle; nothing is written past the last row."""
+    q, k, v = oracle.seeded_normal(tokens, (1, tokens, 32, 128), (1, tokens, 8, 128), (1, tokens, 8, 128))
+    got_o, got_lse = run_prefill(ops, gpu_device, q, k, v)
+    assert torch.isfinite(got_lse).all() and torch.isfinite(got_o.float()).all()
+    for r0, count in ((0, 64), (tokens // 2 - 7, 64), (tokens - 65, 65)):
+        rows = slice(r0, r0 + count)
+        for g in (1, 7):
+            qh = q[0, rows, g * 4:(g + 1) * 4].float().permute(1, 0, 2)
+            scores = (qh @ k[0, :r0 + count, g].float().T) * 128 ** -0.5
+            cols = torch.arange(r0 + count)[None, :]
+            scores.masked_fill_(cols > torch.arange(r0, r0 + count)[:, None], float("-inf"))
+            want_lse = scores.logsumexp(-1)
+            want_o = (scores.softmax(-1) @ v[0, :r0 + count, g].float()).permute(1, 0, 2)
+            oracle.check_outputs(got_o[0, rows, g * 4:(g + 1) * 4], got_lse[0, g * 4:(g + 1) * 4, rows], want_o, want_lse)
+
+
 def test_batch_four_is_four_independent_sequences(ops, gpu_device):
     """Config-3 shape B4 x 8192: every sequence of the batch gives the bits of the same sequence run alone,
     and a sample of rows of the last sequence matches the oracle."""
