@@ -234,6 +234,7 @@ class Library:
         self.path = Path(path)
         self.handle = ctypes.CDLL(str(self.path))
         self.symbols = set()
+        self.functions = {}
         for name, (restype, argtypes) in self.SIGNATURES.items():
             try:
                 function = getattr(self.handle, name)
@@ -242,6 +243,7 @@ class Library:
             function.restype = restype
             function.argtypes = list(argtypes)
             self.symbols.add(name)
+            self.functions[name] = function
         if "tc_last_error" not in self.symbols:
             raise RuntimeError(f"{self.path} does not export the tilecadence_b200 C ABI")
 
@@ -249,9 +251,10 @@ class Library:
         return any(name.startswith(prefix) for name in self.symbols)
 
     def call(self, name, *arguments):
-        if name not in self.symbols:
+        function = self.functions.get(name)
+        if function is None:
             raise RuntimeError(f"{self.path.name} does not export {name}; this library was built for another phase")
-        status = getattr(self.handle, name)(*arguments)
+        status = function(*arguments)
         if status != 0:
             message = self.handle.tc_last_error().decode("utf-8", "replace")
             raise RuntimeError(f"{name}: {message} (status {status})")
@@ -275,9 +278,13 @@ def _strides(tensor):
 
 
 def _stream(tensor):
+    """torch's current stream on the tensor's device as a raw ``cudaStream_t`` value (0 = the default stream)."""
     import torch
 
-    return ctypes.c_void_p(torch.cuda.current_stream(tensor.device).cuda_stream)
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None:  # one C call instead of building a Stream object on every operator call
+        return raw(tensor.device.index)
+    return torch.cuda.current_stream(tensor.device).cuda_stream
 
 
 def _require(condition, message):
@@ -286,7 +293,8 @@ def _require(condition, message):
 
 
 def _pointer(tensor):
-    return ctypes.c_void_p(tensor.data_ptr())
+    """Device address as an integer; every entry point's argtypes declare the slot as a pointer."""
+    return tensor.data_ptr()
 
 
 class PrefillOps:
@@ -356,11 +364,10 @@ class PrefillOps:
         tail = (_pointer(q), _strides(q), _pointer(k), _strides(k), _pointer(v), _strides(v), _pointer(out), _pointer(lse),
                 0, 0, q.size(0), q.size(1), q.size(2), int(num_splits), int(mapping), float(scale), int(bool(causal)))
         function = self.library.handle.tc_prefill_forward_out
-        library, device = self.library, q.device
-        current_stream = torch.cuda.current_stream
+        library, probe = self.library, q
 
         def invoke(_keep=keep):
-            status = function(device.index, ctypes.c_void_p(current_stream(device).cuda_stream), *tail)
+            status = function(probe.device.index, _stream(probe), *tail)
             if status != 0:
                 raise RuntimeError("tc_prefill_forward_out: " + library.handle.tc_last_error().decode("utf-8", "replace"))
 
@@ -433,20 +440,21 @@ class DecodeOps:
         import torch
 
         heads = self.q_heads
-        _require(q.is_cuda and cache.is_cuda and lengths.is_cuda and q.device == cache.device
-                 and q.device == lengths.device, "Q/cache/old_lengths must be CUDA on the same device")
-        _require(q.dim() == 4 and q.size(0) > 0 and q.size(1) == 1 and q.size(2) == heads and q.size(3) == 128,
+        device = q.device
+        _require(q.is_cuda and cache.device == device and lengths.device == device,
+                 "Q/cache/old_lengths must be CUDA on the same device")
+        q_shape, cache_shape = q.shape, cache.shape  # one call each: these checks run on every decode step
+        _require(len(q_shape) == 4 and q_shape[0] > 0 and q_shape[1] == 1 and q_shape[2] == heads and q_shape[3] == 128,
                  f"Q must be [B,1,{heads},128]")
-        _require(cache.dim() == 4 and cache.size(0) == q.size(0) and cache.size(1) >= 4 and cache.size(2) == heads // 4
-                 and cache.size(3) == 128, f"Full capacity cache must be [B,C>=4,{heads // 4},128]")
+        _require(len(cache_shape) == 4 and cache_shape[0] == q_shape[0] and cache_shape[1] >= 4
+                 and cache_shape[2] == heads // 4 and cache_shape[3] == 128,
+                 f"Full capacity cache must be [B,C>=4,{heads // 4},128]")
         _require(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and q.is_contiguous()
                  and cache.is_contiguous() and not q.requires_grad and not cache.requires_grad,
                  "Contiguous BF16 inference Q and FULL capacity cache required")
-        _require(lengths.dtype == torch.int32 and lengths.is_contiguous() and lengths.dim() == 1
-                 and lengths.size(0) == q.size(0) and not lengths.requires_grad,
-                 "old_lengths must be contiguous CUDA int32[B]")
-        for tensor in (q, cache):
-            _require(tensor.data_ptr() % 16 == 0, "16-byte aligned Q/cache required")
+        _require(lengths.dtype == torch.int32 and lengths.is_contiguous() and lengths.shape == (q_shape[0],)
+                 and not lengths.requires_grad, "old_lengths must be contiguous CUDA int32[B]")
+        _require(q.data_ptr() % 16 == 0 and cache.data_ptr() % 16 == 0, "16-byte aligned Q/cache required")
 
     def workspace_spec(self, q, kcache, old_lengths, num_splits, mapping, append):
         self._check_q_cache_lengths(q, kcache, old_lengths)
@@ -459,14 +467,16 @@ class DecodeOps:
         import torch
 
         self._check_q_cache_lengths(q, kcache, old_lengths)
-        _require(vcache.device == q.device and vcache.shape == kcache.shape and vcache.dtype == q.dtype
+        device, dtype = q.device, q.dtype
+        _require(vcache.device == device and vcache.shape == kcache.shape and vcache.dtype == dtype
                  and vcache.is_contiguous() and not vcache.requires_grad, "Vcache must match FULL contiguous BF16 Kcache")
+        new_shape = (q.shape[0], 1, kcache.shape[2], 128)
         for tensor in (knew, vnew):
-            _require(tensor.device == q.device and tensor.dtype == q.dtype
-                     and tuple(tensor.shape) == (q.size(0), 1, kcache.size(2), 128) and tensor.is_contiguous()
-                     and not tensor.requires_grad, "knew/vnew must be contiguous BF16[B,1,Hkv,128]")
+            _require(tensor.device == device and tensor.dtype == dtype and tensor.shape == new_shape
+                     and tensor.is_contiguous() and not tensor.requires_grad,
+                     "knew/vnew must be contiguous BF16[B,1,Hkv,128]")
         for workspace in (workspace_o, workspace_lse):
-            _require(workspace.is_cuda and workspace.device == q.device and workspace.dtype == torch.float32
+            _require(workspace.device == device and workspace.dtype == torch.float32
                      and workspace.is_contiguous() and not workspace.requires_grad,
                      "Contiguous CUDA FP32 workspace required")
 
@@ -523,11 +533,10 @@ class DecodeOps:
             function, tail = self.library.handle.tc_decode_forward_out_flags, tail + (_decode_flags(cache_stable),)
         else:
             function = self.library.handle.tc_decode_forward_out
-        library, device = self.library, q.device
-        current_stream = torch.cuda.current_stream
+        library, probe = self.library, q
 
         def invoke(_keep=keep):
-            status = function(*head, ctypes.c_void_p(current_stream(device).cuda_stream), *tail)
+            status = function(*head, _stream(probe), *tail)
             if status != 0:
                 raise RuntimeError("tc_decode_forward_out: " + library.handle.tc_last_error().decode("utf-8", "replace"))
 
