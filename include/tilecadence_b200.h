@@ -132,8 +132,10 @@ int tc_decode_forward_out(int device, void* stream, const void* q, void* kcache,
  * / vnew, or the decode step of another layer (other caches). TC_DECODE_PREFIX_STABLE is the narrower promise
  * for a preceding kernel that was the previous decode step of the SAME caches: it may have written row
  * old_lengths[b] - 1 and nothing else of the above; then only the tiles that end below that row are fetched
- * early. The two flags are alternatives. If the promise does not hold, results are undefined; flags = 0 is
- * tc_decode_forward_out. No counterpart in the reference. */
+ * early. The two flags are alternatives. A CTA whose share of the cache is longer than 32 tiles (2048 rows) makes
+ * no use of either promise: such a launch is bandwidth-bound from end to end and an early start only competes with
+ * the preceding kernel. If the promise does not hold, results are undefined; flags = 0 is tc_decode_forward_out.
+ * No counterpart in the reference. */
 #define TC_DECODE_CACHE_STABLE 1
 #define TC_DECODE_PREFIX_STABLE 2
 int tc_decode_forward_out_flags(int device, void* stream, const void* q, void* kcache, void* vcache, const void* knew,

@@ -58,6 +58,7 @@ constexpr int kGroup = 4;  // query heads per KV head
 constexpr int kDim = 128;
 constexpr int kMaxSplits = 128;
 constexpr int kPrefetchTiles = 12;  // tiles a CTA may prefetch into L2 beyond its shared-memory ring
+constexpr int kEarlyLimitTiles = 32;  // shares longer than this stream nothing ahead of the stream dependency
 constexpr int kStagingBytes = 2304;  // dedicated O/LSE staging when the handoff is disabled
 constexpr int kBarrierBytes = 256;
 // Cross-GPU exchange of per-rank partials (KV sequence sharded over the ranks of one node). Every
@@ -325,6 +326,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
             const int64_t count = stable_end - tile_begin;
             early_tiles = int(count < 0 ? 0 : (count > n_tiles ? n_tiles : count));
         }
+        // A long share gains nothing from an early start (its launch is bandwidth-bound from end to end) and the
+        // early reads compete with the preceding launch's stream: config 5 ran 5 % slower with them.
+        if (n_tiles > kEarlyLimitTiles) early_tiles = 0;
         auto issue_tile = [&](int it, int slot, int row0) {
             const int stage = (n_tiles - 1 - it) % kStages;  // the last tile always lands in stage 0
             const uint32_t generation = uint32_t(it / kStages);
@@ -370,6 +374,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
         } else {
             // Paged cache: the whole warp looks up the pages of the next 32 tiles with one coalesced
             // load, so the table's latency is paid once per 32 tiles and not once per tile.
+            if (p.cache_stable == 1 && early_tiles == 0) tc::grid_dependency_wait();  // a long share starts late
             bool ok = true;
             for (int first = 0; first < n_tiles && ok; first += 32) {
                 int slot = 0, local = 0;
